@@ -1,0 +1,206 @@
+"""The cache manager: which pages and which state slot each live request holds.
+
+Layers are put into groups by what they need: all layers with the same `PagedKVNeed`
+(kv heads, head size, window) share one group, with one pool of pages and one block
+table per request; a page id of a group addresses the same page in every layer of the
+group.  Layers with a `FixedStateNeed` get a row per state slot instead.  Pages are given
+back when a request ends, when it is preempted, and - in a group with a window - as soon
+as every position of a page lies before the window of the next query.
+
+Prefix reuse (jllm/engine/cache.py:20-57): full pages are hashed in a chain over the
+tokens; a new request takes the longest run of pages whose hashes are known, in every
+group, but always leaves at least its last token to compute.  It is switched off for
+models with a windowed group or with fixed-size state, where a page hit alone does not
+restore what a layer needs.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Optional
+
+import torch
+
+from ..parts.base import FixedStateNeed, PagedKVNeed, PagedLayerCache, StateLayerCache
+from .page_pool import OutOfPages, PagePool, chain_hash
+from .state_slots import StateSlots
+
+
+@dataclass
+class CacheGroup:
+    need: PagedKVNeed
+    layers: list
+    pool: PagePool
+    k: Optional[torch.Tensor] = None     # [layers, num_pages, page_size, kv_heads, head_dim]
+    v: Optional[torch.Tensor] = None
+
+    def bytes_per_page(self, page_size: int, itemsize: int) -> int:
+        return 2 * len(self.layers) * page_size * self.need.num_kv_heads * self.need.head_dim * itemsize
+
+
+@dataclass
+class RequestCache:
+    """What one live request holds."""
+    request_id: object
+    slot: int
+    tables: list                          # per group: page id by logical page index (-1: given back)
+    num_tokens: int = 0                   # tokens whose keys and values are in the cache
+    hashes: list = field(default_factory=list)   # hash chain of the full pages so far
+    freed_upto: list = field(default_factory=list)  # per group: logical pages below this were given back
+    tokens: list = field(default_factory=list)   # token ids in the cache (kept only with prefix reuse)
+
+
+class CacheManager:
+    def __init__(self, needs: list, page_size: int, num_pages: int, max_live: int, prefix_cache: bool = True):
+        self.page_size, self.num_pages, self.max_live = page_size, num_pages, max_live
+        self.groups: list[CacheGroup] = []
+        self.layer_group: dict[int, int] = {}
+        self.state_layers: dict[int, FixedStateNeed] = {}
+        for layer, need in enumerate(needs):
+            if need is None:
+                continue
+            if isinstance(need, FixedStateNeed):
+                self.state_layers[layer] = need
+            elif isinstance(need, PagedKVNeed):
+                for g, grp in enumerate(self.groups):
+                    if grp.need == need:
+                        grp.layers.append(layer)
+                        self.layer_group[layer] = g
+                        break
+                else:
+                    self.layer_group[layer] = len(self.groups)
+                    self.groups.append(CacheGroup(need, [layer], PagePool(num_pages)))
+            else:
+                raise TypeError(f"layer {layer}: unknown cache need {need!r}")
+        self.slots = StateSlots(max_live)
+        self.prefix_cache = bool(prefix_cache) and not self.state_layers and \
+            all(g.need.window is None for g in self.groups)
+        self.live: dict[object, RequestCache] = {}
+        self.stats = {"prefix_hit_pages": 0, "prefix_hit_tokens": 0, "pages_allocated": 0, "pages_released": 0}
+
+    # ------------------------------------------------------------------- storage
+    def allocate_storage(self, dtype: torch.dtype, device) -> dict:
+        """Allocates pages and state rows on `device`; returns the cache view of every layer
+        that has a need (layer index -> PagedLayerCache | StateLayerCache)."""
+        views = {}
+        for g, grp in enumerate(self.groups):
+            shape = (len(grp.layers), self.num_pages, self.page_size, grp.need.num_kv_heads, grp.need.head_dim)
+            grp.k = torch.zeros(shape, dtype=dtype, device=device)
+            grp.v = torch.zeros(shape, dtype=dtype, device=device)
+            for i, layer in enumerate(grp.layers):
+                views[layer] = PagedLayerCache(group=g, k=grp.k[i], v=grp.v[i])
+        for layer, need in self.state_layers.items():
+            views[layer] = StateLayerCache(self.slots.add_layer(layer, need.shape, need.dtype, device))
+        return views
+
+    def bytes_per_page(self, itemsize: int) -> int:
+        return sum(g.bytes_per_page(self.page_size, itemsize) for g in self.groups)
+
+    # ------------------------------------------------------------------ requests
+    def can_admit(self) -> bool:
+        return self.slots.num_free > 0
+
+    def admit(self, request_id, prompt=None) -> RequestCache:
+        """Gives the request a state slot and, with prefix reuse, the pages of the longest
+        known prefix of `prompt`; `num_tokens` tells how many tokens those pages cover."""
+        if request_id in self.live:
+            raise KeyError(f"request {request_id!r} is already live")
+        rc = RequestCache(request_id, self.slots.take(), [[] for _ in self.groups],
+                          freed_upto=[0 for _ in self.groups])
+        self.live[request_id] = rc
+        if self.prefix_cache and prompt is not None and self.groups:
+            P = self.page_size
+            parent, hits = b"", []
+            for i in range((len(prompt) - 1) // P):       # always leaves >= 1 token to compute
+                h = chain_hash(parent, prompt[i * P:(i + 1) * P])
+                pages = [grp.pool.lookup(h) for grp in self.groups]
+                if any(p is None for p in pages):
+                    break
+                hits.append((h, pages))
+                parent = h
+            for h, pages in hits:
+                for g, p in enumerate(pages):
+                    self.groups[g].pool.touch(p)
+                    rc.tables[g].append(p)
+                rc.hashes.append(h)
+            rc.num_tokens = len(hits) * P
+            rc.tokens = list(prompt[:rc.num_tokens])
+            self.stats["prefix_hit_pages"] += len(hits)
+            self.stats["prefix_hit_tokens"] += rc.num_tokens
+        return rc
+
+    def pages_needed(self, rc: RequestCache, new_len: int) -> list:
+        """Pages each group must still allocate so that positions < new_len have a page."""
+        want = -(-new_len // self.page_size)
+        return [max(0, want - len(t)) for t in rc.tables]
+
+    def can_grow(self, rc: RequestCache, new_len: int) -> bool:
+        return all(n <= g.pool.num_free for n, g in zip(self.pages_needed(rc, new_len), self.groups))
+
+    def max_len_allocatable(self, rc: RequestCache) -> int:
+        """The longest length this request could grow to with the pages that are free now."""
+        if not self.groups:
+            return 1 << 60
+        return min((len(t) + g.pool.num_free) * self.page_size for t, g in zip(rc.tables, self.groups))
+
+    def grow(self, rc: RequestCache, new_len: int) -> None:
+        """Allocates pages so that positions < new_len have one; all or nothing."""
+        need = self.pages_needed(rc, new_len)
+        for n, g in zip(need, self.groups):
+            if n > g.pool.num_free:
+                raise OutOfPages(f"need {n} pages, {g.pool.num_free} are free")
+        for n, g, t in zip(need, self.groups, rc.tables):
+            for _ in range(n):
+                t.append(g.pool.alloc())
+            self.stats["pages_allocated"] += n
+
+    def commit(self, rc: RequestCache, new_tokens) -> None:
+        """Records that the step which writes `new_tokens` at positions num_tokens.. has been
+        issued: hashes pages that became full, gives back pages that a window has passed."""
+        P = self.page_size
+        rc.num_tokens += len(new_tokens)
+        if self.prefix_cache:
+            rc.tokens.extend(int(t) for t in new_tokens)
+            while (len(rc.hashes) + 1) * P <= rc.num_tokens:
+                i = len(rc.hashes)
+                parent = rc.hashes[-1] if rc.hashes else b""
+                h = chain_hash(parent, rc.tokens[i * P:(i + 1) * P])
+                for g, grp in enumerate(self.groups):
+                    grp.pool.register(rc.tables[g][i], h)
+                rc.hashes.append(h)
+        for g, grp in enumerate(self.groups):
+            w = grp.need.window
+            if w is None:
+                continue
+            # the next query is at position >= num_tokens and sees keys > num_tokens - w
+            first_needed = max(0, rc.num_tokens - w + 1)
+            upto = first_needed // P
+            for i in range(rc.freed_upto[g], min(upto, len(rc.tables[g]))):
+                if rc.tables[g][i] >= 0:
+                    grp.pool.release([rc.tables[g][i]])
+                    rc.tables[g][i] = -1
+                    self.stats["pages_released"] += 1
+            rc.freed_upto[g] = max(rc.freed_upto[g], min(upto, len(rc.tables[g])))
+
+    def release(self, request_id) -> None:
+        """The request is over (finished or preempted): everything it holds is given back."""
+        rc = self.live.pop(request_id)
+        for g, grp in enumerate(self.groups):
+            held = [p for p in rc.tables[g] if p >= 0]
+            grp.pool.release(held)
+            self.stats["pages_released"] += len(held)
+        self.slots.give_back(rc.slot)
+
+    # -------------------------------------------------------------------- checks
+    def check(self) -> None:
+        """No page lost, none held twice without being counted twice, none both held and free."""
+        for g, grp in enumerate(self.groups):
+            grp.pool.check()
+            holders = [0] * grp.pool.num_pages
+            for rc in self.live.values():
+                for p in rc.tables[g]:
+                    if p >= 0:
+                        holders[p] += 1
+            assert holders == grp.pool.ref, f"group {g}: reference counts {grp.pool.ref} != holders {holders}"
+        assert len(self.slots.held) == len(self.live) == len({rc.slot for rc in self.live.values()})
+        assert len(self.slots.held) + self.slots.num_free == self.max_live

@@ -1,0 +1,80 @@
+// RMSNorm over rows of the 32-bit residual stream, optionally fused with the residual
+// sum that precedes it and with a row gather.
+//
+//   h[r, :] += delta[r, :]           (if delta is given; the sum is kept in 32-bit)
+//   y[i, :]  = h[r, :] * rsqrt(mean(h[r, :]^2) + eps) * weight[:]
+//
+// with r = rows[i] if `rows` is given, else r = i.  When `rows` is given the sum is
+// not written back to h (the gathered rows are the last use of the stream).  Squares,
+// mean, rsqrt and the scaling are 32-bit; the result is rounded once, to the output
+// type.
+#include "common.cuh"
+
+template <typename TD, typename TW, typename TY>
+__global__ void rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__ delta,
+                               const int* __restrict__ rows, const TW* __restrict__ weight,
+                               TY* __restrict__ y, int hidden, float eps, int n_rows_total,
+                               int* __restrict__ status) {
+  __shared__ float scratch[33];
+  const int i = blockIdx.x;
+  int r = i;
+  if (rows != nullptr) {
+    r = rows[i];
+    if (r < 0 || r >= n_rows_total) {
+      if (threadIdx.x == 0) atomicOr(status, JV_STATUS_BAD_ROW);
+      for (int c = threadIdx.x; c < hidden; c += blockDim.x) y[(size_t)i * hidden + c] = from_f32<TY>(0.f);
+      return;
+    }
+  }
+  float* hr = h + (size_t)r * hidden;
+  const TD* dr = delta ? delta + (size_t)r * hidden : nullptr;
+  const bool write_back = (dr != nullptr) && (rows == nullptr);
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+    float v = hr[c];
+    if (dr) v += to_f32(dr[c]);
+    if (write_back) hr[c] = v;
+    ss += v * v;
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = rsqrtf(ss / (float)hidden + eps);
+  TY* yr = y + (size_t)i * hidden;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+    float v = hr[c];                          // this thread's own write, if any
+    if (dr && !write_back) v += to_f32(dr[c]);
+    yr[c] = from_f32<TY>(v * inv * to_f32(weight[c]));
+  }
+}
+
+// h: [n_total, hidden] float (updated in place when delta is given and rows is null);
+// delta: [n_total, hidden] of dtype `delta_dtype` or null; rows: [n_out] int32 or null;
+// weight: [hidden] of dtype `weight_dtype`; y: [n_out, hidden] of dtype `out_dtype`.
+JV_EXPORT int jv_rmsnorm(float* h, const void* delta, int delta_dtype, const int* rows,
+                         const void* weight, int weight_dtype, void* y, int out_dtype, int n_out,
+                         int n_total, int hidden, float eps, int* status, cudaStream_t stream) {
+  if (n_out == 0) return JV_OK;
+  int threads = 32;
+  while (threads < 512 && threads * 4 < hidden) threads *= 2;
+  JV_DISPATCH_DTYPE(out_dtype, TY, JV_DISPATCH_DTYPE(weight_dtype, TW, JV_DISPATCH_DTYPE(delta_dtype, TD,
+      (rmsnorm_kernel<TD, TW, TY><<<n_out, threads, 0, stream>>>(
+          h, (const TD*)delta, rows, (const TW*)weight, (TY*)y, hidden, eps, n_total, status)))));
+  return jv_check_launch();
+}
+
+// Adds delta into the 32-bit stream without a norm: h[r, :] += delta[r, :].
+template <typename TD>
+__global__ void residual_add_kernel(float* __restrict__ h, const TD* __restrict__ delta, size_t n) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; i < n; i += stride) h[i] += to_f32(delta[i]);
+}
+
+JV_EXPORT int jv_residual_add(float* h, const void* delta, int delta_dtype, long long n,
+                              cudaStream_t stream) {
+  if (n == 0) return JV_OK;
+  long long blocks = (n + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  JV_DISPATCH_DTYPE(delta_dtype, TD, (residual_add_kernel<TD><<<(int)blocks, 256, 0, stream>>>(
+                                         h, (const TD*)delta, (size_t)n)));
+  return jv_check_launch();
+}

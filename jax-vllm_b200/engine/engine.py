@@ -1,0 +1,230 @@
+"""The engine's programming entry point, in the manner of the reference's
+(jllm/engine/engine.py:63-233): `make_driver`, `add_request`, `step`, `has_work`,
+`stream`, `start`, `stop`, `prewarm`, with the same names and meanings of arguments
+(max_num_seqs, max_model_len, max_prefill_len, block_size, num_blocks, dtype), token ids
+in and out.  `step` admits, runs ONE batch on the device (decoded tokens and prompt
+portions together) and returns the events of the tokens it produced.
+"""
+
+from __future__ import annotations
+
+import queue
+import threading
+import time
+import traceback
+from typing import Iterator, Optional
+
+import torch
+
+from ..cache import CacheManager
+from ..config import EngineConfig, parse_dtype
+from ..sampling import Sampler
+from .batch import StepEntry
+from .request import EngineStats, Request, SamplingParams, StepEvent
+from .runner import Runner
+from .scheduler import Scheduler
+
+_ACTIVE_SLEEP = 0.0001
+_IDLE_SLEEP = 0.001
+_STREAM_POLL = 0.1
+
+
+class Driver:
+    def __init__(self, model, config: EngineConfig, runner=None, sampler=None):
+        """`runner` and `sampler` default to the device ones; tests of the scheduling pass
+        stand-ins with the same `step`/`sample` methods."""
+        self.model, self.config = model, config
+        self.max_num_seqs, self.max_model_len = config.max_num_seqs, config.max_model_len
+        self.max_prefill_len, self.block_size, self.num_blocks = config.prompt_limit, config.block_size, config.pool_pages
+        self.stats = EngineStats()
+        self.cache = CacheManager(model.cache_needs(), config.block_size, config.pool_pages, config.max_num_seqs,
+                                  config.prefix_cache)
+        self.runner = runner if runner is not None else Runner(model, self.cache, config.device, config.dtype)
+        self.scheduler = Scheduler(self.cache, config.max_tokens_per_step, config.max_model_len, config.prompt_limit,
+                                   self.stats)
+        self.sampler = sampler if sampler is not None else Sampler(config.device)
+        self.requests: dict[int, Request] = {}
+        self.streams: dict[int, "queue.Queue[StepEvent]"] = {}
+        self.streams_lock = threading.Lock()
+        self.id_lock = threading.Lock()
+        self.step_lock = threading.Lock()
+        self.next_id = 0
+        self.stop_event = threading.Event()
+        self.thread: Optional[threading.Thread] = None
+        self.thread_error: Optional[str] = None
+
+
+def make_driver(model, max_num_seqs: int = 4, max_model_len: int = 2048, max_prefill_len: Optional[int] = None,
+                block_size: int = 16, num_blocks: Optional[int] = None, dtype=None, runner=None, sampler=None,
+                **more) -> Driver:
+    """A driver for a loaded model.  `dtype` defaults to the model's compute dtype and must
+    equal it.  `more`: max_tokens_per_step, prefix_cache, decode_split_size, cuda_graphs."""
+    model_dtype = model.ctx.dtype
+    dtype = parse_dtype(dtype) if dtype is not None else model_dtype
+    if dtype != model_dtype:
+        raise ValueError(f"the model was loaded as {model_dtype}, the driver was asked for {dtype}")
+    more.setdefault("decode_split_size", model.ctx.decode_split_size)
+    if more["decode_split_size"] != model.ctx.decode_split_size:
+        raise ValueError("decode_split_size is fixed when the model is loaded")
+    cfg = EngineConfig(dtype=dtype, max_num_seqs=max_num_seqs, max_model_len=max_model_len,
+                       max_prefill_len=max_prefill_len, block_size=block_size, num_blocks=num_blocks,
+                       device=str(model.ctx.device), **more)
+    return Driver(model, cfg, runner=runner, sampler=sampler)
+
+
+def add_request(driver: Driver, prompt_ids, sampling: Optional[SamplingParams] = None) -> int:
+    _raise_if_failed(driver)
+    sp = sampling or SamplingParams()
+    prompt = [int(t) for t in prompt_ids]
+    vocab = driver.model.spec.vocab_size
+    if any(t < 0 or t >= vocab for t in prompt):
+        raise ValueError(f"prompt holds token ids outside [0, {vocab})")
+    driver.scheduler.validate(prompt, sp)
+    with driver.id_lock:
+        rid = driver.next_id
+        driver.next_id += 1
+    req = Request(request_id=rid, prompt_ids=prompt, sampling=sp, arrival=time.perf_counter())
+    with driver.streams_lock:
+        driver.streams[rid] = queue.Queue()
+    with driver.step_lock:
+        driver.requests[rid] = req
+        driver.scheduler.add(req)
+    return rid
+
+
+def has_work(driver: Driver) -> bool:
+    return driver.scheduler.has_work()
+
+
+def step(driver: Driver) -> list:
+    """One scheduler iteration: at most one batch on the device; returns its StepEvents."""
+    _raise_if_failed(driver)
+    with driver.step_lock:
+        return _step_locked(driver)
+
+
+def _step_locked(driver: Driver) -> list:
+    sched = driver.scheduler
+    plan = sched.schedule()
+    if not plan:
+        return []
+    entries = [StepEntry(driver.cache.live[s.request.request_id], s.tokens, (len(s.tokens) - 1,) if s.wants_logits else ())
+               for s in plan]
+    logits = driver.runner.step(entries)
+    sched.committed(plan)
+    driver.stats.steps += 1
+    sampled = [s for s in plan if s.wants_logits]
+    events: list = []
+    if not sampled:
+        return events
+    temps = [s.request.sampling.temperature for s in sampled]
+    seeds = [s.request.sampling.seed if s.request.sampling.seed is not None else s.request.request_id for s in sampled]
+    counters = [len(s.request.output_ids) for s in sampled]
+    tokens = driver.sampler.sample(logits, temps, seeds, counters)
+    both = torch.cat([tokens, driver.runner.status_word()]).tolist()     # one copy back, which also synchronises
+    toks, status = both[:-1], both[-1]
+    if status:
+        driver.runner.clear_status()
+        from ..ops import raise_on_status
+        raise_on_status(status)
+    now = time.perf_counter()
+    for s, tok in zip(sampled, toks):
+        req = s.request
+        req.output_ids.append(int(tok))
+        if req.first_token_time is None:
+            req.first_token_time = now
+        driver.stats.emitted_tokens += 1
+        done = len(req.output_ids) >= req.sampling.max_new_tokens or \
+            (req.sampling.eos_id is not None and tok == req.sampling.eos_id)
+        if done:
+            sched.finish(req)
+        events.append(StepEvent(req.request_id, int(tok), done))
+    return events
+
+
+def generate(driver: Driver, prompts, sampling=None) -> list:
+    """Runs the prompts (lists of token ids) to completion; returns the generated token ids of
+    each, in order.  `sampling`: one SamplingParams for all, or one per prompt."""
+    if sampling is None or isinstance(sampling, SamplingParams):
+        sampling = [sampling] * len(prompts)
+    ids = [add_request(driver, p, sp) for p, sp in zip(prompts, sampling)]
+    reqs = [driver.requests[i] for i in ids]
+    while any(not r.finished for r in reqs):
+        if not step(driver) and not has_work(driver):
+            break
+    for i in ids:
+        with driver.streams_lock:
+            driver.streams.pop(i, None)
+        driver.requests.pop(i, None)
+    return [list(r.output_ids) for r in reqs]
+
+
+# --------------------------------------------------------------- streams and thread
+def stream(driver: Driver, request_id: int) -> Iterator[StepEvent]:
+    """Events of one request as the background thread produces them."""
+    _raise_if_failed(driver)
+    with driver.streams_lock:
+        q = driver.streams.get(request_id)
+    if q is None:
+        raise KeyError(f"unknown or already-drained request_id: {request_id}")
+    while True:
+        try:
+            ev = q.get(timeout=_STREAM_POLL)
+        except queue.Empty:
+            _raise_if_failed(driver)
+            if driver.stop_event.is_set() and (driver.thread is None or not driver.thread.is_alive()):
+                raise RuntimeError("engine stopped before request finished")
+            continue
+        yield ev
+        if ev.finished:
+            with driver.streams_lock:
+                driver.streams.pop(request_id, None)
+            driver.requests.pop(request_id, None)
+            return
+
+
+def start(driver: Driver) -> None:
+    if driver.thread is not None and driver.thread.is_alive():
+        return
+    driver.thread_error = None
+    driver.stop_event.clear()
+    driver.thread = threading.Thread(target=_driver_loop, args=(driver,), name="engine", daemon=True)
+    driver.thread.start()
+
+
+def stop(driver: Driver, join: bool = True) -> None:
+    driver.stop_event.set()
+    if join and driver.thread is not None:
+        driver.thread.join()
+        driver.thread = None
+
+
+def _driver_loop(driver: Driver) -> None:
+    try:
+        while not driver.stop_event.is_set():
+            events = step(driver)
+            if events:
+                with driver.streams_lock:
+                    for ev in events:
+                        q = driver.streams.get(ev.request_id)
+                        if q is not None:
+                            q.put(ev)
+                continue
+            time.sleep(_ACTIVE_SLEEP if has_work(driver) else _IDLE_SLEEP)
+    except Exception as exc:  # the latch: every later call re-raises (jllm/engine/engine.py:230-233)
+        driver.thread_error = f"{type(exc).__name__}: {exc}"
+        driver.stop_event.set()
+        traceback.print_exc()
+
+
+def prewarm(driver: Driver) -> float:
+    """Compiles what the model needs and runs one tiny batch, so that the first request does
+    not pay for it.  Returns the seconds it took."""
+    t0 = time.perf_counter()
+    driver.runner.warm_up()
+    return time.perf_counter() - t0
+
+
+def _raise_if_failed(driver: Driver) -> None:
+    if driver.thread_error is not None:
+        raise RuntimeError(f"engine thread failed: {driver.thread_error}")

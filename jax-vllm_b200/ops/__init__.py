@@ -1,0 +1,288 @@
+"""Python faces of the CUDA kernels in `csrc/`.
+
+Every function here checks device, dtype, shape and contiguity of what it is given,
+then passes raw pointers and the current CUDA stream to an `extern "C"` launcher loaded
+by `csrc.build`.  There is no CPU path and no library fallback: a tensor on the CPU, a
+missing compiler or a failed launch raises.  Matrix products of 16-bit operands go to
+cuBLAS through `torch.mm` (a library product, as in the reference, whose every product
+is XLA's); every other operation on the forward path is a kernel of this package.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+
+import torch
+
+from ..csrc import build as _build
+
+DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
+STATUS_BITS = {1: "token id outside the embedding table", 2: "page id outside the pool or missing from the block table",
+               4: "row index outside the batch", 8: "a bounded wait inside a kernel ran out"}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_fn_cache: dict[tuple[str, str], object] = {}
+_status: dict[int, torch.Tensor] = {}
+
+
+def _fn(lib: str, name: str, argtypes):
+    key = (lib, name)
+    f = _fn_cache.get(key)
+    if f is None:
+        f = getattr(_build.load(lib), name)
+        f.argtypes = argtypes
+        f.restype = c_int
+        _fn_cache[key] = f
+    return f
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _check(rc: int, what: str) -> None:
+    if rc == 0:
+        return
+    if rc == 2:
+        raise KernelError(f"{what}: these sizes are outside what the kernel handles")
+    raise KernelError(f"{what}: the launch failed ({torch.cuda.get_device_name()}; "
+                      f"the kernels are built for sm_100a only)")
+
+
+def _cuda(t: torch.Tensor, name: str, dtype=None, contiguous=True) -> torch.Tensor:
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise KernelError(f"{name} must be a CUDA tensor (this engine has no CPU path)")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, got {t.dtype}")
+    if contiguous and not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+    return t
+
+
+def _code(t: torch.Tensor, name: str) -> int:
+    try:
+        return DTYPE_CODE[t.dtype]
+    except KeyError:
+        raise KernelError(f"{name}: dtype {t.dtype} is not supported (float32 or bfloat16)") from None
+
+
+def _ptr(t) -> int:
+    return 0 if t is None else t.data_ptr()
+
+
+def status_word(device=None) -> torch.Tensor:
+    """The int32 word (one per device) in which kernels record indices outside their tables."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    idx = dev.index if dev.index is not None else torch.cuda.current_device()
+    w = _status.get(idx)
+    if w is None:
+        w = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
+        _status[idx] = w
+    return w
+
+
+def raise_on_status(value: int) -> None:
+    if value:
+        msgs = [m for bit, m in STATUS_BITS.items() if value & bit]
+        raise KernelError("a kernel met " + "; ".join(msgs) + f" (status {value})")
+
+
+def check_status(device=None) -> None:
+    """Reads the status word (a device synchronisation) and raises if a kernel set it."""
+    w = status_word(device)
+    v = int(w.item())
+    if v:
+        w.zero_()
+        raise_on_status(v)
+
+
+# ------------------------------------------------------------------------ embedding
+def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """out[n, :] = table[ids[n], :] as float32."""
+    _cuda(table, "table"); _cuda(ids, "ids", torch.int32)
+    n, (vocab, hidden) = ids.numel(), table.shape
+    if out is None:
+        out = torch.empty((n, hidden), dtype=torch.float32, device=table.device)
+    _cuda(out, "out", torch.float32)
+    f = _fn("embed", "jv_embed_gather", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p])
+    _check(f(table.data_ptr(), _code(table, "table"), ids.data_ptr(), out.data_ptr(), n, hidden, vocab,
+             status_word(table.device).data_ptr(), _stream()), "embed_gather")
+    return out
+
+
+# ----------------------------------------------------------------------------- norm
+def rmsnorm(h: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.dtype,
+            delta: torch.Tensor | None = None, rows: torch.Tensor | None = None) -> torch.Tensor:
+    """RMSNorm of rows of the float32 stream `h`, after adding `delta` (if given).
+
+    Without `rows` every row is normalised and, when `delta` is given, `h` is updated
+    in place with the sum.  With `rows` (int32) only those rows are produced and `h`
+    stays as it is.
+    """
+    _cuda(h, "h", torch.float32); _cuda(weight, "weight")
+    n_total, hidden = h.shape
+    if weight.shape != (hidden,):
+        raise KernelError(f"norm weight has shape {tuple(weight.shape)}, rows have {hidden} elements")
+    if delta is not None:
+        _cuda(delta, "delta")
+        if delta.shape != h.shape:
+            raise KernelError("delta and h differ in shape")
+    if rows is not None:
+        _cuda(rows, "rows", torch.int32)
+    n_out = n_total if rows is None else rows.numel()
+    y = torch.empty((n_out, hidden), dtype=out_dtype, device=h.device)
+    f = _fn("norm", "jv_rmsnorm", [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int,
+                                   c_int, c_int, c_int, c_float, c_void_p, c_void_p])
+    _check(f(h.data_ptr(), _ptr(delta), 0 if delta is None else _code(delta, "delta"), _ptr(rows),
+             weight.data_ptr(), _code(weight, "weight"), y.data_ptr(), _code(y, "out"), n_out, n_total, hidden,
+             float(eps), status_word(h.device).data_ptr(), _stream()), "rmsnorm")
+    return y
+
+
+def residual_add(h: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
+    """h += delta, the sum kept in float32."""
+    _cuda(h, "h", torch.float32); _cuda(delta, "delta")
+    if delta.shape != h.shape:
+        raise KernelError("delta and h differ in shape")
+    f = _fn("norm", "jv_residual_add", [c_void_p, c_void_p, c_int, c_longlong, c_void_p])
+    _check(f(h.data_ptr(), delta.data_ptr(), _code(delta, "delta"), h.numel(), _stream()), "residual_add")
+    return h
+
+
+# ----------------------------------------------------------------------- activation
+def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
+    """silu(gate) * up for a packed [n, 2*inter] tensor (gate columns first)."""
+    _cuda(gate_up, "gate_up")
+    n, two_i = gate_up.shape
+    if two_i % 2:
+        raise KernelError("packed gate|up needs an even number of columns")
+    act = torch.empty((n, two_i // 2), dtype=gate_up.dtype, device=gate_up.device)
+    f = _fn("activation", "jv_swiglu", [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(f(gate_up.data_ptr(), act.data_ptr(), _code(gate_up, "gate_up"), n, two_i // 2, _stream()), "swiglu")
+    return act
+
+
+# --------------------------------------------------------- rope + q/k norm + kv write
+def rope_kv(qkv: torch.Tensor, positions: torch.Tensor, token_entry: torch.Tensor, block_table: torch.Tensor,
+            inv_freq: torch.Tensor | None, q_norm_w, k_norm_w, eps: float, k_cache, v_cache,
+            n_q_heads: int, n_kv_heads: int, head_dim: int) -> None:
+    """Normalises and rotates the query and key heads of `qkv` in place and writes the new
+    keys and values into the paged cache (see csrc/rope_kv.cu).  `inv_freq` None = no
+    rotation.  `k_cache`/`v_cache` None = the layer writes no cache (queries only)."""
+    _cuda(qkv, "qkv"); _cuda(positions, "positions", torch.int32); _cuda(token_entry, "token_entry", torch.int32)
+    _cuda(block_table, "block_table", torch.int32)
+    n, width = qkv.shape
+    heads = n_q_heads + (2 * n_kv_heads if k_cache is not None else 0)
+    if width < heads * head_dim:
+        raise KernelError(f"qkv has {width} columns, {heads} heads of {head_dim} need {heads * head_dim}")
+    rot_dim = 0
+    if inv_freq is not None:
+        _cuda(inv_freq, "inv_freq", torch.float32)
+        rot_dim = 2 * inv_freq.numel()
+    w_code = 0
+    for w, nm in ((q_norm_w, "q_norm"), (k_norm_w, "k_norm")):
+        if w is not None:
+            _cuda(w, nm)
+            if w.shape != (head_dim,):
+                raise KernelError(f"{nm} weight has shape {tuple(w.shape)}, head size is {head_dim}")
+            w_code = _code(w, nm)
+    if (q_norm_w is not None and k_norm_w is not None) and q_norm_w.dtype != k_norm_w.dtype:
+        raise KernelError("q_norm and k_norm weights differ in dtype")
+    page_size = num_pages = 1
+    if k_cache is not None:
+        _cuda(k_cache, "k_cache", qkv.dtype); _cuda(v_cache, "v_cache", qkv.dtype)
+        if k_cache.shape != v_cache.shape or k_cache.shape[2:] != (n_kv_heads, head_dim):
+            raise KernelError(f"cache shape {tuple(k_cache.shape)} does not fit {n_kv_heads} kv heads of {head_dim}")
+        num_pages, page_size = k_cache.shape[0], k_cache.shape[1]
+    f = _fn("rope_kv", "jv_rope_kv", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
+                                      c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p, c_int, c_int, c_int,
+                                      c_int, c_int, c_int, c_void_p, c_void_p])
+    _check(f(qkv.data_ptr(), _code(qkv, "qkv"), qkv.stride(0), positions.data_ptr(), token_entry.data_ptr(),
+             block_table.data_ptr(), block_table.shape[1], _ptr(inv_freq), rot_dim, _ptr(q_norm_w), _ptr(k_norm_w),
+             w_code, float(eps), _ptr(k_cache), _ptr(v_cache), n, n_q_heads, n_kv_heads, head_dim, page_size,
+             num_pages, status_word(qkv.device).data_ptr(), _stream()), "rope_kv")
+
+
+# ------------------------------------------------------------------------ attention
+def attn_simt_tokens_per_tile(n_q_heads: int, n_kv_heads: int) -> int:
+    g = n_q_heads // n_kv_heads
+    return 16 // min(g, 16)
+
+
+def attn_simt(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+              block_table: torch.Tensor, cu_seqlens: torch.Tensor, start_pos: torch.Tensor, work: torch.Tensor,
+              n_work: int, n_q_heads: int, n_kv_heads: int, head_dim: int, window: int, scale: float,
+              split_size: int = 0, n_splits: int = 0) -> None:
+    """Paged causal attention on CUDA cores (csrc/attn_simt.cu).  `work` is [n_work, 2] int32
+    (entry, first token of the tile); with `n_splits` > 0 the work items are single tokens
+    whose keys are split into `n_splits` ranges of `split_size` positions."""
+    for t, nm in ((q, "q"), (out, "out"), (k_cache, "k_cache"), (v_cache, "v_cache")):
+        _cuda(t, nm, q.dtype, contiguous=(nm != "q"))
+    for t, nm in ((block_table, "block_table"), (cu_seqlens, "cu_seqlens"), (start_pos, "start_pos"), (work, "work")):
+        _cuda(t, nm, torch.int32)
+    if n_work == 0:
+        return
+    part_o = part_ml = None
+    if n_splits > 0:
+        part_o = torch.empty(n_work * n_q_heads * n_splits * head_dim, dtype=torch.float32, device=q.device)
+        part_ml = torch.empty(n_work * n_q_heads * n_splits * 2, dtype=torch.float32, device=q.device)
+    f = _fn("attn_simt", "jv_attn_simt", [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                          c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                          c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p,
+                                          c_void_p])
+    _check(f(q.data_ptr(), q_stride, out.data_ptr(), out.stride(0), _code(q, "q"), _ptr(part_o), _ptr(part_ml),
+             k_cache.data_ptr(), v_cache.data_ptr(), block_table.data_ptr(), block_table.shape[1],
+             cu_seqlens.data_ptr(), start_pos.data_ptr(), work.data_ptr(), n_work, n_q_heads, n_kv_heads, head_dim,
+             k_cache.shape[1], k_cache.shape[0], int(window), float(scale), int(split_size), int(n_splits),
+             status_word(q.device).data_ptr(), _stream()), "attn_simt")
+
+
+# --------------------------------------------------------------------------- linear
+def gemm_simt(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """x [M, K] times weight [N, K] transposed, accumulated in float32 on CUDA cores."""
+    _cuda(x, "x", contiguous=False); _cuda(weight, "weight")
+    if x.dim() != 2 or weight.dim() != 2 or x.shape[1] != weight.shape[1] or x.stride(1) != 1:
+        raise KernelError(f"gemm shapes {tuple(x.shape)} x {tuple(weight.shape)}^T do not fit")
+    m, k = x.shape
+    n = weight.shape[0]
+    y = torch.empty((m, n), dtype=out_dtype, device=x.device)
+    f = _fn("gemm_simt", "jv_gemm_tn_simt", [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int,
+                                             c_int, c_int, c_int, c_void_p])
+    _check(f(x.data_ptr(), _code(x, "x"), x.stride(0), weight.data_ptr(), _code(weight, "weight"), weight.stride(0),
+             y.data_ptr(), _code(y, "out"), y.stride(0), m, n, k, _stream()), "gemm_simt")
+    return y
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """y = x @ weight.T.
+
+    float32 weights: the CUDA-core product of this package in true 32-bit (16-bit
+    activations are read as they are and widened inside).  bfloat16 weights and
+    activations: cuBLAS through torch.mm, accumulating in 32-bit, the result in
+    `out_dtype` (bfloat16 by default, float32 for logits)."""
+    out_dtype = out_dtype or x.dtype
+    if weight.dtype == torch.float32 or x.dtype == torch.float32:
+        return gemm_simt(x, weight, out_dtype)
+    _cuda(x, "x", torch.bfloat16, contiguous=False); _cuda(weight, "weight", torch.bfloat16)
+    if out_dtype == torch.bfloat16:
+        return torch.mm(x, weight.t())
+    return torch.mm(x, weight.t(), out_dtype=out_dtype)
+
+
+# ------------------------------------------------------------------------- sampling
+def sample(logits: torch.Tensor, temperature: torch.Tensor, seeds: torch.Tensor, counters: torch.Tensor) -> torch.Tensor:
+    """One token per row of float32 logits: argmax where temperature is 0, else a draw from
+    softmax(logits / temperature) that depends on (seed, counter) of the row only."""
+    _cuda(logits, "logits", torch.float32); _cuda(temperature, "temperature", torch.float32)
+    _cuda(seeds, "seeds", torch.int64); _cuda(counters, "counters", torch.int64)
+    rows, vocab = logits.shape
+    out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    f = _fn("sampling", "jv_sample", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p])
+    _check(f(logits.data_ptr(), rows, vocab, temperature.data_ptr(), seeds.data_ptr(), counters.data_ptr(),
+             out.data_ptr(), _stream()), "sample")
+    return out

@@ -1,0 +1,112 @@
+"""Grouped-query causal attention over the paged cache.
+
+    qkv = x @ [Wq; Wk; Wv]^T                     one product over the packed matrix
+    q, k = per-head RMSNorm (optional), rotation  csrc/rope_kv.cu, in place; k, v -> cache
+    o    = softmax(q k^T * scale + mask) v        over the request's pages
+    y    = o @ Wo^T
+
+Formulas as in the reference (jllm/model/common.py:107-137,173-214): query head h reads kv
+head h // (Hq/Hkv); key j is visible to the query at position p iff j <= p (and
+j > p - window if the layer has a window); the scale is a parameter of the spec.  The
+three projection matrices are stored packed so that one product reads the input once.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from .base import PagedKVNeed, Part, TensorSpec
+from .registry import POSITIONS, build, register_mixer
+
+
+class Attention(Part):
+    kernels = ("rope_kv", "attn_simt", "gemm_simt")
+
+    def __init__(self, spec, prefix, ctx):
+        self.spec, self.ctx = spec, ctx
+        self.prefix = f"{prefix}.{spec.prefix}" if spec.prefix else prefix
+        self.hq, self.hkv, self.d = spec.num_heads, spec.num_kv_heads, spec.head_dim
+        if self.hq % self.hkv:
+            raise ValueError(f"{self.hq} query heads are not a multiple of {self.hkv} kv heads")
+        if self.d % 16 or not 16 <= self.d <= 256:
+            raise ValueError(f"head size {self.d} is not supported: the attention kernels take multiples of 16 "
+                             f"from 16 to 256")
+        self.position = build(POSITIONS, "position encoding", spec.position, self.prefix, ctx) \
+            if spec.position is not None else None
+        if self.position is not None and self.position.dim > self.d:
+            raise ValueError("rotary dim exceeds the head size")
+        self.window = int(spec.window) if spec.window else 0
+        self.writes_cache = True          # set False by the model for a layer that reads another's cache
+        self.w_qkv = self.w_o = self.q_norm = self.k_norm = None
+
+    # -------------------------------------------------------------------- weights
+    def _names(self):
+        p = self.prefix
+        return {k: f"{p}.{k}.weight" for k in ("q_proj", "k_proj", "v_proj", "o_proj", "q_norm", "k_norm")}
+
+    def tensor_specs(self):
+        n, s = self._names(), self.spec
+        specs = {n["q_proj"]: TensorSpec((self.hq * self.d, s.hidden_size)),
+                 n["o_proj"]: TensorSpec((s.hidden_size, self.hq * self.d))}
+        if self.writes_cache:
+            specs[n["k_proj"]] = TensorSpec((self.hkv * self.d, s.hidden_size))
+            specs[n["v_proj"]] = TensorSpec((self.hkv * self.d, s.hidden_size))
+        if s.qk_norm_eps is not None:
+            specs[n["q_norm"]] = TensorSpec((self.d,), kind="vector", init="ones_normal")
+            if self.writes_cache:
+                specs[n["k_norm"]] = TensorSpec((self.d,), kind="vector", init="ones_normal")
+        return specs
+
+    def bind(self, tensors):
+        n = self._names()
+        mats = [tensors[n["q_proj"]]]
+        if self.writes_cache:
+            mats += [tensors[n["k_proj"]], tensors[n["v_proj"]]]
+        mats = [self.compute_weight(m, self.ctx) for m in mats]
+        if len({m.dtype for m in mats}) > 1:
+            mats = [m.to(torch.float32) for m in mats]
+        self.w_qkv = torch.cat(mats, dim=0).contiguous()
+        self.w_o = self.compute_weight(tensors[n["o_proj"]], self.ctx).contiguous()
+        if self.spec.qk_norm_eps is not None:
+            self.q_norm = tensors[n["q_norm"]].contiguous()
+            self.k_norm = tensors[n["k_norm"]].contiguous() if self.writes_cache else None
+            if self.k_norm is not None and self.k_norm.dtype != self.q_norm.dtype:
+                self.q_norm, self.k_norm = self.q_norm.float(), self.k_norm.float()
+
+    # ---------------------------------------------------------------------- cache
+    def cache_need(self):
+        return PagedKVNeed(self.hkv, self.d, self.window or None)
+
+    def tile_tokens(self):
+        return ops.attn_simt_tokens_per_tile(self.hq, self.hkv)
+
+    # ----------------------------------------------------------------------- step
+    def forward(self, x, step, cache):
+        dt = self.ctx.dtype
+        qkv = ops.linear(x, self.w_qkv, dt)
+        table = step.block_tables[cache.group]
+        writes = self.writes_cache and cache.writes
+        ops.rope_kv(qkv, step.positions, step.token_entry, table,
+                    self.position.table() if self.position is not None else None,
+                    self.q_norm, self.k_norm, self.spec.qk_norm_eps or 0.0,
+                    cache.k if writes else None, cache.v if writes else None, self.hq, self.hkv, self.d)
+        out = torch.empty((step.n_tokens, self.hq * self.d), dtype=dt, device=x.device)
+        self.attend(qkv, out, step, cache, table)
+        return ops.linear(out, self.w_o, dt)
+
+    def attend(self, qkv, out, step, cache, table):
+        work, n_work = step.tile_work[self.tile_tokens()]
+        common = (cache.k, cache.v, table, step.cu_seqlens, step.start_pos)
+        if n_work:
+            ops.attn_simt(qkv, qkv.stride(0), out, *common, work, n_work, self.hq, self.hkv, self.d,
+                          self.window, self.spec.scale)
+        dwork, n_dec = step.decode_work
+        if n_dec:
+            split = self.ctx.decode_split_size
+            n_splits = max(1, -(-step.max_seq_len // split))
+            ops.attn_simt(qkv, qkv.stride(0), out, *common, dwork, n_dec, self.hq, self.hkv, self.d,
+                          self.window, self.spec.scale, split_size=split, n_splits=n_splits)
+
+
+register_mixer("attention", Attention)

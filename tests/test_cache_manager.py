@@ -1,0 +1,190 @@
+"""The page pool and the cache manager on the host (no GPU): order of reuse, reference
+counts, prefix hashes, windows, state slots, and invariants under random request orders."""
+
+import random
+
+import pytest
+
+from jax_vllm_b200.cache import CacheManager, OutOfPages, PagePool, chain_hash
+from jax_vllm_b200.parts import FixedStateNeed, PagedKVNeed
+
+FULL = PagedKVNeed(2, 16)
+WIN = PagedKVNeed(2, 16, window=20)
+
+
+def test_alloc_order_and_reversed_release():
+    # as the reference's pool behaves (tests/test_paged.py:87-106), minus its sink page
+    pool = PagePool(7)
+    got = [pool.alloc() for _ in range(3)]
+    assert got == [0, 1, 2]
+    pool.release(got)
+    assert pool.free_pages() == [3, 4, 5, 6, 2, 1, 0]
+    pool.check()
+
+
+def test_out_of_pages_and_double_release():
+    pool = PagePool(2)
+    a, b = pool.alloc(), pool.alloc()
+    with pytest.raises(OutOfPages):
+        pool.alloc()
+    pool.release([a])
+    with pytest.raises(RuntimeError, match="more often"):
+        pool.release([a])
+    pool.release([b])
+    assert pool.num_free == 2
+    pool.check()
+
+
+def test_touch_takes_a_cached_page_off_the_free_list_and_alloc_evicts_hashes():
+    pool = PagePool(3)
+    p = pool.alloc()
+    h = chain_hash(b"", [1, 2, 3])
+    pool.register(p, h)
+    pool.release([p])
+    assert pool.lookup(h) == p and p in pool.free_pages()
+    pool.touch(p)
+    assert p not in pool.free_pages() and pool.ref[p] == 1
+    pool.touch(p)
+    pool.release([p]); pool.release([p])
+    # p is now at the tail; taking every page drops its hash when p is handed out again
+    for _ in range(3):
+        pool.alloc()
+    assert pool.lookup(h) is None
+    pool.check()
+
+
+def test_first_hash_and_first_page_win():
+    pool = PagePool(4)
+    a, b = pool.alloc(), pool.alloc()
+    h1, h2 = chain_hash(b"", [1]), chain_hash(b"", [2])
+    pool.register(a, h1); pool.register(b, h1); pool.register(a, h2)
+    assert pool.lookup(h1) == a and pool.lookup(h2) is None and pool.hash_of[b] is None
+
+
+def test_chain_hash_depends_on_parent_and_tokens():
+    h = chain_hash(b"", [1, 2])
+    assert h == chain_hash(b"", [1, 2]) and h != chain_hash(b"", [2, 1]) and h != chain_hash(h, [1, 2])
+
+
+def test_groups_by_need_and_state_layers():
+    m = CacheManager([FULL, WIN, FULL, None, FixedStateNeed((4, 3)), WIN], page_size=8, num_pages=10, max_live=2)
+    assert [g.layers for g in m.groups] == [[0, 2], [1, 5]]
+    assert m.layer_group == {0: 0, 2: 0, 1: 1, 5: 1} and list(m.state_layers) == [4]
+    assert m.prefix_cache is False          # a window and fixed state switch prefix reuse off
+    assert m.bytes_per_page(2) == 2 * (2 * 2 * 8 * 2 * 16 * 2)
+
+
+def test_grow_commit_release_and_slots():
+    m = CacheManager([FULL, FULL], page_size=4, num_pages=6, max_live=2, prefix_cache=False)
+    a = m.admit("a")
+    assert a.slot == 0 and m.pages_needed(a, 9) == [3]
+    m.grow(a, 9); m.commit(a, list(range(9)))
+    b = m.admit("b")
+    assert b.slot == 1 and not m.can_admit()
+    assert m.max_len_allocatable(b) == 12 and not m.can_grow(b, 13)
+    with pytest.raises(OutOfPages):
+        m.grow(b, 13)
+    assert b.tables == [[]]                  # all or nothing
+    m.grow(b, 12); m.check()
+    m.release("a"); m.check()
+    assert m.groups[0].pool.num_free == 3 and m.can_admit()
+    c = m.admit("c")
+    assert c.slot == 0
+    m.release("b"); m.release("c"); m.check()
+    assert m.groups[0].pool.num_free == 6
+    with pytest.raises(KeyError):
+        m.release("c")
+
+
+def test_window_pages_are_given_back_as_the_window_passes():
+    m = CacheManager([WIN], page_size=8, num_pages=5, max_live=1)
+    rc = m.admit("r")
+    n = 0
+    for step in range(12):
+        m.grow(rc, n + 7)
+        m.commit(rc, [0] * 7)
+        n += 7
+        first_needed = max(0, n - 20 + 1)
+        assert all((p == -1) == ((i + 1) * 8 <= first_needed) for i, p in enumerate(rc.tables[0]))
+        assert sum(p >= 0 for p in rc.tables[0]) <= 4
+        m.check()
+    assert n == 84                          # far more tokens than the 40 the pool holds
+    m.release("r"); m.check()
+    assert m.groups[0].pool.num_free == 5
+
+
+def test_prefix_reuse_hits_full_pages_but_leaves_a_token():
+    m = CacheManager([FULL], page_size=4, num_pages=8, max_live=2)
+    toks = list(range(100, 112))            # three full pages
+    a = m.admit("a", toks)
+    assert a.num_tokens == 0
+    m.grow(a, 12); m.commit(a, toks)
+    assert len(a.hashes) == 3
+    b = m.admit("b", toks)                  # same prompt: 2 pages hit, the last page is computed
+    assert b.num_tokens == 8 and b.tables[0] == a.tables[0][:2]
+    assert [m.groups[0].pool.ref[p] for p in a.tables[0]] == [2, 2, 1]
+    m.check()
+    m.release("a"); m.release("b"); m.check()
+    c = m.admit("c", toks + [7])            # freed pages keep content and hash: 3 pages hit now
+    assert c.num_tokens == 12 and m.stats["prefix_hit_pages"] == 5
+    d = m.admit("d", [1] + toks)            # different first page: nothing
+    assert d.num_tokens == 0
+    m.check()
+
+
+def test_eviction_drops_prefix():
+    m = CacheManager([FULL], page_size=2, num_pages=3, max_live=2)
+    a = m.admit("a", [1, 2, 3, 4, 5]); m.grow(a, 5); m.commit(a, [1, 2, 3, 4, 5]); m.release("a")
+    b = m.admit("b", [9, 9, 9, 9, 9, 9])    # takes all three pages: a's hashes go
+    m.grow(b, 6); m.commit(b, [9] * 6); m.release("b")
+    c = m.admit("c", [1, 2, 3, 4, 5])
+    assert c.num_tokens == 0
+    m.check()
+
+
+@pytest.mark.parametrize("seed", range(6))
+@pytest.mark.parametrize("needs,prefix", [([FULL, FULL], True), ([FULL, WIN], False), ([FULL], False)])
+def test_random_orders_lose_no_page(seed, needs, prefix):
+    rng = random.Random(seed)
+    m = CacheManager(needs, page_size=4, num_pages=24, max_live=4, prefix_cache=prefix)
+    shared = [rng.randrange(50) for _ in range(16)]
+    live, next_id = {}, 0
+    for _ in range(400):
+        op = rng.random()
+        if op < 0.25 and m.can_admit():
+            prompt = (shared[: rng.choice([0, 4, 8, 16])] + [rng.randrange(50) for _ in range(rng.randrange(1, 20))])
+            rc = m.admit(next_id, prompt)
+            assert rc.num_tokens < len(prompt)
+            live[next_id] = (rc, prompt)
+            next_id += 1
+        elif op < 0.85 and live:
+            rid = rng.choice(list(live))
+            rc, toks = live[rid]
+            n = rng.randrange(1, 9)
+            new = (toks[rc.num_tokens:rc.num_tokens + n] + [rng.randrange(50) for _ in range(n)])[:n]
+            if m.can_grow(rc, rc.num_tokens + n):
+                before = rc.num_tokens
+                m.grow(rc, before + n)
+                m.commit(rc, new)
+                assert rc.num_tokens == before + n
+            else:
+                with pytest.raises(OutOfPages):
+                    m.grow(rc, rc.num_tokens + n)
+        elif live:
+            rid = rng.choice(list(live))
+            m.release(rid)
+            del live[rid]
+        m.check()
+        for g in m.groups:                  # no page is in two live tables unless it is a shared prefix page
+            seen = {}
+            for rc, _ in live.values():
+                for p in rc.tables[m.groups.index(g)]:
+                    if p >= 0:
+                        seen[p] = seen.get(p, 0) + 1
+            assert all(n == g.pool.ref[p] for p, n in seen.items())
+            if not prefix:
+                assert all(n == 1 for n in seen.values())
+    for rid in list(live):
+        m.release(rid)
+    m.check()
+    assert all(g.pool.num_free == 24 for g in m.groups) and m.slots.num_free == 4
