@@ -32,6 +32,7 @@ HEADERS = ["common.cuh"]
 
 _loaded: dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()
+_dir_lock = threading.Lock()
 
 
 class BuildError(RuntimeError):
@@ -52,7 +53,17 @@ def _nvcc() -> str:
                      "the CUDA kernels of this engine cannot be built and there is no fallback")
 
 
+_dir_cache: list = []
+
+
 def _build_dir() -> Path:
+    with _dir_lock:
+        if not _dir_cache:
+            _dir_cache.append(_find_build_dir())
+        return _dir_cache[0]
+
+
+def _find_build_dir() -> Path:
     env = os.environ.get("JAX_VLLM_B200_BUILD_DIR")
     cands = [Path(env)] if env else []
     cands.append(SRC_DIR / "_build")
@@ -60,9 +71,8 @@ def _build_dir() -> Path:
     for d in cands:
         try:
             d.mkdir(parents=True, exist_ok=True)
-            probe = d / f".w{os.getpid()}"
-            probe.write_bytes(b"")
-            probe.unlink()
+            with tempfile.NamedTemporaryFile(dir=d, prefix=".probe"):
+                pass
             return d
         except OSError:
             continue
@@ -107,6 +117,9 @@ def _compile(name: str, out: Path) -> None:
         tmp.unlink(missing_ok=True)
         raise BuildError(f"nvcc failed on {src.name}:\n{log}")
     os.replace(tmp, out)
+    for old in out.parent.glob(f"{name}-*"):          # libraries of earlier versions of this source
+        if old.stem != out.stem:
+            old.unlink(missing_ok=True)
     print(f"[jax-vllm_b200] built {out.name} in {time.time() - t0:.1f} s", file=sys.stderr, flush=True)
 
 

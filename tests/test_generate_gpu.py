@@ -1,0 +1,130 @@
+"""Generation through the entry point on the GPU: greedy tokens equal the plain
+implementation's, alone and batched, through prompt portions, preemption and prefix reuse;
+temperature sampling is reproducible and does not depend on the batch; long decoding; the
+first tokens of a sequence."""
+
+import pytest
+import torch
+
+from tests.plain.qwen3_plain import PlainModel
+from tests.util import PAGE_SIZE, TINY, make_folder, random_tokens
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module", params=["a", "b"])
+def setup(request, tmp_path_factory):
+    tag = request.param
+    folder = make_folder(tmp_path_factory.mktemp(f"gen_{tag}"), tag, seed=5)
+    return tag, folder, PlainModel(folder)
+
+
+def load(folder, dtype):
+    from jax_vllm_b200 import load_from_path
+    return load_from_path(folder, dtype=dtype)
+
+
+def test_greedy_equals_plain_alone_batched_and_chunked(setup):
+    from jax_vllm_b200 import SamplingParams, generate, make_driver
+    tag, folder, plain = setup
+    vocab = TINY[tag]["vocab_size"]
+    prompts = [random_tokens(n, vocab, seed=20 + n) for n in (5, 17, 33, 1, 40)]
+    want = [plain.greedy(p, 8) for p in prompts]
+    model = load(folder, "fp32")
+    sp = SamplingParams(max_new_tokens=8)
+    solo = make_driver(model, max_num_seqs=1, max_model_len=64, block_size=PAGE_SIZE[tag])
+    assert [generate(solo, [p], sp)[0] for p in prompts] == want
+    batched = make_driver(model, max_num_seqs=4, max_model_len=64, block_size=PAGE_SIZE[tag])
+    assert generate(batched, prompts, sp) == want
+    chunked = make_driver(model, max_num_seqs=3, max_model_len=64, block_size=PAGE_SIZE[tag], max_tokens_per_step=7)
+    assert generate(chunked, prompts, sp) == want
+    assert chunked.stats.steps > batched.stats.steps
+    for d in (solo, batched, chunked):
+        d.cache.check()
+        assert not d.cache.live
+
+
+def test_bf16_greedy_follows_plain_where_the_choice_is_clear(setup):
+    """In bfloat16 the engine must pick the plain implementation's token wherever the plain top-1
+    leads the runner-up by more than the bfloat16 error bound (3 % of the largest logit)."""
+    from jax_vllm_b200 import SamplingParams, generate, make_driver
+    tag, folder, plain = setup
+    vocab = TINY[tag]["vocab_size"]
+    model = load(folder, "bf16")
+    d = make_driver(model, max_num_seqs=2, max_model_len=64, block_size=PAGE_SIZE[tag])
+    checked = 0
+    for seed in range(6):
+        p = random_tokens(12, vocab, seed=40 + seed)
+        got = generate(d, [p], SamplingParams(max_new_tokens=6))[0]
+        seq = list(p)
+        for tok in got:
+            logits = plain.logits(seq)[-1]
+            top = logits.topk(2).values
+            if (top[0] - top[1]).item() > 0.06 * logits.abs().max().item():
+                assert tok == int(logits.argmax())
+                checked += 1
+            seq.append(tok)
+    assert checked >= 10
+
+
+def test_preemption_and_prefix_reuse_leave_tokens_unchanged(setup):
+    from jax_vllm_b200 import SamplingParams, generate, make_driver
+    tag, folder, plain = setup
+    vocab, P = TINY[tag]["vocab_size"], PAGE_SIZE[tag]
+    shared = random_tokens(2 * P, vocab, seed=70)
+    prompts = [shared + random_tokens(5, vocab, seed=71), shared + random_tokens(9, vocab, seed=72),
+               random_tokens(2 * P + 3, vocab, seed=73)]
+    want = [plain.greedy(p, 2 * P) for p in prompts]
+    model = load(folder, "fp32")
+    sp = SamplingParams(max_new_tokens=2 * P)
+    # each request ends with more than 4P tokens (5 or 6 pages); 10 pages cannot hold all three to the end
+    tight = make_driver(model, max_num_seqs=3, max_model_len=6 * P, block_size=P, num_blocks=10)
+    assert generate(tight, prompts, sp) == want
+    assert tight.stats.preemptions >= 1
+    tight.cache.check()
+    roomy = make_driver(model, max_num_seqs=3, max_model_len=6 * P, block_size=P)
+    assert generate(roomy, prompts[:1], sp) == want[:1]
+    assert generate(roomy, prompts, sp) == want
+    assert roomy.stats.cache_hit_tokens >= 2 * P + 2 * P      # the same prompt again, and the shared prefix
+    no_reuse = make_driver(model, max_num_seqs=3, max_model_len=6 * P, block_size=P, prefix_cache=False)
+    assert generate(no_reuse, prompts, sp) == want and no_reuse.stats.cache_hit_tokens == 0
+
+
+def test_temperature_sampling_is_reproducible_and_batch_independent(setup):
+    from jax_vllm_b200 import SamplingParams, generate, make_driver
+    tag, folder, _ = setup
+    vocab = TINY[tag]["vocab_size"]
+    model = load(folder, "fp32")
+    prompts = [random_tokens(n, vocab, seed=80 + n) for n in (1, 9, 40, 23, 7)]
+    sps = [SamplingParams(max_new_tokens=12, temperature=0.8, seed=4 + i) for i in range(5)]
+    a = make_driver(model, max_num_seqs=1, max_model_len=64, block_size=PAGE_SIZE[tag])
+    solo = [generate(a, [p], sp)[0] for p, sp in zip(prompts, sps)]
+    b = make_driver(model, max_num_seqs=4, max_model_len=64, block_size=PAGE_SIZE[tag], max_tokens_per_step=7)
+    assert generate(b, prompts, sps) == solo
+    greedy = generate(b, prompts, SamplingParams(max_new_tokens=12))
+    assert greedy != solo
+    other = generate(b, prompts, [SamplingParams(max_new_tokens=12, temperature=0.8, seed=99 + i) for i in range(5)])
+    assert other != solo
+
+
+def test_long_decoding_and_first_tokens(setup):
+    """Two hundred tokens decoded one by one (crossing many pages and several splits) equal the
+    plain implementation's logits; so do the logits of the very first positions."""
+    from jax_vllm_b200.cache import CacheManager
+    from jax_vllm_b200.engine import Runner, StepEntry
+    tag, folder, plain = setup
+    vocab, P = TINY[tag]["vocab_size"], PAGE_SIZE[tag]
+    toks = random_tokens(230, vocab, seed=90)
+    want = plain.logits(toks)
+    from jax_vllm_b200 import load_from_path
+    model = load_from_path(folder, dtype="fp32", decode_split_size=48)
+    cache = CacheManager(model.cache_needs(), P, -(-230 // P), 2, prefix_cache=False)
+    runner = Runner(model, cache, "cuda:0", torch.float32)
+    rc = cache.admit("x")
+    first = runner.run([StepEntry(rc, toks[:3], (0, 1, 2))]).cpu()
+    lim = 1e-4 * max(1.0, want.abs().max().item())
+    assert (first - want[:3]).abs().max().item() <= lim
+    for i in range(3, 230):
+        row = runner.run([StepEntry(rc, [toks[i]], (0,))]).cpu()[0]
+        assert (row - want[i]).abs().max().item() <= lim, f"position {i}"
+    runner.check_kernels()

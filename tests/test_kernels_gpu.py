@@ -1,0 +1,325 @@
+"""Each CUDA kernel alone against a plain float32 reference, at sizes other than the
+engine's (odd widths, vocabularies that are no power of two, many head groupings)."""
+
+import math
+
+import pytest
+import torch
+
+from tests.plain import qwen3_plain as plain
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype):
+    return dict(atol=2e-5, rtol=2e-5) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from jax_vllm_b200 import ops as o
+    return o
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embed_gather(ops, dtype):
+    g = torch.Generator().manual_seed(0)
+    table = torch.randn(1000, 200, generator=g).to(dtype).to(DEV)
+    ids = torch.randint(0, 1000, (37,), generator=g, dtype=torch.int32).to(DEV)
+    out = ops.embed_gather(table, ids)
+    assert out.dtype == torch.float32 and torch.equal(out, table.float()[ids.long()])
+    ops.check_status()
+    bad = torch.tensor([3, 1000, -1], dtype=torch.int32, device=DEV)
+    out = ops.embed_gather(table, bad)
+    with pytest.raises(ops.KernelError, match="token id"):
+        ops.check_status()
+    assert torch.equal(out[1], torch.zeros(200, device=DEV))
+    ops.check_status()                       # the word was cleared
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden", [200, 4096])
+@pytest.mark.parametrize("wdtype", DTYPES)
+def test_rmsnorm_variants(ops, dtype, hidden, wdtype):
+    g = torch.Generator().manual_seed(1)
+    h = (3 * torch.randn(19, hidden, generator=g)).to(DEV)
+    w = (1 + 0.1 * torch.randn(hidden, generator=g)).to(wdtype).to(DEV)
+    delta = torch.randn(19, hidden, generator=g).to(dtype).to(DEV)
+    eps = 1e-5
+    y = ops.rmsnorm(h.clone(), w, eps, dtype)
+    torch.testing.assert_close(y.float(), plain.rms_norm(h, w.float(), eps), **tol(dtype))
+    h2 = h.clone()
+    y = ops.rmsnorm(h2, w, eps, dtype, delta=delta)
+    want_h = h + delta.float()
+    torch.testing.assert_close(h2, want_h, atol=1e-6, rtol=1e-6)       # the sum is kept in float32
+    torch.testing.assert_close(y.float(), plain.rms_norm(want_h, w.float(), eps), **tol(dtype))
+    rows = torch.tensor([18, 0, 7, 7], dtype=torch.int32, device=DEV)
+    h3 = h.clone()
+    y = ops.rmsnorm(h3, w, eps, dtype, delta=delta, rows=rows)
+    assert torch.equal(h3, h)                                          # gathered rows: h is left alone
+    torch.testing.assert_close(y.float(), plain.rms_norm(want_h, w.float(), eps)[rows.long()], **tol(dtype))
+    y = ops.rmsnorm(h3, w, eps, dtype, rows=rows)
+    torch.testing.assert_close(y.float(), plain.rms_norm(h, w.float(), eps)[rows.long()], **tol(dtype))
+    ops.check_status()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_residual_add_and_swiglu(ops, dtype):
+    g = torch.Generator().manual_seed(2)
+    h = torch.randn(23, 72, generator=g).to(DEV)
+    d = torch.randn(23, 72, generator=g).to(dtype).to(DEV)
+    want = h + d.float()
+    ops.residual_add(h, d)
+    torch.testing.assert_close(h, want, atol=1e-6, rtol=1e-6)
+    gu = (2 * torch.randn(23, 2 * 56, generator=g)).to(dtype).to(DEV)
+    act = ops.swiglu(gu)
+    gate, up = gu.float()[:, :56], gu.float()[:, 56:]
+    torch.testing.assert_close(act.float(), torch.nn.functional.silu(gate) * up, **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("m,n,k", [(37, 70, 45), (1, 384, 96), (130, 129, 64), (5, 8, 300)])
+def test_gemm_simt(ops, dtype, m, n, k):
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(m, k, generator=g).to(dtype).to(DEV)
+    w = torch.randn(n, k, generator=g).to(dtype).to(DEV)
+    y = ops.gemm_simt(x, w, torch.float32)
+    want = x.double() @ w.double().T
+    torch.testing.assert_close(y.double(), want, atol=1e-4, rtol=1e-5)
+    # a row's result does not depend on the other rows of the batch
+    y1 = ops.gemm_simt(x[m // 2:m // 2 + 1], w, torch.float32)
+    assert torch.equal(y1[0], y[m // 2])
+    # strided input rows (a column slice of a wider tensor)
+    wide = torch.randn(m, k + 24, generator=g).to(dtype).to(DEV)
+    ys = ops.gemm_simt(wide[:, 8:8 + k], w, torch.float32)
+    torch.testing.assert_close(ys.double(), wide[:, 8:8 + k].double() @ w.double().T, atol=1e-4, rtol=1e-5)
+
+
+def test_linear_uses_true_float32(ops):
+    # operands whose product needs more than 10 mantissa bits: a reduced-precision matrix mode would show
+    x = torch.full((4, 256), 1.0 + 2 ** -12, device=DEV)
+    w = torch.full((8, 256), 1.0 + 2 ** -12, device=DEV)
+    y = ops.linear(x, w)
+    want = 256 * (1.0 + 2 ** -12) ** 2
+    assert abs(y[0, 0].item() - want) < 1e-3 and abs(y[0, 0].item() - 256.0) > 0.1
+
+
+# ------------------------------------------------------------------ rope + kv write
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hq,hkv,d,page", [(4, 2, 16, 16), (6, 1, 32, 8), (3, 3, 48, 4), (8, 2, 128, 16)])
+def test_rope_kv(ops, dtype, hq, hkv, d, page):
+    g = torch.Generator().manual_seed(4)
+    q_lens, starts = [5, 1, 9], [3, 40, 0]
+    n = sum(q_lens)
+    qkv = torch.randn(n, (hq + 2 * hkv) * d, generator=g).to(dtype)
+    positions = torch.cat([torch.arange(s, s + q) for s, q in zip(starts, q_lens)]).to(torch.int32)
+    entry = torch.cat([torch.full((q,), e) for e, q in enumerate(q_lens)]).to(torch.int32)
+    width = -(-48 // page)
+    num_pages = 3 * width + 4
+    perm = torch.randperm(num_pages, generator=g)
+    table = perm[: 3 * width].reshape(3, width).to(torch.int32)
+    theta, eps = 1e4, 1e-5
+    inv_freq = 1.0 / (theta ** (torch.arange(0, d, 2, dtype=torch.float32) / d))
+    qw = (1 + 0.1 * torch.randn(d, generator=g)).to(dtype)
+    kw = (1 + 0.1 * torch.randn(d, generator=g)).to(dtype)
+    kc = torch.full((num_pages, page, hkv, d), 7.0).to(dtype).to(DEV)
+    vc = torch.full((num_pages, page, hkv, d), 7.0).to(dtype).to(DEV)
+    dq = qkv.clone().to(DEV)
+    ops.rope_kv(dq, positions.to(DEV), entry.to(DEV), table.to(DEV), inv_freq.to(DEV), qw.to(DEV), kw.to(DEV),
+                eps, kc, vc, hq, hkv, d)
+    ops.check_status()
+    f = qkv.float()
+    q = f[:, : hq * d].reshape(n, hq, d).transpose(0, 1)
+    k = f[:, hq * d:(hq + hkv) * d].reshape(n, hkv, d).transpose(0, 1)
+    v = f[:, (hq + hkv) * d:].reshape(n, hkv, d)
+    cos, sin = plain.rope_cos_sin(positions, d, theta)
+    q_want = plain.apply_rope(plain.rms_norm(q, qw.float(), eps), cos, sin).transpose(0, 1).reshape(n, hq * d)
+    k_want = plain.apply_rope(plain.rms_norm(k, kw.float(), eps), cos, sin).transpose(0, 1)
+    torch.testing.assert_close(dq[:, : hq * d].float().cpu(), q_want, **tol(dtype))
+    written = torch.zeros(num_pages, page, dtype=torch.bool)
+    for i in range(n):
+        p, e = positions[i].item(), entry[i].item()
+        pg, sl = table[e, p // page].item(), p % page
+        written[pg, sl] = True
+        torch.testing.assert_close(kc[pg, sl].float().cpu(), k_want[i], **tol(dtype))
+        assert torch.equal(vc[pg, sl].cpu(), qkv[i, (hq + hkv) * d:].reshape(hkv, d))
+    assert torch.all(kc.cpu()[~written] == 7.0) and torch.all(vc.cpu()[~written] == 7.0)   # nothing else touched
+
+
+def test_rope_kv_without_norm_rotation_or_cache(ops):
+    g = torch.Generator().manual_seed(5)
+    hq, d, n = 2, 32, 4
+    qkv = torch.randn(n, hq * d, generator=g)
+    pos = torch.tensor([0, 5, 100, 3000], dtype=torch.int32)
+    ent = torch.zeros(n, dtype=torch.int32)
+    table = torch.zeros((1, 1), dtype=torch.int32)
+    dq = qkv.clone().to(DEV)
+    ops.rope_kv(dq, pos.to(DEV), ent.to(DEV), table.to(DEV), None, None, None, 0.0, None, None, hq, 1, d)
+    assert torch.equal(dq.cpu(), qkv)
+    # partial rotation: only the first 16 of 32 elements rotate; large positions keep 32-bit angles
+    inv_freq = 1.0 / (1e6 ** (torch.arange(0, 16, 2, dtype=torch.float32) / 16))
+    ops.rope_kv(dq, pos.to(DEV), ent.to(DEV), table.to(DEV), inv_freq.to(DEV), None, None, 0.0, None, None, hq, 1, d)
+    x = qkv.reshape(n, hq, d)
+    cos, sin = plain.rope_cos_sin(pos, 16, 1e6)
+    rot = plain.apply_rope(x[..., :16].transpose(0, 1), cos, sin).transpose(0, 1)
+    want = torch.cat([rot, x[..., 16:]], dim=-1).reshape(n, hq * d)
+    torch.testing.assert_close(dq.cpu(), want, atol=2e-5, rtol=2e-5)
+
+
+def test_rope_kv_flags_a_missing_page(ops):
+    hq = hkv = 1; d = 16
+    qkv = torch.zeros(1, 3 * d, device=DEV)
+    kc = torch.zeros(2, 4, 1, d, device=DEV); vc = torch.zeros_like(kc)
+    args = (torch.tensor([5], dtype=torch.int32, device=DEV), torch.zeros(1, dtype=torch.int32, device=DEV))
+    ops.rope_kv(qkv, *args, torch.tensor([[0, -1]], dtype=torch.int32, device=DEV), None, None, None, 0.0, kc, vc,
+                hq, hkv, d)
+    with pytest.raises(ops.KernelError, match="page"):
+        ops.check_status()
+
+
+# ------------------------------------------------------------------------ attention
+def dense_attention(q, k_all, v_all, q_pos, scale, window, g):
+    """q: [n, hq, d]; k_all, v_all: [len, hkv, d]; one request; float32 throughout."""
+    k = k_all.repeat_interleave(g, dim=1)
+    v = v_all.repeat_interleave(g, dim=1)
+    s = torch.einsum("nhd,lhd->hnl", q, k) * scale
+    j = torch.arange(k_all.shape[0])[None, :]
+    vis = j <= q_pos[:, None]
+    if window:
+        vis = vis & (j > q_pos[:, None] - window)
+    s = torch.where(vis[None], s, torch.tensor(float("-inf")))
+    return torch.einsum("hnl,lhd->nhd", torch.softmax(s, -1), v)
+
+
+def run_attention(ops, dtype, hq, hkv, d, page, q_lens, starts, window=0, split=0, seed=6, boost=None):
+    g = torch.Generator().manual_seed(seed)
+    G = hq // hkv
+    R, n = len(q_lens), sum(q_lens)
+    total = [s + q for s, q in zip(starts, q_lens)]
+    pages_per = [-(-t // page) for t in total]
+    num_pages = sum(pages_per) + 5
+    perm = torch.randperm(num_pages, generator=g).tolist()
+    width = max(pages_per)
+    table = torch.full((R, width), -1, dtype=torch.int32)
+    kc = torch.full((num_pages, page, hkv, d), float("nan"))          # unowned slots hold NaN: reading one shows
+    vc = torch.full((num_pages, page, hkv, d), float("nan"))
+    ks, vs = [], []
+    for e in range(R):
+        k = torch.randn(total[e], hkv, d, generator=g).to(dtype).float()
+        v = torch.randn(total[e], hkv, d, generator=g).to(dtype).float()
+        if boost is not None and e == boost[0]:
+            k[boost[1]] *= 6.0                                        # one far key that the last query must find
+        ks.append(k); vs.append(v)
+        for i in range(pages_per[e]):
+            pg = perm.pop()
+            table[e, i] = pg
+            m = min(page, total[e] - i * page)
+            kc[pg, :m] = k[i * page:i * page + m]
+            vc[pg, :m] = v[i * page:i * page + m]
+    q = torch.randn(n, hq, d, generator=g).to(dtype).float()
+    if boost is not None:
+        last = sum(q_lens[: boost[0] + 1]) - 1
+        q[last] = ks[boost[0]][boost[1]].repeat_interleave(G, dim=0) * 1.0
+    scale = 1.0 / math.sqrt(d)
+    cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32)
+    want = torch.cat([dense_attention(q[cu[e]:cu[e + 1]], ks[e], vs[e], torch.arange(starts[e], total[e]), scale,
+                                      window, G) for e in range(R)])
+    dq = q.reshape(n, hq * d).to(dtype).to(DEV)
+    out = torch.zeros(n, hq * d, dtype=dtype, device=DEV)
+    common = (kc.to(dtype).to(DEV), vc.to(dtype).to(DEV), table.to(DEV), cu.to(DEV),
+              torch.tensor(starts, dtype=torch.int32, device=DEV))
+    tpt = ops.attn_simt_tokens_per_tile(hq, hkv)
+    if split:
+        assert all(ql == 1 for ql in q_lens)
+        work = torch.tensor([[e, 0] for e in range(R)], dtype=torch.int32, device=DEV)
+        ops.attn_simt(dq, hq * d, out, *common, work, R, hq, hkv, d, window, scale, split_size=split,
+                      n_splits=-(-max(total) // split))
+    else:
+        work = torch.tensor([[e, t] for e in range(R) for t in range(0, q_lens[e], tpt)], dtype=torch.int32, device=DEV)
+        ops.attn_simt(dq, hq * d, out, *common, work, work.shape[0], hq, hkv, d, window, scale)
+    ops.check_status()
+    got = out.float().cpu().reshape(n, hq, d)
+    assert not torch.isnan(got).any()
+    return got, want
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hq,hkv,d,page", [(4, 2, 16, 16), (6, 1, 32, 8), (5, 5, 48, 4), (8, 2, 128, 16),
+                                           (20, 1, 64, 16), (2, 1, 256, 32)])
+def test_attention_portions_with_context(ops, dtype, hq, hkv, d, page):
+    got, want = run_attention(ops, dtype, hq, hkv, d, page, q_lens=[7, 1, 33, 2], starts=[0, 50, 21, 64])
+    torch.testing.assert_close(got, want, **(dict(atol=3e-5, rtol=3e-5) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hq,hkv,d,page,split", [(4, 2, 16, 16, 32), (6, 1, 32, 8, 24), (8, 2, 128, 16, 256), (20, 2, 64, 4, 64)])
+def test_attention_decode_splits(ops, dtype, hq, hkv, d, page, split):
+    got, want = run_attention(ops, dtype, hq, hkv, d, page, q_lens=[1, 1, 1, 1], starts=[0, 31, 300, 63], split=split)
+    torch.testing.assert_close(got, want, **(dict(atol=3e-5, rtol=3e-5) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)))
+
+
+@pytest.mark.parametrize("window", [1, 5, 16, 40])
+@pytest.mark.parametrize("split", [0, 16])
+def test_attention_window_edges(ops, window, split):
+    q_lens, starts = ([1, 1, 1], [0, 39, 77]) if split else ([9, 30, 1], [0, 35, 77])
+    got, want = run_attention(ops, torch.float32, 4, 2, 32, 8, q_lens=q_lens, starts=starts, window=window, split=split)
+    torch.testing.assert_close(got, want, atol=3e-5, rtol=3e-5)
+
+
+@pytest.mark.parametrize("split", [0, 64])
+@pytest.mark.parametrize("far", [0, 3, 130, 511])
+def test_attention_finds_one_far_key_among_hundreds(ops, split, far):
+    # the last query equals one key scaled up, so that key takes nearly all the weight
+    q_lens = [1, 1] if split else [3, 2]
+    starts = [10, 600 - q_lens[1]]
+    got, want = run_attention(ops, torch.float32, 4, 2, 64, 16, q_lens=q_lens, starts=starts, split=split,
+                              boost=(1, far))
+    torch.testing.assert_close(got, want, atol=3e-5, rtol=3e-5)
+
+
+def test_attention_refuses_what_it_cannot_do(ops):
+    z = torch.zeros(1, 512, device=DEV)
+    i = torch.zeros(2, dtype=torch.int32, device=DEV)
+    c = torch.zeros(1, 4, 1, 512, device=DEV)
+    with pytest.raises(ops.KernelError, match="outside what the kernel handles"):
+        ops.attn_simt(z, 512, z.clone(), c, c, i.view(1, 2), i, i[:1], i.view(1, 2), 1, 1, 1, 512, 0, 1.0)
+
+
+# ------------------------------------------------------------------------- sampling
+def test_greedy_is_argmax_with_lowest_index_on_ties(ops):
+    g = torch.Generator().manual_seed(7)
+    logits = torch.randn(9, 1531, generator=g).to(DEV)
+    logits[3, 700] = logits[3, 20] = 50.0
+    z = torch.zeros(9, device=DEV); zi = torch.zeros(9, dtype=torch.int64, device=DEV)
+    got = ops.sample(logits, z, zi, zi)
+    want = logits.argmax(-1)
+    want[3] = 20
+    assert torch.equal(got.long(), want)
+
+
+def test_temperature_draws_follow_the_host_restatement_and_the_distribution(ops):
+    from jax_vllm_b200.sampling import uniform
+    V = 11
+    logits = torch.tensor([[0.3 * i for i in range(V)]])
+    temp = 0.8
+    n = 4000
+    big = logits.repeat(n, 1).to(DEV)
+    t = torch.full((n,), temp, device=DEV)
+    seeds = torch.full((n,), 1234, dtype=torch.int64, device=DEV)
+    counters = torch.arange(n, dtype=torch.int64, device=DEV)
+    got = ops.sample(big, t, seeds, counters).cpu()
+    # exact agreement with the host formula on the first draws
+    for c in range(50):
+        scores = [logits[0, v].item() / temp - math.log(-math.log(uniform(1234, c, v))) for v in range(V)]
+        assert got[c].item() == max(range(V), key=lambda v: scores[v])
+    # frequencies follow softmax(logits / T)
+    p = torch.softmax(logits[0] / temp, -1)
+    freq = torch.bincount(got.long(), minlength=V).float() / n
+    assert (freq - p).abs().max().item() < 0.03
+    # same (seed, counter) -> same token wherever the row stands; another seed -> another stream
+    again = ops.sample(big.flip(0), t, seeds, counters.flip(0)).cpu().flip(0)
+    assert torch.equal(again, got)
+    other = ops.sample(big, t, seeds + 1, counters).cpu()
+    assert (other != got).float().mean().item() > 0.3

@@ -1,0 +1,281 @@
+"""Each part of a model alone against the plain formulas, and the generality of the
+assembly: a layer run twice, a layer that reads another layer's cache, a windowed layer
+beside a full one, and a toy mixer with state of its own that is defined here, registered,
+built and stepped without any change to the package."""
+
+from dataclasses import dataclass, replace
+
+import pytest
+import torch
+
+from tests.plain import qwen3_plain as plain
+from tests.util import TINY_B, random_tokens
+
+pytestmark = pytest.mark.gpu
+DEV = torch.device("cuda:0")
+
+
+def pkg():
+    import jax_vllm_b200 as j
+    from jax_vllm_b200 import cache, config, engine, parts, weights
+    return j, cache, config, engine, parts, weights
+
+
+def make_runner(spec, seed=0, dtype=torch.float32, page=8, pages=64, std=None):
+    """A runner for `spec` with random float32 weights; returns (runner, weights on the CPU)."""
+    j, cache, config, engine, parts, weights = pkg()
+    ctx = parts.BuildContext(dtype=dtype, device=DEV, decode_split_size=32)
+    model = parts.Model(spec, ctx)
+    g = torch.Generator().manual_seed(seed)
+    w = {}
+    for name, ts in model.tensor_specs().items():
+        z = torch.randn(ts.shape, generator=g)
+        w[name] = (1 + 0.1 * z) if ts.kind == "vector" else z * (std or 1.5 / ts.shape[-1] ** 0.5)
+    model.bind({k: v.to(DEV) for k, v in w.items()})
+    cm = cache.CacheManager(model.cache_needs(), page, pages, 4, prefix_cache=False)
+    return engine.Runner(model, cm, DEV, dtype), w
+
+
+def run_cut(runner, toks, cuts):
+    """Feeds `toks` in portions of the sizes in `cuts` (cycled); returns logits of all positions."""
+    j, cache, config, engine, parts, weights = pkg()
+    rc = runner.cache.admit(object())
+    rows, i, k = [], 0, 0
+    while i < len(toks):
+        n = min(cuts[k % len(cuts)], len(toks) - i)
+        rows.append(runner.run([engine.StepEntry(rc, toks[i:i + n], tuple(range(n)))]).cpu())
+        i += n; k += 1
+    runner.check_kernels()
+    runner.cache.release(rc.request_id)
+    return torch.cat(rows)
+
+
+def qwen_cfg(c):
+    return dict(num_heads=c["num_attention_heads"], num_kv_heads=c["num_key_value_heads"], head_dim=c["head_dim"],
+                rms_norm_eps=c["rms_norm_eps"], rope_theta=c["rope_theta"], num_hidden_layers=c["num_hidden_layers"],
+                tie_word_embeddings=c["tie_word_embeddings"])
+
+
+def spec_b():
+    j = pkg()[0]
+    return j.registry.config_from_dict(TINY_B).to_spec()
+
+
+# ----------------------------------------------------------------- parts, one by one
+def test_norm_and_position_parts():
+    j, cache, config, engine, parts, weights = pkg()
+    ctx = parts.BuildContext(torch.float32, DEV)
+    norm = parts.NORMS["rmsnorm"](config.NormSpec(72, 1e-5, "n.weight"), "pre", ctx)
+    assert list(norm.tensor_specs()) == ["pre.n.weight"]
+    w = 1 + 0.1 * torch.randn(72)
+    norm.bind({"pre.n.weight": w.to(DEV)})
+    h, d = torch.randn(5, 72), torch.randn(5, 72)
+    hd = h.clone().to(DEV)
+    y = norm.norm(hd, d.to(DEV))
+    torch.testing.assert_close(y.cpu(), plain.rms_norm(h + d, w, 1e-5), atol=1e-5, rtol=1e-5)
+    torch.testing.assert_close(hd.cpu(), h + d)
+    rope = parts.POSITIONS["rope"](config.RopeSpec(dim=48, theta=1e6), "", ctx)
+    want = 1.0 / (1e6 ** (torch.arange(0, 48, 2, dtype=torch.float32) / 48))
+    assert torch.equal(rope.table().cpu(), want)
+    with pytest.raises(ValueError):
+        parts.POSITIONS["rope"](config.RopeSpec(dim=7, theta=1e4), "", ctx)
+
+
+@pytest.mark.parametrize("window", [None, 11])
+def test_attention_mixer_alone(window):
+    """The mixer stepped in portions equals the plain attention block over the whole sequence."""
+    j, cache, config, engine, parts, weights = pkg()
+    spec = config.AttentionSpec(hidden_size=40, num_heads=6, num_kv_heads=2, head_dim=16, scale=0.25,
+                                position=config.RopeSpec(16, 1e4), qk_norm_eps=1e-5, window=window)
+    ctx = parts.BuildContext(torch.float32, DEV, decode_split_size=16)
+    mixer = parts.MIXERS["attention"](spec, "L", ctx)
+    g = torch.Generator().manual_seed(1)
+    w = {n: (1 + 0.1 * torch.randn(ts.shape, generator=g)) if ts.kind == "vector" else torch.randn(ts.shape, generator=g) * 0.3
+         for n, ts in mixer.tensor_specs().items()}
+    mixer.bind({k: v.to(DEV) for k, v in w.items()})
+    cm = cache.CacheManager([mixer.cache_need()], 8, 16, 2, prefix_cache=False)
+    views = cm.allocate_storage(torch.float32, DEV)
+    builder = engine.BatchBuilder(1, 8, [mixer.tile_tokens()], DEV)
+    x = torch.randn(37, 40, generator=g)
+    rc = cm.admit("r")
+    outs, i = [], 0
+    for n in (5, 1, 2, 17, 1, 11):
+        cm.grow(rc, i + n)
+        step = builder.build([engine.StepEntry(rc, [0] * n, ())])
+        outs.append(mixer.forward(x[i:i + n].to(DEV), step, views[0]).cpu())
+        cm.commit(rc, [0] * n)
+        i += n
+    pcfg = dict(num_heads=6, num_kv_heads=2, head_dim=16, rms_norm_eps=1e-5, rope_theta=1e4)
+    pw = {k.replace("L.self_attn", "p"): v for k, v in w.items()}
+    T = x.shape[0]
+    q = plain.linear(x, pw["p.q_proj.weight"]).reshape(T, 6, 16).transpose(0, 1)
+    k = plain.linear(x, pw["p.k_proj.weight"]).reshape(T, 2, 16).transpose(0, 1)
+    v = plain.linear(x, pw["p.v_proj.weight"]).reshape(T, 2, 16).transpose(0, 1)
+    cos, sin = plain.rope_cos_sin(torch.arange(T), 16, 1e4)
+    q = plain.apply_rope(plain.rms_norm(q, pw["p.q_norm.weight"], 1e-5), cos, sin)
+    k = plain.apply_rope(plain.rms_norm(k, pw["p.k_norm.weight"], 1e-5), cos, sin)
+    # head size 16 gives the plain scale 0.25 as well
+    o = plain.causal_attention(q, k, v, 6, 2, 16, window=window).transpose(0, 1).reshape(T, 96)
+    want = plain.linear(o, pw["p.o_proj.weight"])
+    torch.testing.assert_close(torch.cat(outs), want, atol=2e-4, rtol=2e-4)
+    if window:
+        assert sum(p >= 0 for p in rc.tables[0]) <= 3          # pages behind the window went back
+
+
+def test_feed_forward_and_block_alone():
+    j, cache, config, engine, parts, weights = pkg()
+    ctx = parts.BuildContext(torch.float32, DEV)
+    ff = parts.FEED_FORWARDS["gated_mlp"](config.GatedMLPSpec(40, 56), "L", ctx)
+    g = torch.Generator().manual_seed(2)
+    w = {n: torch.randn(ts.shape, generator=g) * 0.3 for n, ts in ff.tensor_specs().items()}
+    ff.bind({k: v.to(DEV) for k, v in w.items()})
+    x = torch.randn(9, 40, generator=g)
+    torch.testing.assert_close(ff.forward(x.to(DEV), None).cpu(), plain.swiglu(x, w, "L.mlp"), atol=1e-4, rtol=1e-4)
+    with pytest.raises(ValueError, match="activation"):
+        parts.FEED_FORWARDS["gated_mlp"](config.GatedMLPSpec(40, 56, activation="gelu"), "L", ctx)
+
+
+def test_kinds_are_looked_up_in_the_registries():
+    j, cache, config, engine, parts, weights = pkg()
+    spec = spec_b()
+    bad = replace(spec, layers=(replace(spec.layers[0], mixer=replace(spec.layers[0].mixer, kind="nonesuch")),))
+    with pytest.raises(ValueError, match="unknown mixer kind 'nonesuch'"):
+        parts.Model(bad, parts.BuildContext(torch.float32, DEV))
+
+
+# --------------------------------------------------- arrangements of layers as data
+def plain_layers(w, cfg, toks, order, windows=None, cache_from=None):
+    """Plain forward with a run order, per-layer windows and layers that read another layer's keys/values."""
+    ids = torch.as_tensor(toks)
+    T = len(toks)
+    pos = torch.arange(T)
+    h = plain.embedding(w["model.embed_tokens.weight"], ids)
+    Hq, Hkv, D, eps = cfg["num_heads"], cfg["num_kv_heads"], cfg["head_dim"], cfg["rms_norm_eps"]
+    cos, sin = plain.rope_cos_sin(pos, D, cfg["rope_theta"])
+    kv = {}
+    for i in order:
+        p = f"model.layers.{i}"
+        x = plain.rms_norm(h, w[f"{p}.input_layernorm.weight"], eps)
+        q = plain.linear(x, w[f"{p}.self_attn.q_proj.weight"]).reshape(T, Hq, D).transpose(0, 1)
+        q = plain.apply_rope(plain.rms_norm(q, w[f"{p}.self_attn.q_norm.weight"], eps), cos, sin)
+        src = (cache_from or {}).get(i)
+        if src is None:
+            k = plain.linear(x, w[f"{p}.self_attn.k_proj.weight"]).reshape(T, Hkv, D).transpose(0, 1)
+            v = plain.linear(x, w[f"{p}.self_attn.v_proj.weight"]).reshape(T, Hkv, D).transpose(0, 1)
+            k = plain.apply_rope(plain.rms_norm(k, w[f"{p}.self_attn.k_norm.weight"], eps), cos, sin)
+            kv[i] = (k, v)
+        else:
+            k, v = kv[src]
+        o = plain.causal_attention(q, k, v, Hq, Hkv, D, window=(windows or {}).get(i))
+        h = h + plain.linear(o.transpose(0, 1).reshape(T, Hq * D), w[f"{p}.self_attn.o_proj.weight"])
+        h = h + plain.swiglu(plain.rms_norm(h, w[f"{p}.post_attention_layernorm.weight"], eps), w, f"{p}.mlp")
+    h = plain.rms_norm(h, w["model.norm.weight"], eps)
+    return plain.linear(h, w["lm_head.weight"])
+
+
+def test_a_layer_run_twice_a_shared_cache_and_a_window_beside_full_layers():
+    spec = spec_b()
+    layers = list(spec.layers)
+    layers[1] = replace(layers[1], mixer=replace(layers[1].mixer, window=13))   # its own cache group
+    layers[2] = replace(layers[2], cache_from=0)                                 # reads layer 0's keys and values
+    spec = replace(spec, layers=tuple(layers), schedule=(0, 1, 2, 1))
+    runner, w = make_runner(spec, seed=3)
+    assert [g.layers for g in runner.cache.groups] == [[0], [1]]
+    assert "model.layers.2.self_attn.k_proj.weight" not in w
+    toks = random_tokens(61, TINY_B["vocab_size"], seed=4)
+    want = plain_layers(w, qwen_cfg(TINY_B), toks, (0, 1, 2, 1), windows={1: 13}, cache_from={2: 0})
+    lim = 1e-4 * max(1.0, want.abs().max().item())
+    for cuts in [(61,), (7, 2, 13, 1, 1, 5), (29, 1)]:
+        got = run_cut(runner, toks, cuts)
+        assert (got - want).abs().max().item() <= lim, cuts
+    runner.cache.check()
+
+
+# --------------------------------------------- a toy mixer with state of its own
+@dataclass(frozen=True)
+class DecaySpec:
+    hidden_size: int
+    decay: float
+    kind: str = "toy_decay"
+
+
+def register_toy():
+    j, cache, config, engine, parts, weights = pkg()
+
+    class DecayMixer(parts.Part):
+        """y_t = s_t * w with s_t = decay * s_{t-1} + x_t: a running sum kept per request in a
+        fixed-size state row, carried from step to step (torch ops: a toy for this test)."""
+
+        def __init__(self, spec, prefix, ctx):
+            self.spec, self.name, self.ctx = spec, f"{prefix}.decay.weight", ctx
+
+        def tensor_specs(self):
+            return {self.name: parts.TensorSpec((self.spec.hidden_size,), kind="vector", init="ones_normal")}
+
+        def bind(self, tensors):
+            self.w = tensors[self.name].float()
+
+        def cache_need(self):
+            return parts.FixedStateNeed((self.spec.hidden_size,), torch.float32)
+
+        def forward(self, x, step, cache):
+            out = torch.empty_like(x)
+            i = 0
+            for q, slot in zip(step.host_q_lens, step.host_slots):
+                s = cache.state[slot]
+                for t in range(i, i + q):
+                    s = self.spec.decay * s + x[t].float()
+                    out[t] = (s * self.w).to(x.dtype)
+                cache.state[slot] = s
+                i += q
+            return out
+
+    parts.register_mixer("toy_decay", DecayMixer)
+
+
+def plain_with_toy(w, cfg, toks, toy_layers, decay):
+    ids = torch.as_tensor(toks)
+    T = len(toks)
+    h = plain.embedding(w["model.embed_tokens.weight"], ids)
+    eps = cfg["rms_norm_eps"]
+    for i in range(cfg["num_hidden_layers"]):
+        p = f"model.layers.{i}"
+        x = plain.rms_norm(h, w[f"{p}.input_layernorm.weight"], eps)
+        if i in toy_layers:
+            s, ys = torch.zeros(x.shape[1]), []
+            for t in range(T):
+                s = decay * s + x[t]
+                ys.append(s * w[f"{p}.decay.weight"])
+            h = h + torch.stack(ys)
+        else:
+            h = h + plain.attention_block(x, w, f"{p}.self_attn", cfg, torch.arange(T))
+        h = h + plain.swiglu(plain.rms_norm(h, w[f"{p}.post_attention_layernorm.weight"], eps), w, f"{p}.mlp")
+    return plain.linear(plain.rms_norm(h, w["model.norm.weight"], eps), w["lm_head.weight"])
+
+
+def test_toy_mixer_with_own_state_registers_builds_and_steps():
+    j, cache, config, engine, parts, weights = pkg()
+    register_toy()
+    spec = spec_b()
+    layers = list(spec.layers)
+    layers[1] = replace(layers[1], mixer=DecaySpec(spec.hidden_size, 0.9))
+    spec = replace(spec, layers=tuple(layers))
+    runner, w = make_runner(spec, seed=5)
+    assert runner.cache.state_layers.keys() == {1} and [g.layers for g in runner.cache.groups] == [[0, 2]]
+    assert runner.cache.prefix_cache is False
+    toks = random_tokens(45, TINY_B["vocab_size"], seed=6)
+    want = plain_with_toy(w, qwen_cfg(TINY_B), toks, {1}, 0.9)
+    lim = 1e-4 * max(1.0, want.abs().max().item())
+    for cuts in [(45,), (6, 1, 2, 9)]:
+        got = run_cut(runner, toks, cuts)          # a fresh request each time: its state row starts at zero
+        assert (got - want).abs().max().item() <= lim, cuts
+    # two requests side by side keep their states apart
+    other = random_tokens(20, TINY_B["vocab_size"], seed=7)
+    want_other = plain_with_toy(w, qwen_cfg(TINY_B), other, {1}, 0.9)
+    a, b = runner.cache.admit("a"), runner.cache.admit("b")
+    la = runner.run([engine.StepEntry(a, toks[:10], ()), engine.StepEntry(b, other[:7], (6,))])
+    lb = runner.run([engine.StepEntry(b, other[7:], tuple(range(13))), engine.StepEntry(a, toks[10:12], (1,))]).cpu()
+    assert (la.cpu()[0] - want_other[6]).abs().max().item() <= lim
+    assert (lb[:13] - want_other[7:]).abs().max().item() <= lim
+    assert (lb[13] - want[11]).abs().max().item() <= lim
+    runner.check_kernels()

@@ -1,0 +1,174 @@
+"""Trace replay against the plain implementation: the same requests whole, with the last 32
+tokens one by one, in portions of changing size down to two tokens, and mixed with other
+requests in a pool so small that pages are used again; in 32-bit and in bfloat16; for two
+tiny configurations that differ in every size."""
+
+import json
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+from tests.plain.qwen3_plain import PlainModel
+from tests.util import PAGE_SIZE, TINY, collect, make_folder, portions, prefix_then_single, random_tokens, whole
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+LENGTHS = {"a": [70, 45, 100, 33], "b": [90, 38, 64, 51]}
+
+
+def limits(dtype, want: torch.Tensor):
+    """Largest allowed |difference| of logits.  32-bit: 1e-4 relative to the size of the logits
+    (at least 1).  bfloat16: 3 % of the largest logit (8 bits of mantissa through a few layers)."""
+    scale = max(1.0, want.abs().max().item())
+    return (1e-4 if dtype == "float32" else 3e-2) * scale
+
+
+@pytest.fixture(scope="module", params=["a", "b"])
+def setup(request, tmp_path_factory):
+    tag = request.param
+    folder = make_folder(tmp_path_factory.mktemp(f"model_{tag}"), tag, seed=3)
+    plain = PlainModel(folder)           # the folder holds bfloat16 weights; both sides read the same values
+    seqs = {f"r{i}": random_tokens(n, TINY[tag]["vocab_size"], seed=10 + i) for i, n in enumerate(LENGTHS[tag])}
+    want = {rid: plain.logits(t) for rid, t in seqs.items()}
+    assert all(w.abs().max() > 1.0 for w in want.values())     # logits of order one, not a flat model
+    return tag, folder, seqs, want
+
+
+def replay(folder, tag, dtype, steps, out_dir, max_tokens):
+    from jax_vllm_b200.engine.replay import Replayer
+
+    rep = Replayer(folder, dtype, out_dir, max_tokens=max_tokens, page_size=PAGE_SIZE[tag])
+    rep.run_stream(json.dumps(s) for s in steps)
+    rep.cache.check()
+    assert not rep.cache.live
+    return rep
+
+
+def compare(steps, out_dir, vocab, want, dtype):
+    got = collect(steps, out_dir, vocab)
+    worst = 0.0
+    for rid, rows in got.items():
+        for pos, row in rows.items():
+            w = want[rid][pos]
+            diff = (torch.from_numpy(row.copy()) - w).abs().max().item()
+            lim = limits(dtype, want[rid])
+            assert diff <= lim, f"{rid} position {pos}: |diff| {diff:.3e} > {lim:.3e}"
+            worst = max(worst, diff)
+            if dtype == "float32":
+                assert int(row.argmax()) == int(w.argmax())
+    return got, worst
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_each_request_alone_and_whole(setup, dtype, tmp_path):
+    tag, folder, seqs, want = setup
+    for rid, toks in seqs.items():
+        steps = whole(rid, toks)
+        out = tmp_path / rid
+        replay(folder, tag, dtype, steps, out, max_tokens=128)
+        got, _ = compare(steps, out, TINY[tag]["vocab_size"], want, dtype)
+        assert sorted(got[rid]) == list(range(len(toks)))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_last_32_tokens_one_by_one(setup, dtype, tmp_path):
+    tag, folder, seqs, want = setup
+    for rid, toks in list(seqs.items())[:3]:
+        steps = prefix_then_single(rid, toks, tail=32)
+        out = tmp_path / rid
+        replay(folder, tag, dtype, steps, out, max_tokens=128)
+        compare(steps, out, TINY[tag]["vocab_size"], want, dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("sizes", [(7, 2, 13, 5, 2, 3), (2,), (16, 1, 15, 17), (31, 2, 33)])
+def test_portions_of_changing_size(setup, dtype, sizes, tmp_path):
+    tag, folder, seqs, want = setup
+    rid, toks = "r2", seqs["r2"]
+    steps = portions(rid, toks, sizes)
+    replay(folder, tag, dtype, steps, tmp_path, max_tokens=128)
+    got, _ = compare(steps, tmp_path, TINY[tag]["vocab_size"], want, dtype)
+    assert sorted(got[rid]) == list(range(len(toks)))
+
+
+def mixed_trace(seqs):
+    """Up to four live requests; portions of some beside single tokens of others; requests
+    end and new ones start, in a pool that the sum of all requests would overflow."""
+    ids = list(seqs)
+    fed = {r: 0 for r in ids}
+    plan = [  # (request, tokens to feed) per step; a request may sit a step out
+        [("r0", 9), ("r1", 2)],
+        [("r0", 1), ("r1", 17), ("r2", 5)],
+        [("r0", 1), ("r1", 1), ("r2", 30), ("r3", 2)],
+        [("r0", 24), ("r1", 1), ("r3", 7)],
+        [("r0", 1), ("r1", 1), ("r2", 1), ("r3", 1)],
+        [("r1", 100), ("r0", 100)],              # both finish here: their pages go back
+        [("r2", 3), ("r3", 100), ("r4", 40)],    # r4 and r5 repeat r0 and r1 in reused pages
+        [("r2", 1), ("r4", 1), ("r5", 2)],
+        [("r2", 100), ("r4", 100), ("r5", 100)],
+    ]
+    seqs = dict(seqs, r4=seqs["r0"], r5=seqs["r1"])
+    fed.update(r4=0, r5=0)
+    steps = []
+    for i, row in enumerate(plan):
+        entries, end = [], []
+        for rid, n in row:
+            toks = seqs[rid][fed[rid]:fed[rid] + n]
+            if not toks:
+                continue
+            entries.append({"id": rid, "tokens": toks, "want": list(range(len(toks)))})
+            fed[rid] += len(toks)
+            if fed[rid] == len(seqs[rid]):
+                end.append(rid)
+        steps.append({"step": i, "entries": entries, "end": end})
+    assert all(fed[r] == len(seqs[r]) for r in seqs)
+    return steps, seqs
+
+
+def pool_tokens(seqs):
+    """The most tokens that live requests hold at any time in `mixed_trace`, each request's
+    count rounded up to a multiple of 64: the first four requests together.  The whole trace
+    needs more pages than that, so pages are used again."""
+    return sum(-(-len(s) // 64) * 64 for s in list(seqs.values())[:4])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_mixed_requests_in_reused_pages(setup, dtype, tmp_path):
+    tag, folder, seqs, want = setup
+    steps, all_seqs = mixed_trace(seqs)
+    want = dict(want, r4=want["r0"], r5=want["r1"])
+    rep = replay(folder, tag, dtype, steps, tmp_path, max_tokens=pool_tokens(seqs))
+    got, _ = compare(steps, tmp_path, TINY[tag]["vocab_size"], want, dtype)
+    assert all(sorted(got[r]) == list(range(len(all_seqs[r]))) for r in all_seqs)
+    assert rep.cache.stats["pages_allocated"] > rep.cache.num_pages       # pages were handed out again
+
+
+def test_schedules_agree_with_each_other_in_32_bit(setup, tmp_path):
+    """Differences between ways of cutting are rounding only: far below the distance to the oracle's limit."""
+    tag, folder, seqs, want = setup
+    rid, toks = "r0", seqs["r0"]
+    vocab = TINY[tag]["vocab_size"]
+    a = whole(rid, toks); replay(folder, tag, "float32", a, tmp_path / "a", 128)
+    b = portions(rid, toks, (3, 2, 11)); replay(folder, tag, "float32", b, tmp_path / "b", 128)
+    ga, gb = collect(a, tmp_path / "a", vocab)[rid], collect(b, tmp_path / "b", vocab)[rid]
+    worst = max(np.abs(ga[p] - gb[p]).max() for p in ga)
+    assert worst <= 2e-5 * max(1.0, want[rid].abs().max().item())
+
+
+def test_trace_run_program(setup, tmp_path):
+    """bin/trace_run as a program: stdin steps, `done <step>` lines, files on disk, exit 0."""
+    tag, folder, seqs, want = setup
+    steps, all_seqs = mixed_trace(seqs)
+    env = dict(os.environ)
+    proc = subprocess.run([sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(folder), "--dtype", "float32",
+                           "--out", str(tmp_path), "--max-tokens", str(pool_tokens(seqs)), "--page-size", str(PAGE_SIZE[tag])],
+                          input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, env=env,
+                          timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert proc.stdout.split() == [w for s in steps for w in ("done", str(s["step"]))]
+    compare(steps, tmp_path, TINY[tag]["vocab_size"], dict(want, r4=want["r0"], r5=want["r1"]), "float32")
