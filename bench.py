@@ -1,0 +1,304 @@
+"""Decode and prefill throughput of the engine on one B200, for the Qwen3-8B shape with
+random bfloat16 weights (the metric and configuration that BASELINE.json names).
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L]
+
+Prints ONE JSON line.  `value` is decoded tokens per second at the given batch, each request
+holding 2,048 tokens of context, timed on the device with CUDA events over K decode steps
+after W warm-up steps (a "step" is one decode step: one token for every request of the
+batch).  `e2e` is the same through the Python entry point (`add_request`/`step`), token ids
+from the host and sampled tokens back to the host in every step.  `prefill` is one
+2,048-token prompt in one step; `points` holds decoding at batch 1 and 64; `roofline` is
+the decode step's bytes (every weight it uses once, and the cache of the live requests)
+over its time, against the measured copy bandwidth.  Weights (15 GB) are far larger than
+the L2, so nothing is flushed between iterations.  The engine runs on one GPU only: for
+--gpus N > 1 it says so and exits with 2.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import statistics
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+QWEN3_8B = dict(architectures=["Qwen3ForCausalLM"], vocab_size=151936, hidden_size=4096, intermediate_size=12288,
+                num_hidden_layers=36, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+                rms_norm_eps=1e-6, rope_theta=1e6, max_position_embeddings=40960, tie_word_embeddings=False)
+CONTEXT = 2048
+PREFILL_TOKENS = 2048
+PAGE = 16
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+
+def peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.is_file():
+        try:
+            d = json.loads(p.read_text())
+            return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
+                    "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"]))}, "measured"
+        except Exception:
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons every 200 ms while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index=0):
+        self.proc = None
+        self.index = index
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+        return self
+
+    def __exit__(self, *exc):
+        self.summary = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if self.proc is None:
+            return
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        mhz, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 6:
+                continue
+            try:
+                mhz.append(float(f[0])); mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        if mhz:
+            self.summary = {"sm_mhz": statistics.median(mhz), "sm_max_mhz": max(mx), "reasons": sorted(reasons)}
+
+
+def layer_params(c):
+    H, I, D = c["hidden_size"], c["intermediate_size"], c["head_dim"]
+    Hq, Hkv = c["num_attention_heads"], c["num_key_value_heads"]
+    return H * (Hq + 2 * Hkv) * D + Hq * D * H + 3 * H * I
+
+
+def decode_bytes(c, layers, batch, ctx, itemsize=2):
+    weights = (layers * layer_params(c) + c["vocab_size"] * c["hidden_size"]) * itemsize
+    kv = batch * ctx * layers * 2 * c["num_key_value_heads"] * c["head_dim"] * itemsize
+    return weights + kv
+
+
+def prefill_flops(c, layers, T):
+    gemm = 2 * T * layers * layer_params(c) + 2 * c["vocab_size"] * c["hidden_size"]
+    attn = layers * 4 * c["num_attention_heads"] * c["head_dim"] * T * (T + 1) // 2
+    return gemm + attn
+
+
+def fake_context(driver, batch, ctx):
+    """`batch` live requests that hold `ctx` tokens each, their pages filled with random keys and values
+    (what the tokens were does not change the work of a decode step)."""
+    import torch
+    rcs = []
+    for i in range(batch):
+        rc = driver.cache.admit(("bench", i))
+        driver.cache.grow(rc, ctx)
+        rc.num_tokens = ctx
+        rcs.append(rc)
+    for grp in driver.cache.groups:
+        grp.k.normal_(0, 1)
+        grp.v.normal_(0, 1)
+    torch.cuda.synchronize()
+    return rcs
+
+
+def time_decode(model, batch, steps, warmup, ctx=CONTEXT):
+    """Device time of `steps` decode steps at `batch`; returns (ms per step, launches per step)."""
+    import torch
+    from jax_vllm_b200 import make_driver, ops
+    from jax_vllm_b200.engine import StepEntry
+    max_len = ctx + warmup + steps + 8
+    max_len = -(-max_len // PAGE) * PAGE
+    driver = make_driver(model, max_num_seqs=batch, max_model_len=max_len, block_size=PAGE, prefix_cache=False)
+    rcs = fake_context(driver, batch, ctx)
+    runner, cache, sampler = driver.runner, driver.cache, driver.sampler
+
+    def one(i):
+        entries = []
+        for b, rc in enumerate(rcs):
+            cache.grow(rc, rc.num_tokens + 1)
+            entries.append(StepEntry(rc, [(i * 7919 + b) % 1000], (0,)))
+        logits = runner.step(entries)
+        toks = sampler.greedy(logits)
+        for e in entries:
+            rc = e.cache
+            rc.num_tokens += 1
+        return toks
+
+    for i in range(warmup):
+        one(i)
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    before = ops.launch_count
+    start.record()
+    for i in range(steps):
+        one(warmup + i)
+    end.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(end) / steps
+    launches = (ops.launch_count - before) // steps
+    runner.check_kernels()
+    del driver, runner, cache
+    torch.cuda.empty_cache()
+    return ms, launches
+
+
+def time_prefill(model, tokens, warmup, reps=3):
+    import torch
+    from jax_vllm_b200 import make_driver
+    from jax_vllm_b200.engine import StepEntry
+    max_len = -(-(tokens + 16) // PAGE) * PAGE
+    driver = make_driver(model, max_num_seqs=1, max_model_len=max_len, block_size=PAGE, prefix_cache=False,
+                         max_tokens_per_step=tokens)
+    ids = [(i * 7919 + 13) % 1000 for i in range(tokens)]
+    times = []
+    for r in range(warmup + reps):
+        rc = driver.cache.admit(("prefill", r))
+        driver.cache.grow(rc, tokens)
+        torch.cuda.synchronize()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        driver.runner.step([StepEntry(rc, ids, (tokens - 1,))])
+        e.record()
+        torch.cuda.synchronize()
+        if r >= warmup:
+            times.append(s.elapsed_time(e))
+        driver.cache.release(("prefill", r))
+    driver.runner.check_kernels()
+    del driver
+    torch.cuda.empty_cache()
+    return statistics.median(times)
+
+
+def time_e2e(model, batch, steps, warmup, ctx=CONTEXT):
+    """Through the entry point: `batch` prompts of `ctx` tokens from the host, then decode steps whose
+    sampled tokens come back to the host each step."""
+    import torch
+    from jax_vllm_b200 import SamplingParams, add_request, make_driver, step
+    new = warmup + steps + 4
+    max_len = -(-(ctx + new) // PAGE) * PAGE
+    driver = make_driver(model, max_num_seqs=batch, max_model_len=max_len, block_size=PAGE, prefix_cache=False,
+                         max_tokens_per_step=max(2048, batch))
+    for b in range(batch):
+        add_request(driver, [(i * 31 + b * 977) % 50000 for i in range(ctx)], SamplingParams(max_new_tokens=new))
+    while any(len(r.output_ids) < 1 + warmup for r in driver.requests.values()):   # prompts, then warm-up decodes
+        step(driver)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    emitted = 0
+    for _ in range(steps):
+        emitted += len(step(driver))
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    layout_bytes = 0
+    g = driver.runner.graphs.get(batch)
+    if g is not None:
+        layout_bytes = g.layout.total * 4
+    h2d = layout_bytes + batch * (4 + 16)        # batch description; temperatures, seeds and counters
+    d2h = (batch + 1) * 4                        # sampled tokens and the kernels' status word
+    del driver
+    torch.cuda.empty_cache()
+    return emitted / dt, h2d, d2h
+
+
+def reference_arm():
+    why = ("the reference (jllm) needs jax, jaxlib and equinox and the hatchling build backend; none is installed "
+           "and none is in the offline wheelhouse, so it can neither be installed nor run here")
+    print(json.dumps({"impl": "reference", "unavailable": why}))
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=QWEN3_8B["num_hidden_layers"],
+                    help="fewer layers than the configuration has (same layer sizes), for a quick run")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64, and the prefill")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm()
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    warmup = max(3, args.warmup)
+
+    import torch
+    from jax_vllm_b200 import random_model, registry
+
+    cfg_dict = dict(QWEN3_8B, num_hidden_layers=args.layers)
+    cfg = registry.config_from_dict(cfg_dict)
+    model = random_model(cfg, seed=5, dtype="bf16", device="cuda:0")
+    pk, pk_src = peaks()
+
+    with ClockSampler() as clocks:
+        ms, launches = time_decode(model, args.batch, args.steps, warmup)
+    value = args.batch / (ms / 1e3)
+    bytes_step = decode_bytes(cfg_dict, args.layers, args.batch, CONTEXT + warmup + args.steps // 2)
+    achieved = bytes_step / (ms / 1e3) / 1e9
+    out = {
+        "metric": "decode tok/s (Qwen3-8B shape, bf16, batch 8, 2048-token context)",
+        "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup,
+        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic (uniform random token ids, random N(0,0.02) weights, seed 5)",
+        "config": {"model": "Qwen3-8B shape", "layers": args.layers, "layers_of_config": QWEN3_8B["num_hidden_layers"],
+                   "hidden": 4096, "q_heads": 32, "kv_heads": 8, "head_dim": 128, "intermediate": 12288,
+                   "vocab": 151936, "global_batch": args.batch, "seq_len": CONTEXT, "max_context": 4096,
+                   "page_size": PAGE, "parallelism": "none (1 GPU)", "l2": "inputs larger than L2 (15 GB of weights)",
+                   "cuda_graphs": True},
+        "gpu_launches": launches * args.steps,
+        "clocks": clocks.summary,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4), "peak_source": pk_src},
+    }
+    if not args.skip_points:
+        e2e, h2d, d2h = time_e2e(model, args.batch, args.steps, warmup)
+        out["e2e"] = {"value": round(e2e, 1), "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
+        pms = time_prefill(model, PREFILL_TOKENS, warmup=2)
+        flops = prefill_flops(cfg_dict, args.layers, PREFILL_TOKENS)
+        out["prefill"] = {"value": round(PREFILL_TOKENS / (pms / 1e3), 1), "tokens": PREFILL_TOKENS, "ms": round(pms, 3),
+                          "frac": round(flops / (pms / 1e3) / 1e12 / pk["bf16_tflops"], 4),
+                          "peak_tflops": pk["bf16_tflops"], "peak_source": pk_src}
+        points = {}
+        for b in (1, 64):
+            pms_b, _ = time_decode(model, b, max(8, args.steps // 2), warmup)
+            points[f"decode_b{b}"] = round(b / (pms_b / 1e3), 1)
+        out["points"] = points
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -281,8 +281,12 @@ JV_EXPORT int jv_attn_simt(const void* q, int q_stride, void* out, int out_strid
   JV_DISPATCH_DTYPE(dtype, T, {
     if (n_splits > 0) {
       auto kern = attn_simt_kernel<T, true>;
-      if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-        return JV_ERR_UNSUPPORTED;
+      static size_t allowed = 0;   // set once per size: the attribute call is kept out of stream captures
+      if (smem > allowed) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+          return JV_ERR_UNSUPPORTED;
+        allowed = smem;
+      }
       kern<<<grid, THREADS, smem, stream>>>(p);
       rc = jv_check_launch();
       if (rc == JV_OK) {
@@ -291,8 +295,12 @@ JV_EXPORT int jv_attn_simt(const void* q, int q_stride, void* out, int out_strid
       }
     } else {
       auto kern = attn_simt_kernel<T, false>;
-      if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-        return JV_ERR_UNSUPPORTED;
+      static size_t allowed = 0;
+      if (smem > allowed) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+          return JV_ERR_UNSUPPORTED;
+        allowed = smem;
+      }
       kern<<<grid, THREADS, smem, stream>>>(p);
       rc = jv_check_launch();
     }

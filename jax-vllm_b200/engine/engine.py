@@ -39,7 +39,9 @@ class Driver:
         self.stats = EngineStats()
         self.cache = CacheManager(model.cache_needs(), config.block_size, config.pool_pages, config.max_num_seqs,
                                   config.prefix_cache)
-        self.runner = runner if runner is not None else Runner(model, self.cache, config.device, config.dtype)
+        self.runner = runner if runner is not None else Runner(
+            model, self.cache, config.device, config.dtype, max_model_len=config.max_model_len,
+            cuda_graphs=config.cuda_graphs)
         self.scheduler = Scheduler(self.cache, config.max_tokens_per_step, config.max_model_len, config.prompt_limit,
                                    self.stats)
         self.sampler = sampler if sampler is not None else Sampler(config.device)

@@ -18,15 +18,33 @@ from ..parts import BuildContext, Model
 from .batch import BatchBuilder, StepEntry
 
 
+class _DecodeGraph:
+    """A captured step for `n` single-token entries: fixed buffers, fixed launch sizes."""
+
+    def __init__(self, layout, dev, logits, graph, launches):
+        self.layout, self.dev, self.logits, self.graph, self.launches = layout, dev, logits, graph, launches
+
+
 class Runner:
-    def __init__(self, model: Model, cache: CacheManager, device, dtype: torch.dtype):
+    def __init__(self, model: Model, cache: CacheManager, device, dtype: torch.dtype, max_model_len: int | None = None,
+                 cuda_graphs: bool = False, max_graph_batch: int = 256):
+        """With `cuda_graphs` (which needs `max_model_len`), a step whose entries are all single
+        tokens with their logits wanted is replayed from a CUDA graph captured for that number
+        of entries: block tables have the width of `max_model_len`, and the split attention is
+        launched for `max_model_len` keys (blocks beyond a request's length leave at once)."""
         self.model, self.cache = model, cache
+        self.max_model_len = max_model_len
+        self.cuda_graphs = bool(cuda_graphs) and max_model_len is not None
+        self.max_graph_batch = max_graph_batch
+        self.graphs: dict[int, _DecodeGraph] = {}
+        self.graph_warm: set[int] = set()
+        self.launches_last_step = 0
         self.device, self.dtype = torch.device(device), dtype
         if self.device.type != "cuda":
             raise RuntimeError("the engine runs on a CUDA device only (there is no CPU path)")
         kernel_build.build_all(model.kernels() + ["sampling"])
         views = cache.allocate_storage(dtype, self.device)
-        self.layer_caches = [views.get(i) for i in range(len(model.layers))]
+        self.layer_caches = [views.get(k) for k in range(len(model.order))]
         self.builder = BatchBuilder(len(cache.groups), cache.page_size, model.tile_token_sizes(), self.device)
         self.steps = 0
 
@@ -39,10 +57,63 @@ class Runner:
         if not entries:
             return torch.empty((0, self.model.spec.vocab_size), dtype=torch.float32, device=self.device)
         with torch.cuda.device(self.device):
-            ctx = self.builder.build(entries)
-            logits = self.model.forward(ctx, self.layer_caches)
+            if self._graphable(entries):
+                logits = self._step_graph(entries)
+            else:
+                ctx = self.builder.build(entries)
+                logits = self.model.forward(ctx, self.layer_caches)
         self.steps += 1
         return logits
+
+    # ----------------------------------------------------------- captured decode steps
+    def _graphable(self, entries) -> bool:
+        if not self.cuda_graphs or len(entries) > self.max_graph_batch:
+            return False
+        return all(len(e.tokens) == 1 and tuple(e.want) == (0,) and e.cache.num_tokens < self.max_model_len
+                   for e in entries)
+
+    def _graph_layout(self, entries):
+        width = -(-self.max_model_len // self.cache.page_size)
+        return self.builder.layout_for(entries, table_width=width)
+
+    def _step_graph(self, entries) -> torch.Tensor:
+        n = len(entries)
+        b = self.builder
+        g = self.graphs.get(n)
+        if g is None and n not in self.graph_warm:
+            # first time at this size: run it eagerly once (kernels get their one-time set-up
+            # outside a capture), with the same fixed sizes that the capture will have
+            self.graph_warm.add(n)
+            layout = self._graph_layout(entries)
+            pinned = b._staging(layout.total)
+            b.fill(entries, pinned.numpy()[:layout.total], layout)
+            dev = torch.empty(layout.total, dtype=torch.int32, device=self.device)
+            dev.copy_(pinned[:layout.total], non_blocking=True)
+            b._copied = torch.cuda.Event(); b._copied.record()
+            return self.model.forward(b.context(entries, layout, dev, max_seq_len=self.max_model_len),
+                                      self.layer_caches)
+        if g is None:
+            layout = self._graph_layout(entries)
+            dev = torch.zeros(layout.total, dtype=torch.int32, device=self.device)
+            pinned = b._staging(layout.total)
+            b.fill(entries, pinned.numpy()[:layout.total], layout)
+            dev.copy_(pinned[:layout.total], non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+            ctx = b.context(entries, layout, dev, max_seq_len=self.max_model_len)
+            graph = torch.cuda.CUDAGraph()
+            before = ops.launch_count
+            with torch.cuda.graph(graph):
+                logits = self.model.forward(ctx, self.layer_caches)
+            g = _DecodeGraph(layout, dev, logits, graph, ops.launch_count - before)
+            ops.launch_count = before           # nothing ran yet: a replay counts them
+            self.graphs[n] = g
+        pinned = b._staging(g.layout.total)
+        b.fill(entries, pinned.numpy()[:g.layout.total], g.layout)
+        g.dev.copy_(pinned[:g.layout.total], non_blocking=True)
+        b._copied = torch.cuda.Event(); b._copied.record()
+        g.graph.replay()
+        ops.launch_count += g.launches
+        return g.logits
 
     def run(self, entries: list) -> torch.Tensor:
         """grow -> step -> commit, for callers that do not schedule (replay, tests)."""

@@ -27,6 +27,7 @@ class KernelError(RuntimeError):
 
 
 _fn_cache: dict[tuple[str, str], object] = {}
+launch_count = 0     # kernels of this package launched so far (library products are not counted)
 _status: dict[int, torch.Tensor] = {}
 
 
@@ -45,8 +46,10 @@ def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
-def _check(rc: int, what: str) -> None:
+def _check(rc: int, what: str, launches: int = 1) -> None:
     if rc == 0:
+        global launch_count
+        launch_count += launches
         return
     if rc == 2:
         raise KernelError(f"{what}: these sizes are outside what the kernel handles")
@@ -239,7 +242,7 @@ def attn_simt(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cache: torch.
              k_cache.data_ptr(), v_cache.data_ptr(), block_table.data_ptr(), block_table.shape[1],
              cu_seqlens.data_ptr(), start_pos.data_ptr(), work.data_ptr(), n_work, n_q_heads, n_kv_heads, head_dim,
              k_cache.shape[1], k_cache.shape[0], int(window), float(scale), int(split_size), int(n_splits),
-             status_word(q.device).data_ptr(), _stream()), "attn_simt")
+             status_word(q.device).data_ptr(), _stream()), "attn_simt", launches=2 if n_splits > 0 else 1)
 
 
 # --------------------------------------------------------------------------- linear

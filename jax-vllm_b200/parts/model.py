@@ -19,6 +19,18 @@ class Model(Part):
         self.layers = [build_block(layer, ctx) for layer in spec.layers]
         self.final_norm = build(NORMS, "norm", spec.final_norm, "", ctx)
         self.embedding = self.lm_head = None
+        # A cache belongs to a place in the run order, not to a layer: a layer that the order
+        # names twice shares its weights between the two places but keeps keys and values
+        # (or state) for each.  A layer with `cache_from` reads the cache of the latest
+        # earlier place at which the layer it names ran.
+        self.order = tuple(spec.run_order())
+        self.place_cache = []
+        for k, i in enumerate(self.order):
+            src = spec.layers[i].cache_from
+            if src is None:
+                self.place_cache.append(k)
+            else:
+                self.place_cache.append(max(kk for kk in range(k) if self.order[kk] == src))
 
     # -------------------------------------------------------------------- weights
     def tensor_specs(self):
@@ -54,12 +66,10 @@ class Model(Part):
 
     # ---------------------------------------------------------------------- cache
     def cache_needs(self):
-        """Per layer: its need, or None; a layer with `cache_from` has none of its own."""
-        return [None if layer.spec.cache_from is not None else layer.mixer.cache_need() for layer in self.layers]
-
-    def cache_index(self, layer: int) -> int:
-        src = self.layers[layer].spec.cache_from
-        return layer if src is None else src
+        """Per place in the run order: what the layer there needs to keep, or None (nothing, or
+        it reads another place's cache)."""
+        return [self.layers[i].mixer.cache_need() if self.place_cache[k] == k else None
+                for k, i in enumerate(self.order)]
 
     def tile_token_sizes(self):
         sizes = set()
@@ -74,9 +84,8 @@ class Model(Part):
         """Logits [n_logit_rows, vocab] float32 for one batch; caches are updated in place."""
         h = ops.embed_gather(self.embedding, step.token_ids)
         delta = None
-        for i in self.spec.run_order():
-            cache = caches[self.cache_index(i)]
-            h, delta = self.layers[i].forward(h, delta, step, cache)
+        for k, i in enumerate(self.order):
+            h, delta = self.layers[i].forward(h, delta, step, caches[self.place_cache[k]])
         if step.n_logit_rows == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=h.device)
         x = self.final_norm.gather(h, delta, step.logit_rows)

@@ -180,7 +180,7 @@ def test_a_layer_run_twice_a_shared_cache_and_a_window_beside_full_layers():
     layers[2] = replace(layers[2], cache_from=0)                                 # reads layer 0's keys and values
     spec = replace(spec, layers=tuple(layers), schedule=(0, 1, 2, 1))
     runner, w = make_runner(spec, seed=3)
-    assert [g.layers for g in runner.cache.groups] == [[0], [1]]
+    assert [g.layers for g in runner.cache.groups] == [[0], [1, 3]]      # caches belong to places in the order
     assert "model.layers.2.self_attn.k_proj.weight" not in w
     toks = random_tokens(61, TINY_B["vocab_size"], seed=4)
     want = plain_layers(w, qwen_cfg(TINY_B), toks, (0, 1, 2, 1), windows={1: 13}, cache_from={2: 0})
