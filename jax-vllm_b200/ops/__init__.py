@@ -245,6 +245,44 @@ def attn_simt(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cache: torch.
              status_word(q.device).data_ptr(), _stream()), "attn_simt", launches=2 if n_splits > 0 else 1)
 
 
+MMA_HEAD_DIMS = (16, 32, 64, 128)      # head sizes the tensor-core attention kernels are instantiated for
+
+
+def attn_mma_supports(dtype: torch.dtype, head_dim: int) -> bool:
+    return dtype == torch.bfloat16 and head_dim in MMA_HEAD_DIMS
+
+
+def attn_mma_tokens_per_tile(n_q_heads: int, n_kv_heads: int) -> int:
+    g = n_q_heads // n_kv_heads
+    return 64 // min(g, 16)
+
+
+def attn_mma(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+             block_table: torch.Tensor, cu_seqlens: torch.Tensor, start_pos: torch.Tensor, work: torch.Tensor,
+             n_work: int, n_q_heads: int, n_kv_heads: int, head_dim: int, window: int, scale: float,
+             split_size: int = 0, n_splits: int = 0) -> None:
+    """Paged causal attention for bfloat16 on the tensor cores (csrc/attn_mma.cu); arguments as
+    for `attn_simt`, with `attn_mma_tokens_per_tile` tokens per prompt tile."""
+    for t, nm in ((q, "q"), (out, "out"), (k_cache, "k_cache"), (v_cache, "v_cache")):
+        _cuda(t, nm, torch.bfloat16, contiguous=(nm != "q"))
+    for t, nm in ((block_table, "block_table"), (cu_seqlens, "cu_seqlens"), (start_pos, "start_pos"), (work, "work")):
+        _cuda(t, nm, torch.int32)
+    if n_work == 0:
+        return
+    part_o = part_ml = None
+    if n_splits > 0:
+        part_o = torch.empty(n_work * n_q_heads * n_splits * head_dim, dtype=torch.float32, device=q.device)
+        part_ml = torch.empty(n_work * n_q_heads * n_splits * 2, dtype=torch.float32, device=q.device)
+    f = _fn("attn_mma", "jv_attn_mma", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                        c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                        c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p])
+    _check(f(q.data_ptr(), q_stride, out.data_ptr(), out.stride(0), _ptr(part_o), _ptr(part_ml), k_cache.data_ptr(),
+             v_cache.data_ptr(), block_table.data_ptr(), block_table.shape[1], cu_seqlens.data_ptr(),
+             start_pos.data_ptr(), work.data_ptr(), n_work, n_q_heads, n_kv_heads, head_dim, k_cache.shape[1],
+             k_cache.shape[0], int(window), float(scale), int(split_size), int(n_splits),
+             status_word(q.device).data_ptr(), _stream()), "attn_mma", launches=2 if n_splits > 0 else 1)
+
+
 # --------------------------------------------------------------------------- linear
 def gemm_simt(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
     """x [M, K] times weight [N, K] transposed, accumulated in float32 on CUDA cores."""

@@ -38,6 +38,10 @@ class Attention(Part):
             raise ValueError("rotary dim exceeds the head size")
         self.window = int(spec.window) if spec.window else 0
         self.writes_cache = True          # set False by the model for a layer that reads another's cache
+        # bfloat16 with a head size the tensor-core kernels are built for; else the CUDA-core kernel
+        self.use_mma = ops.attn_mma_supports(ctx.dtype, self.d)
+        if self.use_mma:
+            self.kernels = ("rope_kv", "attn_mma", "gemm_simt")
         self.w_qkv = self.w_o = self.q_norm = self.k_norm = None
 
     # -------------------------------------------------------------------- weights
@@ -79,7 +83,8 @@ class Attention(Part):
         return PagedKVNeed(self.hkv, self.d, self.window or None)
 
     def tile_tokens(self):
-        return ops.attn_simt_tokens_per_tile(self.hq, self.hkv)
+        f = ops.attn_mma_tokens_per_tile if self.use_mma else ops.attn_simt_tokens_per_tile
+        return f(self.hq, self.hkv)
 
     # ----------------------------------------------------------------------- step
     def forward(self, x, step, cache):
@@ -98,15 +103,16 @@ class Attention(Part):
     def attend(self, qkv, out, step, cache, table):
         work, n_work = step.tile_work[self.tile_tokens()]
         common = (cache.k, cache.v, table, step.cu_seqlens, step.start_pos)
+        kernel = ops.attn_mma if self.use_mma else ops.attn_simt
         if n_work:
-            ops.attn_simt(qkv, qkv.stride(0), out, *common, work, n_work, self.hq, self.hkv, self.d,
+            kernel(qkv, qkv.stride(0), out, *common, work, n_work, self.hq, self.hkv, self.d,
                           self.window, self.spec.scale)
         dwork, n_dec = step.decode_work
         if n_dec:
             split = self.ctx.decode_split_size
             n_splits = max(1, -(-step.max_seq_len // split))
-            ops.attn_simt(qkv, qkv.stride(0), out, *common, dwork, n_dec, self.hq, self.hkv, self.d,
-                          self.window, self.spec.scale, split_size=split, n_splits=n_splits)
+            kernel(qkv, qkv.stride(0), out, *common, dwork, n_dec, self.hq, self.hkv, self.d,
+                   self.window, self.spec.scale, split_size=split, n_splits=n_splits)
 
 
 register_mixer("attention", Attention)

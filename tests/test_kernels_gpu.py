@@ -193,7 +193,7 @@ def dense_attention(q, k_all, v_all, q_pos, scale, window, g):
     return torch.einsum("hnl,lhd->nhd", torch.softmax(s, -1), v)
 
 
-def run_attention(ops, dtype, hq, hkv, d, page, q_lens, starts, window=0, split=0, seed=6, boost=None):
+def run_attention(ops, dtype, hq, hkv, d, page, q_lens, starts, window=0, split=0, seed=6, boost=None, mma=False):
     g = torch.Generator().manual_seed(seed)
     G = hq // hkv
     R, n = len(q_lens), sum(q_lens)
@@ -230,15 +230,16 @@ def run_attention(ops, dtype, hq, hkv, d, page, q_lens, starts, window=0, split=
     out = torch.zeros(n, hq * d, dtype=dtype, device=DEV)
     common = (kc.to(dtype).to(DEV), vc.to(dtype).to(DEV), table.to(DEV), cu.to(DEV),
               torch.tensor(starts, dtype=torch.int32, device=DEV))
-    tpt = ops.attn_simt_tokens_per_tile(hq, hkv)
+    tpt = (ops.attn_mma_tokens_per_tile if mma else ops.attn_simt_tokens_per_tile)(hq, hkv)
+    attn = ops.attn_mma if mma else ops.attn_simt
     if split:
         assert all(ql == 1 for ql in q_lens)
         work = torch.tensor([[e, 0] for e in range(R)], dtype=torch.int32, device=DEV)
-        ops.attn_simt(dq, hq * d, out, *common, work, R, hq, hkv, d, window, scale, split_size=split,
-                      n_splits=-(-max(total) // split))
+        attn(dq, hq * d, out, *common, work, R, hq, hkv, d, window, scale, split_size=split,
+             n_splits=-(-max(total) // split))
     else:
         work = torch.tensor([[e, t] for e in range(R) for t in range(0, q_lens[e], tpt)], dtype=torch.int32, device=DEV)
-        ops.attn_simt(dq, hq * d, out, *common, work, work.shape[0], hq, hkv, d, window, scale)
+        attn(dq, hq * d, out, *common, work, work.shape[0], hq, hkv, d, window, scale)
     ops.check_status()
     got = out.float().cpu().reshape(n, hq, d)
     assert not torch.isnan(got).any()
@@ -277,6 +278,54 @@ def test_attention_finds_one_far_key_among_hundreds(ops, split, far):
     got, want = run_attention(ops, torch.float32, 4, 2, 64, 16, q_lens=q_lens, starts=starts, split=split,
                               boost=(1, far))
     torch.testing.assert_close(got, want, atol=3e-5, rtol=3e-5)
+
+
+# ---- the tensor-core kernels (bfloat16) against the same dense reference
+BF16_TOL = dict(atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("hq,hkv,d,page", [(4, 2, 16, 16), (6, 1, 32, 8), (5, 5, 64, 4), (32, 8, 128, 16),
+                                           (20, 1, 64, 16), (3, 1, 128, 32)])
+def test_mma_attention_portions_with_context(ops, hq, hkv, d, page):
+    got, want = run_attention(ops, torch.bfloat16, hq, hkv, d, page, q_lens=[7, 1, 133, 2, 70], starts=[0, 50, 21, 64, 190],
+                              mma=True)
+    torch.testing.assert_close(got, want, **BF16_TOL)
+
+
+@pytest.mark.parametrize("hq,hkv,d,page,split", [(4, 2, 16, 16, 32), (6, 1, 32, 8, 24), (32, 8, 128, 16, 256),
+                                                 (20, 2, 64, 4, 64), (8, 2, 128, 16, 1024)])
+def test_mma_attention_decode_splits(ops, hq, hkv, d, page, split):
+    got, want = run_attention(ops, torch.bfloat16, hq, hkv, d, page, q_lens=[1, 1, 1, 1, 1], starts=[0, 31, 300, 63, 1500],
+                              split=split, mma=True)
+    torch.testing.assert_close(got, want, **BF16_TOL)
+
+
+@pytest.mark.parametrize("window", [1, 5, 16, 40, 100])
+@pytest.mark.parametrize("split", [0, 16])
+def test_mma_attention_window_edges(ops, window, split):
+    q_lens, starts = ([1, 1, 1], [0, 39, 177]) if split else ([9, 130, 1], [0, 35, 177])
+    got, want = run_attention(ops, torch.bfloat16, 4, 2, 32, 8, q_lens=q_lens, starts=starts, window=window, split=split,
+                              mma=True)
+    torch.testing.assert_close(got, want, **BF16_TOL)
+
+
+@pytest.mark.parametrize("split", [0, 64])
+@pytest.mark.parametrize("far", [0, 3, 130, 511])
+def test_mma_attention_finds_one_far_key_among_hundreds(ops, split, far):
+    q_lens = [1, 1] if split else [3, 2]
+    starts = [10, 600 - q_lens[1]]
+    got, want = run_attention(ops, torch.bfloat16, 4, 2, 64, 16, q_lens=q_lens, starts=starts, split=split,
+                              boost=(1, far), mma=True)
+    torch.testing.assert_close(got, want, **BF16_TOL)
+
+
+def test_mma_support_table_matches_the_library(ops):
+    from jax_vllm_b200.csrc import build
+    lib = build.load("attn_mma")
+    for d in range(8, 300, 8):
+        assert bool(lib.jv_attn_mma_supports(d)) == (d in ops.MMA_HEAD_DIMS)
+    assert lib.jv_attn_mma_tokens_per_tile(32, 8) == ops.attn_mma_tokens_per_tile(32, 8) == 16
+    assert not ops.attn_mma_supports(torch.float32, 128)
 
 
 def test_attention_refuses_what_it_cannot_do(ops):
