@@ -247,6 +247,7 @@ def main():
                     help="fewer layers than the configuration has (same layer sizes), for a quick run")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64, and the prefill")
+    ap.add_argument("--only-prefill", action="store_true", help="time the 2,048-token prefill alone (for profiling)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -262,6 +263,10 @@ def main():
     cfg = registry.config_from_dict(cfg_dict)
     model = random_model(cfg, seed=5, dtype="bf16", device="cuda:0")
     pk, pk_src = peaks()
+    if args.only_prefill:
+        pms = time_prefill(model, PREFILL_TOKENS, warmup=1, reps=max(1, args.steps))
+        print(json.dumps({"prefill_ms": round(pms, 3), "tokens": PREFILL_TOKENS, "layers": args.layers}))
+        return 0
 
     with ClockSampler() as clocks:
         ms, launches = time_decode(model, args.batch, args.steps, warmup)
