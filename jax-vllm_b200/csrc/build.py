@@ -29,6 +29,8 @@ SRC_DIR = Path(__file__).resolve().parent
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--shared", "-Xcompiler", "-fPIC"]
 HEADERS = ["common.cuh"]
+# further files that a source includes (they count for its hash)
+DEPENDS = {"attn_decode_static": ["attn_mma.cu", "attn_decode_static.h"]}
 
 _loaded: dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()
@@ -85,7 +87,7 @@ def _extra_flags(name: str) -> list[str]:
 
 def _hash(name: str) -> str:
     h = hashlib.sha256()
-    for f in [f"{name}.cu", *HEADERS]:
+    for f in [f"{name}.cu", *HEADERS, *DEPENDS.get(name, [])]:
         h.update((SRC_DIR / f).read_bytes())
     h.update(" ".join(ARCH_FLAGS + NVCC_FLAGS + _extra_flags(name)).encode())
     return h.hexdigest()[:16]
