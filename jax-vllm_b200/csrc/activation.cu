@@ -17,10 +17,44 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ act, int
   }
 }
 
+// Same, 16 bytes per access (inter a multiple of the vector length, rows 16-byte aligned).
+template <typename T>
+__global__ void swiglu_vec_kernel(const T* __restrict__ gu, T* __restrict__ act, int inter, size_t total_vec) {
+  constexpr int V = 16 / sizeof(T);
+  const int vec_per_row = inter / V;
+  size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; idx < total_vec; idx += stride) {
+    const size_t n = idx / vec_per_row;
+    const int i = (int)(idx - n * vec_per_row) * V;
+    const uint4 g4 = *reinterpret_cast<const uint4*>(gu + n * 2 * inter + i);
+    const uint4 u4 = *reinterpret_cast<const uint4*>(gu + n * 2 * inter + inter + i);
+    const T* g = reinterpret_cast<const T*>(&g4);
+    const T* u = reinterpret_cast<const T*>(&u4);
+    uint4 o4;
+    T* o = reinterpret_cast<T*>(&o4);
+#pragma unroll
+    for (int k = 0; k < V; ++k) {
+      const float gv = to_f32(g[k]);
+      o[k] = from_f32<T>(gv / (1.f + expf(-gv)) * to_f32(u[k]));
+    }
+    *reinterpret_cast<uint4*>(act + n * inter + i) = o4;
+  }
+}
+
 // gu: [n, 2*inter]; act: [n, inter]; both of dtype `dtype`.
 JV_EXPORT int jv_swiglu(const void* gu, void* act, int dtype, int n, int inter, cudaStream_t stream) {
   const size_t total = (size_t)n * inter;
   if (total == 0) return JV_OK;
+  const int vec = dtype == 0 ? 4 : 8;
+  if (inter % vec == 0 && ((uintptr_t)gu % 16) == 0 && ((uintptr_t)act % 16) == 0) {
+    const size_t total_vec = total / vec;
+    size_t blocks = (total_vec + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    JV_DISPATCH_DTYPE(dtype, T, (swiglu_vec_kernel<T><<<(int)blocks, 256, 0, stream>>>(
+                                    (const T*)gu, (T*)act, inter, total_vec)));
+    return jv_check_launch();
+  }
   size_t blocks = (total + 255) / 256;
   if (blocks > 148 * 32) blocks = 148 * 32;
   JV_DISPATCH_DTYPE(dtype, T, (swiglu_kernel<T><<<(int)blocks, 256, 0, stream>>>(

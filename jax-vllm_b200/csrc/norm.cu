@@ -46,6 +46,87 @@ __global__ void rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__ del
   }
 }
 
+// The same with the row held in registers and 8 elements per thread and pass (hidden a multiple
+// of 8, at most blockDim.x * 8 * RM_ITERS): one read of the stream, no second read for the scaling.
+constexpr int RM_ITERS = 4;
+
+template <typename T> __device__ __forceinline__ void load8(const T* p, float (&v)[8]);
+template <> __device__ __forceinline__ void load8<float>(const float* p, float (&v)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+template <> __device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[8]) {
+  const uint4 a = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&a);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) { const float2 f = __bfloat1622float2(h[k]); v[2 * k] = f.x; v[2 * k + 1] = f.y; }
+}
+template <typename T> __device__ __forceinline__ void store8(T* p, const float (&v)[8]);
+template <> __device__ __forceinline__ void store8<float>(float* p, const float (&v)[8]) {
+  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
+template <> __device__ __forceinline__ void store8<__nv_bfloat16>(__nv_bfloat16* p, const float (&v)[8]) {
+  uint4 a;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&a);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) h[k] = __floats2bfloat162_rn(v[2 * k], v[2 * k + 1]);
+  *reinterpret_cast<uint4*>(p) = a;
+}
+
+template <typename TD, typename TW, typename TY>
+__global__ void rmsnorm_vec_kernel(float* __restrict__ h, const TD* __restrict__ delta,
+                                   const int* __restrict__ rows, const TW* __restrict__ weight,
+                                   TY* __restrict__ y, int hidden, float eps, int n_rows_total,
+                                   int* __restrict__ status) {
+  __shared__ float scratch[33];
+  const int i = blockIdx.x;
+  int r = i;
+  if (rows != nullptr) {
+    r = rows[i];
+    if (r < 0 || r >= n_rows_total) {
+      if (threadIdx.x == 0) atomicOr(status, JV_STATUS_BAD_ROW);
+      for (int c = threadIdx.x; c < hidden; c += blockDim.x) y[(size_t)i * hidden + c] = from_f32<TY>(0.f);
+      return;
+    }
+  }
+  float* hr = h + (size_t)r * hidden;
+  const TD* dr = delta ? delta + (size_t)r * hidden : nullptr;
+  const bool write_back = (dr != nullptr) && (rows == nullptr);
+  float v[RM_ITERS][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int it = 0; it < RM_ITERS; ++it) {
+    const int c = (it * blockDim.x + threadIdx.x) * 8;
+    if (c < hidden) {
+      load8<float>(hr + c, v[it]);
+      if (dr) {
+        float d[8];
+        load8<TD>(dr + c, d);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) v[it][k] += d[k];
+        if (write_back) store8<float>(hr + c, v[it]);
+      }
+#pragma unroll
+      for (int k = 0; k < 8; ++k) ss += v[it][k] * v[it][k];
+    }
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = rsqrtf(ss / (float)hidden + eps);
+  TY* yr = y + (size_t)i * hidden;
+#pragma unroll
+  for (int it = 0; it < RM_ITERS; ++it) {
+    const int c = (it * blockDim.x + threadIdx.x) * 8;
+    if (c < hidden) {
+      float w[8];
+      load8<TW>(weight + c, w);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) w[k] = v[it][k] * inv * w[k];
+      store8<TY>(yr + c, w);
+    }
+  }
+}
+
 // h: [n_total, hidden] float (updated in place when delta is given and rows is null);
 // delta: [n_total, hidden] of dtype `delta_dtype` or null; rows: [n_out] int32 or null;
 // weight: [hidden] of dtype `weight_dtype`; y: [n_out, hidden] of dtype `out_dtype`.
@@ -53,6 +134,19 @@ JV_EXPORT int jv_rmsnorm(float* h, const void* delta, int delta_dtype, const int
                          const void* weight, int weight_dtype, void* y, int out_dtype, int n_out,
                          int n_total, int hidden, float eps, int* status, cudaStream_t stream) {
   if (n_out == 0) return JV_OK;
+  const bool aligned = ((uintptr_t)h % 16) == 0 && ((uintptr_t)delta % 16) == 0 && ((uintptr_t)weight % 16) == 0 &&
+                       ((uintptr_t)y % 16) == 0;
+  if (hidden % 8 == 0 && hidden <= 1024 * 8 * RM_ITERS && aligned) {
+    const int vecs = hidden / 8;
+    int iters = (vecs + 511) / 512;                 // up to 512 threads, then more passes per thread
+    if (iters > RM_ITERS) iters = RM_ITERS;
+    int vthreads = ((vecs + iters - 1) / iters + 31) / 32 * 32;
+    if (vthreads > 1024) vthreads = 1024;
+    JV_DISPATCH_DTYPE(out_dtype, TY, JV_DISPATCH_DTYPE(weight_dtype, TW, JV_DISPATCH_DTYPE(delta_dtype, TD,
+        (rmsnorm_vec_kernel<TD, TW, TY><<<n_out, vthreads, 0, stream>>>(
+            h, (const TD*)delta, rows, (const TW*)weight, (TY*)y, hidden, eps, n_total, status)))));
+    return jv_check_launch();
+  }
   int threads = 32;
   while (threads < 512 && threads * 4 < hidden) threads *= 2;
   JV_DISPATCH_DTYPE(out_dtype, TY, JV_DISPATCH_DTYPE(weight_dtype, TW, JV_DISPATCH_DTYPE(delta_dtype, TD,

@@ -83,6 +83,77 @@ __global__ void rope_kv_kernel(T* __restrict__ qkv, int row_stride, const int* _
   }
 }
 
+// The common case without shared memory: the whole head rotates (rot_dim == head_dim) and half
+// the head is a multiple of 32 (head sizes 64, 128, 256).  A lane holds E = head_dim/64 consecutive
+// elements of the first half and their partners of the second half, so norm and rotation stay in
+// registers and accesses are E elements wide.
+template <typename T, int E> struct alignas(sizeof(T) * E) VecE { T v[E]; };
+
+template <typename T, typename TW, int E>
+__global__ void rope_kv_fast_kernel(T* __restrict__ qkv, int row_stride, const int* __restrict__ positions,
+                                    const int* __restrict__ token_entry, const int* __restrict__ block_table,
+                                    int table_width, const float* __restrict__ inv_freq,
+                                    const TW* __restrict__ q_norm_w, const TW* __restrict__ k_norm_w, float eps,
+                                    T* __restrict__ k_cache, T* __restrict__ v_cache, int n_q_heads,
+                                    int n_kv_heads, int page_size, int num_pages, int heads_to_do,
+                                    int* __restrict__ status) {
+  constexpr int HALF = 32 * E, D = 2 * HALF;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n = blockIdx.x;
+  const int head = blockIdx.y * (blockDim.x >> 5) + warp;
+  if (head >= heads_to_do) return;
+  const bool is_q = head < n_q_heads;
+  const bool is_k = !is_q && head < n_q_heads + n_kv_heads;
+  const int kv_head = is_q ? 0 : (is_k ? head - n_q_heads : head - n_q_heads - n_kv_heads);
+  T* src = qkv + (size_t)n * row_stride + (size_t)head * D;
+  const int pos = positions[n];
+  T* dst = src;
+  if (!is_q) {
+    const int entry = token_entry[n];
+    const int page_idx = pos / page_size;
+    const int page = (page_idx < table_width) ? block_table[(size_t)entry * table_width + page_idx] : -1;
+    if (page < 0 || page >= num_pages) {
+      if (lane == 0) atomicOr(status, JV_STATUS_BAD_PAGE);
+      return;
+    }
+    T* cache = is_k ? k_cache : v_cache;
+    dst = cache + (((size_t)page * page_size + (pos - page_idx * page_size)) * n_kv_heads + kv_head) * D;
+  }
+  using V = VecE<T, E>;
+  const int d0 = lane * E;
+  V lo = *reinterpret_cast<const V*>(src + d0), hi = *reinterpret_cast<const V*>(src + HALF + d0);
+  if (!is_q && !is_k) {
+    *reinterpret_cast<V*>(dst + d0) = lo;
+    *reinterpret_cast<V*>(dst + HALF + d0) = hi;
+    return;
+  }
+  float a[E], b[E], ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < E; ++i) {
+    a[i] = to_f32(lo.v[i]); b[i] = to_f32(hi.v[i]);
+    ss += a[i] * a[i] + b[i] * b[i];
+  }
+  const TW* w = is_q ? q_norm_w : k_norm_w;
+  if (w != nullptr) {
+    ss = warp_sum(ss);
+    const float inv = rsqrtf(ss / (float)D + eps);
+#pragma unroll
+    for (int i = 0; i < E; ++i) {
+      a[i] = a[i] * inv * to_f32(w[d0 + i]);
+      b[i] = b[i] * inv * to_f32(w[HALF + d0 + i]);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < E; ++i) {
+    float sn = 0.f, cs = 1.f;
+    if (inv_freq != nullptr) sincosf((float)pos * inv_freq[d0 + i], &sn, &cs);
+    lo.v[i] = from_f32<T>(a[i] * cs - b[i] * sn);
+    hi.v[i] = from_f32<T>(b[i] * cs + a[i] * sn);
+  }
+  *reinterpret_cast<V*>(dst + d0) = lo;
+  *reinterpret_cast<V*>(dst + HALF + d0) = hi;
+}
+
 // qkv: [n, row_stride] of `dtype`; positions, token_entry: [n] int32; block_table:
 // [entries, table_width] int32; inv_freq: [rot_dim/2] float; q_norm_w/k_norm_w: [head_dim]
 // of `w_dtype` or null; k_cache/v_cache: [num_pages, page_size, n_kv_heads, head_dim] of
@@ -98,6 +169,22 @@ JV_EXPORT int jv_rope_kv(void* qkv, int dtype, int row_stride, const int* positi
   const int heads_to_do = k_cache ? n_q_heads + 2 * n_kv_heads : n_q_heads;
   const int warps = 4;
   dim3 grid(n, (heads_to_do + warps - 1) / warps);
+  const int E = head_dim / 64;
+  const bool whole = (rot_dim == head_dim || rot_dim == 0) && (head_dim == 64 || head_dim == 128 || head_dim == 256);
+  const int esz = dtype == 0 ? 4 : 2;
+  if (whole && (row_stride * esz) % (E * esz) == 0 && ((uintptr_t)qkv % 16) == 0 &&
+      (k_cache == nullptr || (((uintptr_t)k_cache % 16) == 0 && ((uintptr_t)v_cache % 16) == 0))) {
+    const float* freq = rot_dim ? inv_freq : nullptr;
+#define JV_ROPE_FAST(EE)                                                                                   \
+    JV_DISPATCH_DTYPE(dtype, T, JV_DISPATCH_DTYPE(w_dtype, TW,                                              \
+        (rope_kv_fast_kernel<T, TW, EE><<<grid, warps * 32, 0, stream>>>(                                   \
+            (T*)qkv, row_stride, positions, token_entry, block_table, table_width, freq, (const TW*)q_norm_w, \
+            (const TW*)k_norm_w, eps, (T*)k_cache, (T*)v_cache, n_q_heads, n_kv_heads, page_size, num_pages, \
+            heads_to_do, status))))
+    if (E == 1) JV_ROPE_FAST(1); else if (E == 2) JV_ROPE_FAST(2); else JV_ROPE_FAST(4);
+#undef JV_ROPE_FAST
+    return jv_check_launch();
+  }
   const size_t smem = (size_t)warps * head_dim * sizeof(float);
   if (smem > 48 * 1024) return JV_ERR_UNSUPPORTED;
   JV_DISPATCH_DTYPE(dtype, T, JV_DISPATCH_DTYPE(w_dtype, TW,

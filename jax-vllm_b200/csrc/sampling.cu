@@ -22,53 +22,83 @@ __host__ __device__ __forceinline__ float jv_uniform(unsigned long long seed, un
   return ((float)(unsigned)(h >> 40) + 0.5f) * (1.0f / 16777216.0f);
 }
 
-__global__ void sample_kernel(const float* __restrict__ logits, int vocab, const float* __restrict__ temperature,
-                              const long long* __restrict__ seeds, const long long* __restrict__ counters,
-                              int* __restrict__ out) {
-  __shared__ float best_v[32];
-  __shared__ int best_i[32];
-  const int row = blockIdx.x;
+// (value, index) ordering: larger value wins, the lower index among equal values.
+__device__ __forceinline__ void take_better(float& bv, int& bi, float ov, int oi) {
+  if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+}
+
+__device__ __forceinline__ void block_best(float& bv, int& bi, float* sv, int* si) {
+  for (int o = 16; o > 0; o >>= 1)
+    take_better(bv, bi, __shfl_xor_sync(0xffffffffu, bv, o), __shfl_xor_sync(0xffffffffu, bi, o));
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) { sv[warp] = bv; si[warp] = bi; }
+  __syncthreads();
+  if (warp == 0) {
+    const int nwarps = blockDim.x >> 5;
+    bv = lane < nwarps ? sv[lane] : -INFINITY;
+    bi = lane < nwarps ? si[lane] : 0x7fffffff;
+    for (int o = 16; o > 0; o >>= 1)
+      take_better(bv, bi, __shfl_xor_sync(0xffffffffu, bv, o), __shfl_xor_sync(0xffffffffu, bi, o));
+  }
+}
+
+// Stage 1: block (chunk, row) finds the best entry of its part of the vocabulary.
+__global__ void sample_partial_kernel(const float* __restrict__ logits, int vocab, int chunk,
+                                      const float* __restrict__ temperature, const long long* __restrict__ seeds,
+                                      const long long* __restrict__ counters, float* __restrict__ part_v,
+                                      int* __restrict__ part_i) {
+  __shared__ float sv[32];
+  __shared__ int si[32];
+  const int row = blockIdx.y;
   const float* lr = logits + (size_t)row * vocab;
   const float temp = temperature[row];
   const unsigned long long seed = (unsigned long long)seeds[row];
   const unsigned long long counter = (unsigned long long)counters[row];
+  const int begin = blockIdx.x * chunk, end = min(vocab, begin + chunk);
   float bv = -INFINITY;
   int bi = 0x7fffffff;
-  for (int v = threadIdx.x; v < vocab; v += blockDim.x) {
+  for (int v = begin + threadIdx.x; v < end; v += blockDim.x) {
     float x = lr[v];
-    if (temp > 0.f) {
-      const float u = jv_uniform(seed, counter, (unsigned long long)v);
-      x = x / temp - logf(-logf(u));
-    }
-    if (x > bv || (x == bv && v < bi)) { bv = x; bi = v; }
+    if (temp > 0.f) x = x / temp - logf(-logf(jv_uniform(seed, counter, (unsigned long long)v)));
+    take_better(bv, bi, x, v);
   }
-  for (int o = 16; o > 0; o >>= 1) {
-    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-    if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
-  }
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  if (lane == 0) { best_v[warp] = bv; best_i[warp] = bi; }
-  __syncthreads();
-  if (warp == 0) {
-    const int nwarps = blockDim.x >> 5;
-    bv = lane < nwarps ? best_v[lane] : -INFINITY;
-    bi = lane < nwarps ? best_i[lane] : 0x7fffffff;
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-      if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
-    }
-    if (lane == 0) out[row] = (bi == 0x7fffffff) ? 0 : bi;
+  block_best(bv, bi, sv, si);
+  if (threadIdx.x == 0) {
+    part_v[(size_t)row * gridDim.x + blockIdx.x] = bv;
+    part_i[(size_t)row * gridDim.x + blockIdx.x] = bi;
   }
 }
 
+// Stage 2: one warp per row over the chunk winners.
+__global__ void sample_final_kernel(const float* __restrict__ part_v, const int* __restrict__ part_i, int n_chunks,
+                                    int* __restrict__ out) {
+  const int row = blockIdx.x;
+  float bv = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int c = threadIdx.x; c < n_chunks; c += 32)
+    take_better(bv, bi, part_v[(size_t)row * n_chunks + c], part_i[(size_t)row * n_chunks + c]);
+  for (int o = 16; o > 0; o >>= 1)
+    take_better(bv, bi, __shfl_xor_sync(0xffffffffu, bv, o), __shfl_xor_sync(0xffffffffu, bi, o));
+  if (threadIdx.x == 0) out[row] = (bi == 0x7fffffff) ? 0 : bi;
+}
+
+// Chunks that the vocabulary is cut into (scratch: rows * chunks floats and ints).
+JV_EXPORT int jv_sample_chunks(int vocab) {
+  int c = (vocab + 2047) / 2048;
+  return c < 1 ? 1 : (c > 128 ? 128 : c);
+}
+
 // logits: [rows, vocab] float; temperature: [rows] float; seeds, counters: [rows] int64;
-// out: [rows] int32.
+// part_v/part_i: scratch of rows * jv_sample_chunks(vocab) elements; out: [rows] int32.
 JV_EXPORT int jv_sample(const float* logits, int rows, int vocab, const float* temperature,
-                        const long long* seeds, const long long* counters, int* out,
-                        cudaStream_t stream) {
+                        const long long* seeds, const long long* counters, float* part_v, int* part_i,
+                        int* out, cudaStream_t stream) {
   if (rows == 0) return JV_OK;
-  sample_kernel<<<rows, 512, 0, stream>>>(logits, vocab, temperature, seeds, counters, out);
+  const int chunks = jv_sample_chunks(vocab);
+  const int chunk = (vocab + chunks - 1) / chunks;
+  sample_partial_kernel<<<dim3(chunks, rows), 256, 0, stream>>>(logits, vocab, chunk, temperature, seeds, counters,
+                                                                part_v, part_i);
+  if (jv_check_launch() != JV_OK) return JV_ERR_LAUNCH;
+  sample_final_kernel<<<rows, 32, 0, stream>>>(part_v, part_i, chunks, out);
   return jv_check_launch();
 }

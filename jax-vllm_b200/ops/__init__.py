@@ -323,7 +323,11 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, seeds: torch.Tensor,
     _cuda(seeds, "seeds", torch.int64); _cuda(counters, "counters", torch.int64)
     rows, vocab = logits.shape
     out = torch.empty(rows, dtype=torch.int32, device=logits.device)
-    f = _fn("sampling", "jv_sample", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p])
+    chunks = min(128, max(1, -(-vocab // 2048)))
+    part_v = torch.empty(rows * chunks, dtype=torch.float32, device=logits.device)
+    part_i = torch.empty(rows * chunks, dtype=torch.int32, device=logits.device)
+    f = _fn("sampling", "jv_sample", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                      c_void_p, c_void_p])
     _check(f(logits.data_ptr(), rows, vocab, temperature.data_ptr(), seeds.data_ptr(), counters.data_ptr(),
-             out.data_ptr(), _stream()), "sample")
+             part_v.data_ptr(), part_i.data_ptr(), out.data_ptr(), _stream()), "sample", launches=2)
     return out

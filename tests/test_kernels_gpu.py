@@ -40,7 +40,7 @@ def test_embed_gather(ops, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("hidden", [200, 4096])
+@pytest.mark.parametrize("hidden", [200, 4096, 1000, 12288, 100])
 @pytest.mark.parametrize("wdtype", DTYPES)
 def test_rmsnorm_variants(ops, dtype, hidden, wdtype):
     g = torch.Generator().manual_seed(1)
@@ -108,7 +108,8 @@ def test_linear_uses_true_float32(ops):
 
 # ------------------------------------------------------------------ rope + kv write
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("hq,hkv,d,page", [(4, 2, 16, 16), (6, 1, 32, 8), (3, 3, 48, 4), (8, 2, 128, 16)])
+@pytest.mark.parametrize("hq,hkv,d,page", [(4, 2, 16, 16), (6, 1, 32, 8), (3, 3, 48, 4), (8, 2, 128, 16), (5, 5, 64, 8),
+                                           (2, 1, 256, 16)])
 def test_rope_kv(ops, dtype, hq, hkv, d, page):
     g = torch.Generator().manual_seed(4)
     q_lens, starts = [5, 1, 9], [3, 40, 0]
