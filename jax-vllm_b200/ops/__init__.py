@@ -299,17 +299,44 @@ def gemm_simt(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype) -> 
     return y
 
 
+SKINNY_MAX_ROWS = 64      # batches up to this many rows take the kernel that is bound by reading the weight
+
+
+def linear_skinny(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """x [M <= 64, K] times weight [N, K] transposed, bfloat16 operands, 32-bit accumulation
+    (csrc/linear_skinny.cu); the result is bfloat16 or float32."""
+    _cuda(x, "x", torch.bfloat16, contiguous=False); _cuda(weight, "weight", torch.bfloat16, contiguous=False)
+    if x.dim() != 2 or weight.dim() != 2 or x.shape[1] != weight.shape[1] or x.stride(1) != 1 or weight.stride(1) != 1:
+        raise KernelError(f"linear shapes {tuple(x.shape)} x {tuple(weight.shape)}^T do not fit")
+    m, k = x.shape
+    n = weight.shape[0]
+    y = torch.empty((m, n), dtype=out_dtype, device=x.device)
+    f = _fn("linear_skinny", "jv_linear_skinny", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
+                                                  c_int, c_void_p])
+    _check(f(x.data_ptr(), x.stride(0), weight.data_ptr(), weight.stride(0), y.data_ptr(), _code(y, "out"), y.stride(0),
+             m, n, k, _stream()), "linear_skinny")
+    return y
+
+
+def _skinny_ok(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    return (x.shape[0] <= SKINNY_MAX_ROWS and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0 and weight.stride(0) % 8 == 0
+            and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0 and x.stride(1) == 1)
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
     """y = x @ weight.T.
 
     float32 weights: the CUDA-core product of this package in true 32-bit (16-bit
     activations are read as they are and widened inside).  bfloat16 weights and
-    activations: cuBLAS through torch.mm, accumulating in 32-bit, the result in
-    `out_dtype` (bfloat16 by default, float32 for logits)."""
+    activations: up to SKINNY_MAX_ROWS rows (decoding) the weight-streaming kernel of this
+    package; more rows (prompts) cuBLAS through torch.mm; both accumulate in 32-bit and give
+    the result in `out_dtype` (bfloat16 by default, float32 for logits)."""
     out_dtype = out_dtype or x.dtype
     if weight.dtype == torch.float32 or x.dtype == torch.float32:
         return gemm_simt(x, weight, out_dtype)
     _cuda(x, "x", torch.bfloat16, contiguous=False); _cuda(weight, "weight", torch.bfloat16)
+    if _skinny_ok(x, weight):
+        return linear_skinny(x, weight, out_dtype)
     if out_dtype == torch.bfloat16:
         return torch.mm(x, weight.t())
     return torch.mm(x, weight.t(), out_dtype=out_dtype)

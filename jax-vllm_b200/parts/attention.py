@@ -41,7 +41,7 @@ class Attention(Part):
         # bfloat16 with a head size the tensor-core kernels are built for; else the CUDA-core kernel
         self.use_mma = ops.attn_mma_supports(ctx.dtype, self.d)
         if self.use_mma:
-            self.kernels = ("rope_kv", "attn_mma", "gemm_simt")
+            self.kernels = ("rope_kv", "attn_mma", "gemm_simt", "linear_skinny")
         self.w_qkv = self.w_o = self.q_norm = self.k_norm = None
 
     # -------------------------------------------------------------------- weights

@@ -97,6 +97,42 @@ def test_gemm_simt(ops, dtype, m, n, k):
     torch.testing.assert_close(ys.double(), wide[:, 8:8 + k].double() @ w.double().T, atol=1e-4, rtol=1e-5)
 
 
+@pytest.mark.parametrize("m", [1, 3, 8, 9, 16, 31, 64])
+@pytest.mark.parametrize("n,k", [(70, 96), (4096, 4096), (1000, 1536), (24, 8), (151, 4104)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_linear_skinny(ops, m, n, k, out_dtype):
+    g = torch.Generator().manual_seed(m * 1000 + n)
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(n, k, generator=g) / k ** 0.5).to(torch.bfloat16).to(DEV)
+    y = ops.linear_skinny(x, w, out_dtype)
+    want = (x.double() @ w.double().T)
+    if out_dtype == torch.float32:
+        torch.testing.assert_close(y.double(), want, atol=1e-4, rtol=1e-4)
+    else:
+        torch.testing.assert_close(y.double(), want, atol=2e-2, rtol=2e-2)
+    # a row's result does not depend on the rest of the batch (other batch sizes take other instantiations)
+    for rows in ([m // 2], list(range(min(m, 5)))):
+        ys = ops.linear_skinny(x[rows].contiguous(), w, out_dtype)
+        assert torch.equal(ys, y[rows])
+    # rows of a wider tensor
+    wide = torch.randn(m, k + 16, generator=g).to(torch.bfloat16).to(DEV)
+    y2 = ops.linear_skinny(wide[:, 8:8 + k], w, torch.float32)
+    torch.testing.assert_close(y2.double(), wide[:, 8:8 + k].double() @ w.double().T, atol=1e-4, rtol=1e-4)
+
+
+def test_linear_dispatch(ops):
+    x = torch.randn(4, 64).to(torch.bfloat16).to(DEV)
+    w = torch.randn(32, 64).to(torch.bfloat16).to(DEV)
+    before = ops.launch_count
+    y = ops.linear(x, w, torch.float32)
+    assert ops.launch_count == before + 1                   # this package's kernel, not the library
+    torch.testing.assert_close(y.double(), x.double() @ w.double().T, atol=1e-3, rtol=1e-3)
+    big = torch.randn(200, 64).to(torch.bfloat16).to(DEV)
+    before = ops.launch_count
+    ops.linear(big, w)
+    assert ops.launch_count == before                       # prompts: the library product
+
+
 def test_linear_uses_true_float32(ops):
     # operands whose product needs more than 10 mantissa bits: a reduced-precision matrix mode would show
     x = torch.full((4, 256), 1.0 + 2 ** -12, device=DEV)
