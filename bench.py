@@ -230,6 +230,69 @@ def time_e2e(model, batch, steps, warmup, ctx=CONTEXT):
     return emitted / dt, h2d, d2h
 
 
+def micro(spec: str, reps: int) -> int:
+    """One kernel alone on data larger than the L2, for profiling:
+    linear:<N>x<K>:<M>   the decode product of M rows with an [N, K] weight (several weights in turn)
+    attn_decode:<B>:<CTX>   split decode attention of B requests with CTX cached tokens (8B head layout)
+    attn_prefill:<T>     prompt attention of one request of T tokens (8B head layout)"""
+    import torch
+    from jax_vllm_b200 import ops
+    kind, *rest = spec.split(":")
+    dev = "cuda:0"
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if kind == "linear":
+        n, k = (int(v) for v in rest[0].split("x"))
+        m = int(rest[1])
+        copies = max(2, int(400e6 // (n * k * 2)) + 1)
+        ws = [(torch.randn(n, k, device=dev) * 0.02).to(torch.bfloat16) for _ in range(copies)]
+        x = torch.randn(m, k, device=dev).to(torch.bfloat16)
+        run = lambda i: ops.linear(x, ws[i % copies])
+        nbytes = n * k * 2
+    else:
+        hq, hkv, d, page = 32, 8, 128, PAGE
+        if kind == "attn_decode":
+            b, ctx = int(rest[0]), int(rest[1])
+            q_lens = [1] * b
+        else:
+            b, ctx, q_lens = 1, 0, [int(rest[0])]
+        total = [ctx + q for q in q_lens]
+        pages_per = [-(-t // page) for t in total]
+        num_pages = sum(pages_per)
+        table = torch.full((b, max(pages_per)), -1, dtype=torch.int32)
+        perm = torch.randperm(num_pages).tolist()
+        for e in range(b):
+            for i in range(pages_per[e]):
+                table[e, i] = perm.pop()
+        kc = torch.randn(num_pages, page, hkv, d, device=dev).to(torch.bfloat16)
+        vc = torch.randn(num_pages, page, hkv, d, device=dev).to(torch.bfloat16)
+        n_tok = sum(q_lens)
+        q = torch.randn(n_tok, hq * d, device=dev).to(torch.bfloat16)
+        out = torch.empty_like(q)
+        cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32, device=dev)
+        st = torch.tensor([ctx] * b, dtype=torch.int32, device=dev)
+        common = (kc, vc, table.to(dev), cu, st)
+        if kind == "attn_decode":
+            work = torch.tensor([[e, 0] for e in range(b)], dtype=torch.int32, device=dev)
+            run = lambda i: ops.attn_mma(q, hq * d, out, *common, work, b, hq, hkv, d, 0, d ** -0.5, split_size=256,
+                                         n_splits=-(-max(total) // 256))
+        else:
+            tpt = ops.attn_mma_tokens_per_tile(hq, hkv)
+            work = torch.tensor([[0, t] for t in range(0, q_lens[0], tpt)], dtype=torch.int32, device=dev)
+            run = lambda i: ops.attn_mma(q, hq * d, out, *common, work, work.shape[0], hq, hkv, d, 0, d ** -0.5)
+        nbytes = 2 * kc.numel() * 2
+    for i in range(3):
+        run(i)
+    torch.cuda.synchronize()
+    start.record()
+    for i in range(reps):
+        run(i)
+    end.record()
+    torch.cuda.synchronize()
+    us = start.elapsed_time(end) / reps * 1e3
+    print(json.dumps({"micro": spec, "us": round(us, 2), "GB/s": round(nbytes / us / 1e3, 1)}))
+    return 0
+
+
 def reference_arm():
     why = ("the reference (jllm) needs jax, jaxlib and equinox and the hatchling build backend; none is installed "
            "and none is in the offline wheelhouse, so it can neither be installed nor run here")
@@ -248,9 +311,12 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64, and the prefill")
     ap.add_argument("--only-prefill", action="store_true", help="time the 2,048-token prefill alone (for profiling)")
+    ap.add_argument("--micro", default=None, help="run one kernel alone, e.g. linear:24576x4096:8 (see micro())")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
+    if args.micro:
+        return micro(args.micro, max(1, args.steps))
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2

@@ -9,11 +9,13 @@
 
 namespace {
 
-constexpr size_t SCRATCH_FLOATS = JV_ATTN_STATIC_SCRATCH_BYTES / sizeof(float);
+constexpr size_t SCRATCH_WORDS = JV_ATTN_STATIC_SCRATCH_BYTES / sizeof(float);
+constexpr size_t COUNTER_WORDS = JV_ATTN_STATIC_COUNTERS;            // first part: arrival counters (ints)
+constexpr size_t SCRATCH_FLOATS = SCRATCH_WORDS - COUNTER_WORDS;     // rest: partial outputs and (max, sum) pairs
 
-// Partial outputs and (max, sum) pairs of the key splits.  In host code this name is only a handle
-// for cudaGetSymbolAddress, never a device address.
-static __device__ __align__(256) float g_static_scratch[SCRATCH_FLOATS];
+// Arrival counters, then partial outputs and (max, sum) pairs of the key splits.  In host code this
+// name is only a handle for cudaGetSymbolAddress, never a device address.
+static __device__ __align__(256) float g_static_scratch[SCRATCH_WORDS];
 
 constexpr int MAX_DEVICES = 64;
 float* g_scratch_ptr[MAX_DEVICES] = {};   // per device, filled by its first call
@@ -47,13 +49,21 @@ extern "C" __attribute__((visibility("default"))) int jv_attn_decode_static(
     int split_size, int n_splits, int* status, cudaStream_t stream) {
   if (n_work == 0) return JV_OK;
   if (n_work < 0 || n_splits < 1 || split_size < 1 || n_q_heads < 1) return JV_ERR_UNSUPPORTED;
+  if (n_kv_heads < 1 || n_q_heads % n_kv_heads != 0) return JV_ERR_UNSUPPORTED;
   const long long need = jv_attn_decode_static_scratch_floats(n_work, n_q_heads, n_splits, head_dim);
-  if (need > (long long)SCRATCH_FLOATS) return JV_ERR_UNSUPPORTED;   // beyond the fixed array: refused
+  const int G = n_q_heads / n_kv_heads;
+  const long long n_counters = (long long)n_work * n_kv_heads * ((G + 15) / 16);
+  if (need > (long long)SCRATCH_FLOATS || n_counters > (long long)COUNTER_WORDS)
+    return JV_ERR_UNSUPPORTED;   // beyond the fixed array: refused
   float* scratch = scratch_on_current_device();
   if (scratch == nullptr) return 3;
-  float* part_o = scratch;                                                     // [n_work*Hq*n_splits][D]
-  float* part_ml = scratch + (size_t)n_work * n_q_heads * n_splits * head_dim; // [n_work*Hq*n_splits][2]
-  return jv_attn_mma(q, q_stride, out, out_stride, part_o, part_ml, k_cache, v_cache, block_table, table_width,
+  int* counters = reinterpret_cast<int*>(scratch);
+  // the counters must be zero when the kernel starts; it leaves them zero, but a call that failed half
+  // way would not, so they are cleared every time (a memset node, not an allocation)
+  if (cudaMemsetAsync(counters, 0, (size_t)n_counters * sizeof(int), stream) != cudaSuccess) return JV_ERR_LAUNCH;
+  float* part_o = scratch + COUNTER_WORDS;                                     // [n_work*Hq*n_splits][D]
+  float* part_ml = part_o + (size_t)n_work * n_q_heads * n_splits * head_dim;  // [n_work*Hq*n_splits][2]
+  return jv_attn_mma(q, q_stride, out, out_stride, part_o, part_ml, counters, k_cache, v_cache, block_table, table_width,
                      cu_seqlens, start_pos, work, n_work, n_q_heads, n_kv_heads, head_dim, page_size, num_pages,
                      window, scale, split_size, n_splits, status, stream);
 }

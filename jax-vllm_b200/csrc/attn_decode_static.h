@@ -19,7 +19,12 @@ extern "C" {
 // device memory from load to exit, whether or not the function is ever called.
 #define JV_ATTN_STATIC_SCRATCH_BYTES (16u << 20)
 
-// Floats of scratch that a call needs: n_work * n_q_heads * n_splits * (head_dim + 2).
+// The first JV_ATTN_STATIC_COUNTERS words of the array are arrival counters, one per
+// (token, kv head, group of 16 query heads); the rest holds the partial results.
+#define JV_ATTN_STATIC_COUNTERS 16384u
+
+// Floats of scratch that a call needs: n_work * n_q_heads * n_splits * (head_dim + 2); they must fit
+// into the array less its counters, and n_work * n_kv_heads * ceil(G / 16) into the counters.
 long long jv_attn_decode_static_scratch_floats(int n_work, int n_q_heads, int n_splits, int head_dim);
 
 // Attention of single decoded tokens over the paged cache, keys split into `n_splits` ranges of
@@ -34,8 +39,8 @@ long long jv_attn_decode_static_scratch_floats(int n_work, int n_q_heads, int n_
 // call on each device looks up the device address of the scratch array (cudaGetSymbolAddress)
 // and opts the kernel into its shared-memory size; make that first call outside any stream
 // capture.  All calls on a device share the one array, which keeps what the last call left in
-// it; nothing has to be cleared, because every element a call reads was written by the same call
-// before.  For the same reason two calls whose kernels may overlap on the GPU (different streams
+// it; the partial results need no clearing, because every element a call reads was written by the
+// same call before, and the counters are cleared by the call itself (a memset on `stream`).  For the same reason two calls whose kernels may overlap on the GPU (different streams
 // without an ordering between them) race on the array: order them.
 int jv_attn_decode_static(const void* q, int q_stride, void* out, int out_stride, const void* k_cache,
                           const void* v_cache, const int* block_table, int table_width, const int* cu_seqlens,

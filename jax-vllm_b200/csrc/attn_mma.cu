@@ -9,8 +9,8 @@
 //   attn_decode_mma   single decoded tokens, split along the keys.  A block takes one split
 //       (split_size key positions, by absolute position) of one request and kv head; its 16
 //       rows are the query heads of the group; the 4 warps take 16 keys each of every 64-key
-//       tile (3 tiles in flight) and are merged in shared memory; a second kernel merges the
-//       splits of a row in ascending order.
+//       tile (3 tiles in flight) and are merged in shared memory; the block that finishes last
+//       among the splits of a row merges them, in ascending order.
 //
 // Scores are scaled and masked in 32-bit (key j visible to position p iff j <= p and
 // (window == 0 or j > p - window)); the running softmax keeps (max, sum) in 32-bit;
@@ -40,6 +40,7 @@ struct Params {
   float scale_log2;            // softmax scale * log2(e)
   int tokens_per_tile, heads_per_tile, n_head_groups, split_size, n_splits;
   int* status;
+  int* counters;               // decode: one per (work item, kv head, head group), zero between launches
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -75,29 +76,38 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // is then 4 modulo 8, so the eight 16-byte rows that one ldmatrix phase reads fall into distinct banks.
 template <int D> struct Tile { static constexpr int STRIDE = D + 8; };
 
-// Copies keys [j0, j0 + BN) of one kv head into a K tile and a V tile (rows beyond j_end zero).
+// Element offsets of the cache rows of keys [j0, j0 + BN) of one kv head (-1: beyond j_end, or no
+// page), one per thread n < BN: the block table is read once per key, ahead of the copies.
 template <int D>
-__device__ __forceinline__ void load_kv_tile(__nv_bfloat16* ks, __nv_bfloat16* vs, const Params& p, int entry,
-                                             int kv_head, int j0, int j_end, int tid) {
-  constexpr int CH = D / 8;  // 16-byte chunks per row
-  constexpr int S = Tile<D>::STRIDE;
-  for (int c = tid; c < BN * CH; c += THREADS) {
-    const int n = c / CH, part = c - n * CH;
-    const int j = j0 + n;
-    bool valid = j < j_end;
-    size_t off = 0;
-    if (valid) {
+__device__ __forceinline__ void tile_rows(long long* rows, const Params& p, int entry, int kv_head, int j0, int j_end,
+                                          int tid) {
+  if (tid < BN) {
+    const int j = j0 + tid;
+    long long off = -1;
+    if (j < j_end) {
       const int pi = j / p.page_size;
       const int page = pi < p.table_width ? p.block_table[(size_t)entry * p.table_width + pi] : -1;
-      if (page < 0 || page >= p.num_pages) {
-        if (part == 0) atomicOr(p.status, JV_STATUS_BAD_PAGE);
-        valid = false;
-      } else {
-        off = (((size_t)page * p.page_size + (j - pi * p.page_size)) * p.n_kv_heads + kv_head) * D + part * 8;
-      }
+      if (page < 0 || page >= p.num_pages) atomicOr(p.status, JV_STATUS_BAD_PAGE);
+      else off = (((long long)page * p.page_size + (j - pi * p.page_size)) * p.n_kv_heads + kv_head) * D;
     }
-    cp_async16(ks + n * S + part * 8, p.k_cache + off, valid);
-    cp_async16(vs + n * S + part * 8, p.v_cache + off, valid);
+    rows[tid] = off;
+  }
+}
+
+// Copies the rows listed by tile_rows into a K tile and a V tile (rows without a source are zero).
+template <int D>
+__device__ __forceinline__ void issue_tile(__nv_bfloat16* ks, __nv_bfloat16* vs, const long long* rows, const Params& p,
+                                           int tid) {
+  constexpr int CH = D / 8;  // 16-byte chunks per row
+  constexpr int S = Tile<D>::STRIDE;
+#pragma unroll
+  for (int c = tid; c < BN * CH; c += THREADS) {
+    const int n = c / CH, part = c - n * CH;
+    const long long off = rows[n];
+    const bool valid = off >= 0;
+    const long long src = valid ? off + part * 8 : 0;
+    cp_async16(ks + n * S + part * 8, p.k_cache + src, valid);
+    cp_async16(vs + n * S + part * 8, p.v_cache + src, valid);
   }
 }
 
@@ -197,6 +207,7 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_mma_kernel(const Params 
   __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);    // [64][S]
   __nv_bfloat16* ks = qs + ROWS_PREFILL * S;                          // [2][BN][S]
   __nv_bfloat16* vs = ks + 2 * BN * S;                                // [2][BN][S]
+  __shared__ long long rows[2][BN];
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int entry = p.work[2 * blockIdx.x], q_off = p.work[2 * blockIdx.x + 1];
@@ -222,7 +233,10 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_mma_kernel(const Params 
     cp_async16(qs + r * S + part * 8, p.q + off, valid);
   }
   const int n_tiles = (j_hi - j_lo + BN - 1) / BN;
-  load_kv_tile<D>(ks, vs, p, entry, kv_head, j_lo, j_hi, tid);
+  tile_rows<D>(rows[0], p, entry, kv_head, j_lo, j_hi, tid);
+  tile_rows<D>(rows[1], p, entry, kv_head, j_lo + BN, j_hi, tid);
+  __syncthreads();
+  issue_tile<D>(ks, vs, rows[0], p, tid);
   cp_async_commit();
 
   // ---- this thread's two rows
@@ -247,9 +261,10 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_mma_kernel(const Params 
 
   for (int t = 0; t < n_tiles; ++t) {
     const int buf = t & 1;
-    if (t + 1 < n_tiles)
-      load_kv_tile<D>(ks + (buf ^ 1) * BN * S, vs + (buf ^ 1) * BN * S, p, entry, kv_head, j_lo + (t + 1) * BN, j_hi, tid);
+    if (t + 1 < n_tiles) issue_tile<D>(ks + (buf ^ 1) * BN * S, vs + (buf ^ 1) * BN * S, rows[buf ^ 1], p, tid);
     cp_async_commit();
+    // rows of tile t+2 go where those of tile t were (read when tile t was issued, an iteration ago)
+    if (t + 2 < n_tiles) tile_rows<D>(rows[buf], p, entry, kv_head, j_lo + (t + 2) * BN, j_hi, tid);
     cp_async_wait<1>();
     __syncthreads();
     const int key0 = j_lo + t * BN;
@@ -296,6 +311,8 @@ __global__ void __launch_bounds__(THREADS) attn_decode_mma_kernel(const Params p
   __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);    // [16][S]
   __nv_bfloat16* ks = qs + 16 * S;                                    // [STAGES][BN][S]
   __nv_bfloat16* vs = ks + DECODE_STAGES * BN * S;                    // [STAGES][BN][S]
+  __shared__ long long rows[DECODE_STAGES][BN];
+  __shared__ int is_last;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int entry = p.work[2 * blockIdx.x];
@@ -303,10 +320,9 @@ __global__ void __launch_bounds__(THREADS) attn_decode_mma_kernel(const Params p
   const int G = p.n_q_heads / p.n_kv_heads;
   const int HPT = p.heads_per_tile;
   const int pos_q = p.start_pos[entry];
-  int j_lo = p.window > 0 ? max(0, pos_q - p.window + 1) : 0;
-  int j_hi = pos_q + 1;
-  j_lo = max(j_lo, (int)blockIdx.z * p.split_size);
-  j_hi = min(j_hi, ((int)blockIdx.z + 1) * p.split_size);
+  const int vis_lo = p.window > 0 ? max(0, pos_q - p.window + 1) : 0;   // visible keys: [vis_lo, pos_q]
+  const int j_lo = max(vis_lo, (int)blockIdx.z * p.split_size);
+  const int j_hi = min(pos_q + 1, ((int)blockIdx.z + 1) * p.split_size);
   if (j_lo >= j_hi) return;
   const int token = p.cu_seqlens[entry];
 
@@ -320,9 +336,11 @@ __global__ void __launch_bounds__(THREADS) attn_decode_mma_kernel(const Params p
   }
   const int n_tiles = (j_hi - j_lo + BN - 1) / BN;
 #pragma unroll
+  for (int st = 0; st < DECODE_STAGES; ++st) tile_rows<D>(rows[st], p, entry, kv_head, j_lo + st * BN, j_hi, tid);
+  __syncthreads();
+#pragma unroll
   for (int st = 0; st < DECODE_STAGES - 1; ++st) {
-    if (st < n_tiles)
-      load_kv_tile<D>(ks + st * BN * S, vs + st * BN * S, p, entry, kv_head, j_lo + st * BN, j_hi, tid);
+    if (st < n_tiles) issue_tile<D>(ks + st * BN * S, vs + st * BN * S, rows[st], p, tid);
     cp_async_commit();
   }
 
@@ -344,9 +362,12 @@ __global__ void __launch_bounds__(THREADS) attn_decode_mma_kernel(const Params p
     const int nxt = t + DECODE_STAGES - 1;
     if (nxt < n_tiles) {
       const int nb = nxt % DECODE_STAGES;
-      load_kv_tile<D>(ks + nb * BN * S, vs + nb * BN * S, p, entry, kv_head, j_lo + nxt * BN, j_hi, tid);
+      issue_tile<D>(ks + nb * BN * S, vs + nb * BN * S, rows[nb], p, tid);
     }
     cp_async_commit();
+    // rows of tile t+STAGES go where those of tile t were (read when tile t was issued)
+    if (t + DECODE_STAGES < n_tiles)
+      tile_rows<D>(rows[t % DECODE_STAGES], p, entry, kv_head, j_lo + (t + DECODE_STAGES) * BN, j_hi, tid);
     cp_async_wait<DECODE_STAGES - 1>();
     __syncthreads();
     const int buf = t % DECODE_STAGES;
@@ -405,37 +426,42 @@ __global__ void __launch_bounds__(THREADS) attn_decode_mma_kernel(const Params p
     p.part_o[slot * D + d] = o;
     if (d == 0) { p.part_ml[slot * 2] = m_all; p.part_ml[slot * 2 + 1] = lsum; }
   }
-}
 
-// Merges the splits of one (token, head): one warp each; max and sums in the log2 domain.
-template <int D>
-__global__ void attn_decode_combine_kernel(const Params p, int n_work) {
-  const int lane = threadIdx.x & 31;
-  const int idx = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (idx >= n_work * p.n_q_heads) return;
-  const int x = idx / p.n_q_heads, head = idx - x * p.n_q_heads;
-  const int entry = p.work[2 * x];
-  const int pos = p.start_pos[entry];
-  const int j_lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
-  const int s_first = j_lo / p.split_size;
-  int s_last = pos / p.split_size;
-  if (s_last >= p.n_splits) {
-    if (lane == 0) atomicOr(p.status, JV_STATUS_BAD_ROW);
+  // ---- the block that finishes last among the splits of this (token, kv head, head group) merges them,
+  //      in ascending order of the splits whichever block that is.  Nobody waits: a block adds one to the
+  //      counter when its partial result is written and leaves unless it brought the count to the total.
+  const int s_first = vis_lo / p.split_size;
+  int s_last = pos_q / p.split_size;
+  if (s_last >= p.n_splits) {           // the launch has too few splits for this length
+    if (tid == 0) atomicOr(p.status, JV_STATUS_BAD_ROW);
     s_last = p.n_splits - 1;
   }
-  const size_t base = ((size_t)x * p.n_q_heads + head) * p.n_splits;
-  float m_all = -INFINITY;
-  for (int s = s_first; s <= s_last; ++s) m_all = fmaxf(m_all, p.part_ml[(base + s) * 2]);
-  float l_all = 0.f;
-  for (int s = s_first; s <= s_last; ++s)
-    l_all += exp2f(p.part_ml[(base + s) * 2] - m_all) * p.part_ml[(base + s) * 2 + 1];
-  const float inv = 1.f / l_all;
-  __nv_bfloat16* dst = p.out + (size_t)p.cu_seqlens[entry] * p.out_stride + (size_t)head * D;
-  for (int d = lane; d < D; d += 32) {
-    float o = 0.f;
-    for (int s = s_first; s <= s_last; ++s)
-      o += exp2f(p.part_ml[(base + s) * 2] - m_all) * p.part_o[(base + s) * D + d];
-    dst[d] = __float2bfloat16_rn(o * inv);
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    int* counter = p.counters + (size_t)blockIdx.x * gridDim.y + blockIdx.y;
+    const int done = atomicAdd(counter, 1) + 1;
+    is_last = (done == s_last - s_first + 1);
+    if (is_last) *counter = 0;          // ready for the next launch
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  for (int idx = tid; idx < HPT * D; idx += THREADS) {
+    const int r = idx / D, d = idx - r * D;
+    const int hh = hg * HPT + r;
+    if (hh >= G) continue;
+    const int head = kv_head * G + hh;
+    const size_t base = ((size_t)blockIdx.x * p.n_q_heads + head) * p.n_splits;
+    float m_all = -INFINITY;
+    for (int sp = s_first; sp <= s_last; ++sp) m_all = fmaxf(m_all, __ldcg(p.part_ml + (base + sp) * 2));
+    float o = 0.f, l_all = 0.f;
+    for (int sp = s_first; sp <= s_last; ++sp) {
+      const float f = exp2f(__ldcg(p.part_ml + (base + sp) * 2) - m_all);
+      l_all += f * __ldcg(p.part_ml + (base + sp) * 2 + 1);
+      o += f * __ldcg(p.part_o + (base + sp) * D + d);
+    }
+    p.out[(size_t)token * p.out_stride + (size_t)head * D + d] = __float2bfloat16_rn(o / l_all);
   }
 }
 
@@ -469,10 +495,6 @@ int launch(const Params& p, int n_work, bool split, cudaStream_t stream) {
   }
   dim3 grid(n_work, p.n_kv_heads * p.n_head_groups, p.n_splits);
   attn_decode_mma_kernel<D><<<grid, THREADS, smem, stream>>>(p);
-  int rc = jv_check_launch();
-  if (rc != JV_OK) return rc;
-  const int rows = n_work * p.n_q_heads;
-  attn_decode_combine_kernel<D><<<(rows + 3) / 4, 128, 0, stream>>>(p, n_work);
   return jv_check_launch();
 }
 }  // namespace
@@ -490,9 +512,11 @@ JV_EXPORT int jv_attn_mma_tokens_per_tile(int n_q_heads, int n_kv_heads) {
 
 // Arguments as for jv_attn_simt (csrc/attn_simt.cu), bfloat16 only.  n_splits == 0: prompt portions,
 // work = (entry, first token of the tile) with jv_attn_mma_tokens_per_tile tokens per tile.
-// n_splits > 0: single tokens, part_o [n_work*Hq*n_splits*D] and part_ml [n_work*Hq*n_splits*2] floats.
+// n_splits > 0: single tokens, part_o [n_work*Hq*n_splits*D] and part_ml [n_work*Hq*n_splits*2] floats of
+// scratch, and `counters`, n_work * n_kv_heads * ceil(G/16) ints that are zero before the launch (the
+// kernel leaves them zero).
 JV_EXPORT int jv_attn_mma(const void* q, int q_stride, void* out, int out_stride, float* part_o, float* part_ml,
-                          const void* k_cache, const void* v_cache, const int* block_table, int table_width,
+                          int* counters, const void* k_cache, const void* v_cache, const int* block_table, int table_width,
                           const int* cu_seqlens, const int* start_pos, const int* work, int n_work,
                           int n_q_heads, int n_kv_heads, int head_dim, int page_size, int num_pages, int window,
                           float scale, int split_size, int n_splits, int* status, cudaStream_t stream) {
@@ -502,7 +526,7 @@ JV_EXPORT int jv_attn_mma(const void* q, int q_stride, void* out, int out_stride
     return JV_ERR_UNSUPPORTED;   // 16-byte copies need aligned rows
   Params p;
   p.q = (const __nv_bfloat16*)q; p.q_stride = q_stride; p.out = (__nv_bfloat16*)out; p.out_stride = out_stride;
-  p.part_o = part_o; p.part_ml = part_ml;
+  p.part_o = part_o; p.part_ml = part_ml; p.counters = counters;
   p.k_cache = (const __nv_bfloat16*)k_cache; p.v_cache = (const __nv_bfloat16*)v_cache;
   p.block_table = block_table; p.table_width = table_width; p.cu_seqlens = cu_seqlens; p.start_pos = start_pos;
   p.work = work; p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads; p.page_size = page_size;

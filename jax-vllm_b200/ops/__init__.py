@@ -257,6 +257,21 @@ def attn_mma_tokens_per_tile(n_q_heads: int, n_kv_heads: int) -> int:
     return 64 // min(g, 16)
 
 
+_counters: dict[int, torch.Tensor] = {}
+
+
+def _split_counters(device, n: int) -> torch.Tensor:
+    """Zeroed arrival counters for the split decode attention: one buffer per device, kept for
+    the life of the process (the kernel leaves the counters zero; launches on one stream follow
+    one another, so they can share it)."""
+    idx = torch.device(device).index or 0
+    buf = _counters.get(idx)
+    if buf is None or buf.numel() < n:
+        buf = torch.zeros(max(n, 1 << 16), dtype=torch.int32, device=device)
+        _counters[idx] = buf
+    return buf
+
+
 def attn_mma(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
              block_table: torch.Tensor, cu_seqlens: torch.Tensor, start_pos: torch.Tensor, work: torch.Tensor,
              n_work: int, n_q_heads: int, n_kv_heads: int, head_dim: int, window: int, scale: float,
@@ -269,18 +284,20 @@ def attn_mma(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cache: torch.T
         _cuda(t, nm, torch.int32)
     if n_work == 0:
         return
-    part_o = part_ml = None
+    part_o = part_ml = counters = None
     if n_splits > 0:
         part_o = torch.empty(n_work * n_q_heads * n_splits * head_dim, dtype=torch.float32, device=q.device)
         part_ml = torch.empty(n_work * n_q_heads * n_splits * 2, dtype=torch.float32, device=q.device)
-    f = _fn("attn_mma", "jv_attn_mma", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+        counters = _split_counters(q.device, n_work * n_kv_heads * (-(-(n_q_heads // n_kv_heads) // 16)))
+    f = _fn("attn_mma", "jv_attn_mma", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                         c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                         c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p])
-    _check(f(q.data_ptr(), q_stride, out.data_ptr(), out.stride(0), _ptr(part_o), _ptr(part_ml), k_cache.data_ptr(),
+    _check(f(q.data_ptr(), q_stride, out.data_ptr(), out.stride(0), _ptr(part_o), _ptr(part_ml), _ptr(counters),
+             k_cache.data_ptr(),
              v_cache.data_ptr(), block_table.data_ptr(), block_table.shape[1], cu_seqlens.data_ptr(),
              start_pos.data_ptr(), work.data_ptr(), n_work, n_q_heads, n_kv_heads, head_dim, k_cache.shape[1],
              k_cache.shape[0], int(window), float(scale), int(split_size), int(n_splits),
-             status_word(q.device).data_ptr(), _stream()), "attn_mma", launches=2 if n_splits > 0 else 1)
+             status_word(q.device).data_ptr(), _stream()), "attn_mma")
 
 
 # --------------------------------------------------------------------------- linear
@@ -299,11 +316,11 @@ def gemm_simt(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype) -> 
     return y
 
 
-SKINNY_MAX_ROWS = 64      # batches up to this many rows take the kernel that is bound by reading the weight
+SKINNY_MAX_ROWS = 16      # batches up to this many rows take the kernel that is bound by reading the weight
 
 
 def linear_skinny(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
-    """x [M <= 64, K] times weight [N, K] transposed, bfloat16 operands, 32-bit accumulation
+    """x [M <= 16, K] times weight [N, K] transposed, bfloat16 operands, 32-bit accumulation
     (csrc/linear_skinny.cu); the result is bfloat16 or float32."""
     _cuda(x, "x", torch.bfloat16, contiguous=False); _cuda(weight, "weight", torch.bfloat16, contiguous=False)
     if x.dim() != 2 or weight.dim() != 2 or x.shape[1] != weight.shape[1] or x.stride(1) != 1 or weight.stride(1) != 1:

@@ -97,8 +97,8 @@ def test_gemm_simt(ops, dtype, m, n, k):
     torch.testing.assert_close(ys.double(), wide[:, 8:8 + k].double() @ w.double().T, atol=1e-4, rtol=1e-5)
 
 
-@pytest.mark.parametrize("m", [1, 3, 8, 9, 16, 31, 64])
-@pytest.mark.parametrize("n,k", [(70, 96), (4096, 4096), (1000, 1536), (24, 8), (151, 4104)])
+@pytest.mark.parametrize("m", [1, 3, 8, 9, 16])
+@pytest.mark.parametrize("n,k", [(70, 96), (4096, 4096), (1000, 1536), (24, 8), (151, 4104), (24576, 512)])
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
 def test_linear_skinny(ops, m, n, k, out_dtype):
     g = torch.Generator().manual_seed(m * 1000 + n)
