@@ -5,6 +5,8 @@
 
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ act, int inter, size_t total) {
+  pdl_trigger();
+  pdl_wait();
   size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   for (; idx < total; idx += stride) {
@@ -20,6 +22,8 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ act, int
 // Same, 16 bytes per access (inter a multiple of the vector length, rows 16-byte aligned).
 template <typename T>
 __global__ void swiglu_vec_kernel(const T* __restrict__ gu, T* __restrict__ act, int inter, size_t total_vec) {
+  pdl_trigger();
+  pdl_wait();
   constexpr int V = 16 / sizeof(T);
   const int vec_per_row = inter / V;
   size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -51,13 +55,13 @@ JV_EXPORT int jv_swiglu(const void* gu, void* act, int dtype, int n, int inter, 
     const size_t total_vec = total / vec;
     size_t blocks = (total_vec + 255) / 256;
     if (blocks > 148 * 16) blocks = 148 * 16;
-    JV_DISPATCH_DTYPE(dtype, T, (swiglu_vec_kernel<T><<<(int)blocks, 256, 0, stream>>>(
-                                    (const T*)gu, (T*)act, inter, total_vec)));
-    return jv_check_launch();
+    JV_DISPATCH_DTYPE(dtype, T, return jv_launch(swiglu_vec_kernel<T>, dim3((int)blocks), dim3(256), 0, stream,
+                                                  (const T*)gu, (T*)act, inter, total_vec));
+    return JV_ERR_UNSUPPORTED;
   }
   size_t blocks = (total + 255) / 256;
   if (blocks > 148 * 32) blocks = 148 * 32;
-  JV_DISPATCH_DTYPE(dtype, T, (swiglu_kernel<T><<<(int)blocks, 256, 0, stream>>>(
-                                  (const T*)gu, (T*)act, inter, total)));
-  return jv_check_launch();
+  JV_DISPATCH_DTYPE(dtype, T, return jv_launch(swiglu_kernel<T>, dim3((int)blocks), dim3(256), 0, stream,
+                                                (const T*)gu, (T*)act, inter, total));
+  return JV_ERR_UNSUPPORTED;
 }

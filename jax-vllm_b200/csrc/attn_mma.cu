@@ -1,5 +1,6 @@
 // Paged causal attention for bfloat16 on the tensor cores (mma.sync m16n8k16, 32-bit
-// accumulation), keys and values streamed from the pages with cp.async.  Two kernels share
+// accumulation), keys and values streamed from the pages by bulk copies (one per cache row, completion
+// counted on mbarriers; every wait is bounded and reports to the status word).  Two kernels share
 // the tile code:
 //
 //   attn_prefill_mma  prompt portions.  A tile is 64 rows = (token, query head) pairs of ONE
@@ -94,21 +95,60 @@ __device__ __forceinline__ void tile_rows(long long* rows, const Params& p, int 
   }
 }
 
-// Copies the rows listed by tile_rows into a K tile and a V tile (rows without a source are zero).
+// ---- mbarrier + bulk-copy (TMA) helpers.  A cache row of one kv head is D contiguous elements, so a
+// 64-key tile is 64 + 64 bulk copies, one per thread, instead of 16-byte copies by the thousand; their
+// completion is counted in bytes on the stage's mbarrier.
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect(uint64_t* bar, int bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_copy(void* dst, const void* src, int bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
+               ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+// Waits for phase `parity` of the barrier, at most ~a second; false if it gave up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, int parity) {
+  for (int spin = 0; spin < (1 << 20); ++spin) {
+    uint32_t done;
+    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+                 : "=r"(done) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+
+// Copies the rows listed by tile_rows into a K tile and a V tile: thread n < 64 the key row n, thread
+// 64 + n the value row n (a row without a source is zeroed by the thread).  Every thread arrives once
+// on `bar`, which completes when all bytes have landed.
 template <int D>
 __device__ __forceinline__ void issue_tile(__nv_bfloat16* ks, __nv_bfloat16* vs, const long long* rows, const Params& p,
-                                           int tid) {
-  constexpr int CH = D / 8;  // 16-byte chunks per row
+                                           uint64_t* bar, int tid) {
+  static_assert(THREADS == 2 * BN, "one thread per key row and per value row");
   constexpr int S = Tile<D>::STRIDE;
+  const int n = tid & (BN - 1);
+  const bool is_v = tid >= BN;
+  const long long off = rows[n];
+  __nv_bfloat16* dst = (is_v ? vs : ks) + n * S;
+  if (off >= 0) {
+    mbar_arrive_expect(bar, D * 2);
+    bulk_copy(dst, (is_v ? p.v_cache : p.k_cache) + off, D * 2, bar);
+  } else {
 #pragma unroll
-  for (int c = tid; c < BN * CH; c += THREADS) {
-    const int n = c / CH, part = c - n * CH;
-    const long long off = rows[n];
-    const bool valid = off >= 0;
-    const long long src = valid ? off + part * 8 : 0;
-    cp_async16(ks + n * S + part * 8, p.k_cache + src, valid);
-    cp_async16(vs + n * S + part * 8, p.v_cache + src, valid);
+    for (int c = 0; c < D / 8; ++c) *reinterpret_cast<uint4*>(dst + c * 8) = make_uint4(0, 0, 0, 0);
+    mbar_arrive(bar);
   }
+}
+
+// Waits for a tile; on a timeout records it in the status word (the caller then leaves).
+__device__ __forceinline__ bool wait_tile(uint64_t* bar, int parity, const Params& p) {
+  if (mbar_wait(bar, parity)) return true;
+  atomicOr(p.status, JV_STATUS_WAIT_EXPIRED);
+  return false;
 }
 
 // S[16 rows, NB*8 keys] += Q[16, D] K[keys, D]^T for one warp.  `qs` points at the warp's first
@@ -153,10 +193,19 @@ __device__ __forceinline__ void pv_tile(float (&o)[D / 8][4], const float (&pr)[
   }
 }
 
-// Masks, scales and exponentiates one warp's scores of a tile and updates the running (max, sum)
-// of its two rows per thread; rescales the output accumulators.  pos0/pos1: positions of the rows
-// lane/4 and lane/4 + 8 (-1: unused row).  Key of s[nb][i]: key0 + nb*8 + (lane%4)*2 + (i&1).
-template <int D, int NB>
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// Exponentiates one warp's scores of a tile and updates the running (max, sum) of its two rows per
+// thread; rescales the output accumulators.  The running maximum m is kept in units of the raw
+// score; exp2(s*c - m*c) with c = scale * log2(e) is one multiply-add and one ex2.  With MASK the
+// visibility test is applied first (key0 + nb*8 + (lane%4)*2 + (i&1) is the key of s[nb][i]; pos0/pos1
+// are the positions of rows lane/4 and lane/4 + 8, -1 for an unused row); tiles that lie wholly
+// inside every row's visible range are handled without it.
+template <int D, int NB, bool MASK>
 __device__ __forceinline__ void softmax_tile(float (&s)[NB][4], float (&o)[D / 8][4], float (&m)[2], float (&l)[2],
                                              int pos0, int pos1, int key0, int j_end, int window,
                                              float scale_log2, int lane) {
@@ -165,20 +214,22 @@ __device__ __forceinline__ void softmax_tile(float (&s)[NB][4], float (&o)[D / 8
   for (int nb = 0; nb < NB; ++nb)
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      const int key = key0 + nb * 8 + (lane & 3) * 2 + (i & 1);
-      const int pos = (i < 2) ? pos0 : pos1;
-      const bool vis = pos >= 0 && key < j_end && key <= pos && (window <= 0 || key > pos - window);
-      s[nb][i] = vis ? s[nb][i] * scale_log2 : -INFINITY;
+      if (MASK) {
+        const int key = key0 + nb * 8 + (lane & 3) * 2 + (i & 1);
+        const int pos = (i < 2) ? pos0 : pos1;
+        const bool vis = key < j_end && key <= pos && (window <= 0 || key > pos - window);
+        if (!vis) s[nb][i] = -INFINITY;
+      }
       mx[i >> 1] = fmaxf(mx[i >> 1], s[nb][i]);
     }
-  float alpha[2], m_use[2];
+  float alpha[2], m_scaled[2];
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
     mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
     const float m_new = fmaxf(m[h], mx[h]);
-    alpha[h] = (m[h] == -INFINITY) ? 0.f : exp2f(m[h] - m_new);   // m_new == -inf only if m[h] is too
-    m_use[h] = (m_new == -INFINITY) ? 0.f : m_new;                // then every score is -inf: p = 0
+    alpha[h] = (m[h] == -INFINITY) ? 0.f : fast_exp2((m[h] - m_new) * scale_log2);  // m_new == -inf only if m[h] is
+    m_scaled[h] = (m_new == -INFINITY) ? 0.f : m_new * scale_log2;                   // then every score is -inf: p = 0
     m[h] = m_new;
   }
   float sum[2] = {0.f, 0.f};
@@ -186,16 +237,18 @@ __device__ __forceinline__ void softmax_tile(float (&s)[NB][4], float (&o)[D / 8
   for (int nb = 0; nb < NB; ++nb)
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      const float pr = exp2f(s[nb][i] - m_use[i >> 1]);
+      const float pr = fast_exp2(fmaf(s[nb][i], scale_log2, -m_scaled[i >> 1]));
       s[nb][i] = pr;
       sum[i >> 1] += pr;
     }
 #pragma unroll
   for (int h = 0; h < 2; ++h) l[h] = l[h] * alpha[h] + sum[h];   // per-thread part; lanes are summed at the end
+  if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) {
 #pragma unroll
-  for (int db = 0; db < D / 8; ++db) {
-    o[db][0] *= alpha[0]; o[db][1] *= alpha[0];
-    o[db][2] *= alpha[1]; o[db][3] *= alpha[1];
+    for (int db = 0; db < D / 8; ++db) {
+      o[db][0] *= alpha[0]; o[db][1] *= alpha[0];
+      o[db][2] *= alpha[1]; o[db][3] *= alpha[1];
+    }
   }
 }
 
@@ -208,6 +261,14 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_mma_kernel(const Params 
   __nv_bfloat16* ks = qs + ROWS_PREFILL * S;                          // [2][BN][S]
   __nv_bfloat16* vs = ks + 2 * BN * S;                                // [2][BN][S]
   __shared__ long long rows[2][BN];
+  __shared__ __align__(8) uint64_t bars[2];
+  pdl_trigger();
+  if (threadIdx.x == 0) {
+    mbar_init(&bars[0], THREADS);
+    mbar_init(&bars[1], THREADS);
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  pdl_wait();
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int entry = p.work[2 * blockIdx.x], q_off = p.work[2 * blockIdx.x + 1];
@@ -235,9 +296,9 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_mma_kernel(const Params 
   const int n_tiles = (j_hi - j_lo + BN - 1) / BN;
   tile_rows<D>(rows[0], p, entry, kv_head, j_lo, j_hi, tid);
   tile_rows<D>(rows[1], p, entry, kv_head, j_lo + BN, j_hi, tid);
+  cp_async_commit();                      // the queries
   __syncthreads();
-  issue_tile<D>(ks, vs, rows[0], p, tid);
-  cp_async_commit();
+  issue_tile<D>(ks, vs, rows[0], p, &bars[0], tid);
 
   // ---- this thread's two rows
   int pos[2];
@@ -249,8 +310,12 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_mma_kernel(const Params 
   }
   // the last position any row of this warp has (its tiles beyond that are skipped)
   int warp_last = max(pos[0], pos[1]);
+  int warp_first = min(pos[0] < 0 ? 0x7fffffff : pos[0], pos[1] < 0 ? 0x7fffffff : pos[1]);   // over rows in use
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) warp_last = max(warp_last, __shfl_xor_sync(0xffffffffu, warp_last, o));
+  for (int o = 16; o > 0; o >>= 1) {
+    warp_last = max(warp_last, __shfl_xor_sync(0xffffffffu, warp_last, o));
+    warp_first = min(warp_first, __shfl_xor_sync(0xffffffffu, warp_first, o));
+  }
 
   float o_acc[D / 8][4];
 #pragma unroll
@@ -261,12 +326,16 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_mma_kernel(const Params 
 
   for (int t = 0; t < n_tiles; ++t) {
     const int buf = t & 1;
-    if (t + 1 < n_tiles) issue_tile<D>(ks + (buf ^ 1) * BN * S, vs + (buf ^ 1) * BN * S, rows[buf ^ 1], p, tid);
-    cp_async_commit();
+    if (t + 1 < n_tiles)
+      issue_tile<D>(ks + (buf ^ 1) * BN * S, vs + (buf ^ 1) * BN * S, rows[buf ^ 1], p, &bars[buf ^ 1], tid);
     // rows of tile t+2 go where those of tile t were (read when tile t was issued, an iteration ago)
     if (t + 2 < n_tiles) tile_rows<D>(rows[buf], p, entry, kv_head, j_lo + (t + 2) * BN, j_hi, tid);
-    cp_async_wait<1>();
-    __syncthreads();
+    if (t == 0) cp_async_wait<0>();
+    // every thread takes the same way out: all saw the tile, or the block stops (status word set)
+    if (!__syncthreads_and(wait_tile(&bars[buf], (t >> 1) & 1, p))) {
+      wait_tile(&bars[buf], (t >> 1) & 1, p);   // once more, bounded, for copies that may still be landing
+      return;
+    }
     const int key0 = j_lo + t * BN;
     if (key0 <= warp_last) {
       float s[BN / 8][4];
@@ -275,12 +344,16 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_mma_kernel(const Params 
 #pragma unroll
         for (int i = 0; i < 4; ++i) s[nb][i] = 0.f;
       qk_tile<D, BN / 8>(s, qs + warp * 16 * S, ks + buf * BN * S, lane);
-      softmax_tile<D, BN / 8>(s, o_acc, m, l, pos[0], pos[1], key0, j_hi, p.window, p.scale_log2, lane);
+      // the test is needed only where the tile reaches past the first row's position, past the end,
+      // or a window cuts into it
+      if (key0 + BN - 1 > warp_first || key0 + BN > j_hi || p.window > 0)
+        softmax_tile<D, BN / 8, true>(s, o_acc, m, l, pos[0], pos[1], key0, j_hi, p.window, p.scale_log2, lane);
+      else
+        softmax_tile<D, BN / 8, false>(s, o_acc, m, l, pos[0], pos[1], key0, j_hi, p.window, p.scale_log2, lane);
       pv_tile<D, BN / 8>(o_acc, s, vs + buf * BN * S, lane);
     }
     __syncthreads();
   }
-  cp_async_wait<0>();
 
   // ---- normalise and write
 #pragma unroll
@@ -313,6 +386,14 @@ __global__ void __launch_bounds__(THREADS) attn_decode_mma_kernel(const Params p
   __nv_bfloat16* vs = ks + DECODE_STAGES * BN * S;                    // [STAGES][BN][S]
   __shared__ long long rows[DECODE_STAGES][BN];
   __shared__ int is_last;
+  __shared__ __align__(8) uint64_t bars[DECODE_STAGES];
+  pdl_trigger();
+  if (threadIdx.x == 0) {
+#pragma unroll
+    for (int st = 0; st < DECODE_STAGES; ++st) mbar_init(&bars[st], THREADS);
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  pdl_wait();
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int entry = p.work[2 * blockIdx.x];
@@ -337,12 +418,11 @@ __global__ void __launch_bounds__(THREADS) attn_decode_mma_kernel(const Params p
   const int n_tiles = (j_hi - j_lo + BN - 1) / BN;
 #pragma unroll
   for (int st = 0; st < DECODE_STAGES; ++st) tile_rows<D>(rows[st], p, entry, kv_head, j_lo + st * BN, j_hi, tid);
+  cp_async_commit();                      // the queries
   __syncthreads();
 #pragma unroll
-  for (int st = 0; st < DECODE_STAGES - 1; ++st) {
-    if (st < n_tiles) issue_tile<D>(ks + st * BN * S, vs + st * BN * S, rows[st], p, tid);
-    cp_async_commit();
-  }
+  for (int st = 0; st < DECODE_STAGES - 1; ++st)
+    if (st < n_tiles) issue_tile<D>(ks + st * BN * S, vs + st * BN * S, rows[st], p, &bars[st], tid);
 
   // every row is the same token: position pos_q for rows that hold a head, -1 otherwise
   int pos[2];
@@ -362,14 +442,16 @@ __global__ void __launch_bounds__(THREADS) attn_decode_mma_kernel(const Params p
     const int nxt = t + DECODE_STAGES - 1;
     if (nxt < n_tiles) {
       const int nb = nxt % DECODE_STAGES;
-      issue_tile<D>(ks + nb * BN * S, vs + nb * BN * S, rows[nb], p, tid);
+      issue_tile<D>(ks + nb * BN * S, vs + nb * BN * S, rows[nb], p, &bars[nb], tid);
     }
-    cp_async_commit();
     // rows of tile t+STAGES go where those of tile t were (read when tile t was issued)
     if (t + DECODE_STAGES < n_tiles)
       tile_rows<D>(rows[t % DECODE_STAGES], p, entry, kv_head, j_lo + (t + DECODE_STAGES) * BN, j_hi, tid);
-    cp_async_wait<DECODE_STAGES - 1>();
-    __syncthreads();
+    if (t == 0) cp_async_wait<0>();
+    if (!__syncthreads_and(wait_tile(&bars[t % DECODE_STAGES], (t / DECODE_STAGES) & 1, p))) {
+      wait_tile(&bars[t % DECODE_STAGES], (t / DECODE_STAGES) & 1, p);
+      return;
+    }
     const int buf = t % DECODE_STAGES;
     const int key0 = j_lo + t * BN + warp * 16;      // this warp's 16 keys of the tile
     if (key0 < j_hi) {
@@ -379,16 +461,20 @@ __global__ void __launch_bounds__(THREADS) attn_decode_mma_kernel(const Params p
 #pragma unroll
         for (int i = 0; i < 4; ++i) s[nb][i] = 0.f;
       qk_tile<D, 2>(s, qs, ks + (buf * BN + warp * 16) * S, lane);
-      softmax_tile<D, 2>(s, o_acc, m, l, pos[0], pos[1], key0, j_hi, p.window, p.scale_log2, lane);
+      // keys before j_lo are never loaded, so only the tile that reaches past j_hi needs the test
+      if (key0 + 16 > j_hi)
+        softmax_tile<D, 2, true>(s, o_acc, m, l, pos[0], pos[1], key0, j_hi, 0, p.scale_log2, lane);
+      else
+        softmax_tile<D, 2, false>(s, o_acc, m, l, pos[0], pos[1], key0, j_hi, 0, p.scale_log2, lane);
       pv_tile<D, 2>(o_acc, s, vs + (buf * BN + warp * 16) * S, lane);
     }
     __syncthreads();
   }
-  cp_async_wait<0>();
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
     l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
+    m[h] *= p.scale_log2;   // from here on the maxima are exponents of two (warps and splits are merged with exp2)
   }
 
   // ---- merge the four warps (each saw a quarter of the keys) through shared memory
@@ -398,6 +484,7 @@ __global__ void __launch_bounds__(THREADS) attn_decode_mma_kernel(const Params p
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     const int r = (lane >> 2) + h * 8;
+    if (r >= HPT) continue;               // rows without a head are not merged
     if ((lane & 3) == 0) { mm[warp * 16 + r] = m[h]; ml[warp * 16 + r] = l[h]; }
 #pragma unroll
     for (int db = 0; db < D / 8; ++db) {
@@ -483,8 +570,7 @@ int launch(const Params& p, int n_work, bool split, cudaStream_t stream) {
       ready = true;
     }
     dim3 grid(n_work, p.n_kv_heads * p.n_head_groups);
-    attn_prefill_mma_kernel<D><<<grid, THREADS, smem, stream>>>(p);
-    return jv_check_launch();
+    return jv_launch(attn_prefill_mma_kernel<D>, grid, dim3(THREADS), smem, stream, p);
   }
   static bool ready = false;
   const size_t smem = decode_smem<D>();
@@ -494,8 +580,7 @@ int launch(const Params& p, int n_work, bool split, cudaStream_t stream) {
     ready = true;
   }
   dim3 grid(n_work, p.n_kv_heads * p.n_head_groups, p.n_splits);
-  attn_decode_mma_kernel<D><<<grid, THREADS, smem, stream>>>(p);
-  return jv_check_launch();
+  return jv_launch(attn_decode_mma_kernel<D>, grid, dim3(THREADS), smem, stream, p);
 }
 }  // namespace
 

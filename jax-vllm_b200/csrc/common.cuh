@@ -69,6 +69,41 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
   return t;
 }
 
+// Programmatic dependent launch.  A kernel launched through jv_launch may be made resident while the
+// kernel before it in the stream is still finishing; whatever it does before `pdl_wait()` (index
+// arithmetic, prefetching weights that no kernel writes) overlaps that kernel's tail, and everything
+// after `pdl_wait()` sees all of its results.  `pdl_trigger()` says that the next kernel may be made
+// resident; kernels call it first thing.  No kernel reads activations or writes anything before its
+// `pdl_wait()`.  JAX_VLLM_B200_PDL=0 in the environment launches plainly instead.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+#include <cstdlib>
+static inline bool jv_pdl_enabled() {
+  static int state = -1;
+  if (state < 0) {
+    const char* v = std::getenv("JAX_VLLM_B200_PDL");
+    state = (v != nullptr && v[0] == '0') ? 0 : 1;
+  }
+  return state == 1;
+}
+
+template <typename... KArgs, typename... Args>
+static inline int jv_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                            Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = jv_pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...) == cudaSuccess ? JV_OK : JV_ERR_LAUNCH;
+}
+
 static inline int jv_check_launch() {
   return cudaGetLastError() == cudaSuccess ? JV_OK : JV_ERR_LAUNCH;
 }

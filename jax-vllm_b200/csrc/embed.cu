@@ -6,6 +6,8 @@ template <typename T>
 __global__ void embed_gather_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                                     float* __restrict__ out, int hidden, int vocab,
                                     int* __restrict__ status) {
+  pdl_trigger();
+  pdl_wait();
   const int n = blockIdx.x;
   const int id = ids[n];
   float* dst = out + (size_t)n * hidden;
@@ -23,7 +25,7 @@ JV_EXPORT int jv_embed_gather(const void* table, int dtype, const int* ids, floa
                               int hidden, int vocab, int* status, cudaStream_t stream) {
   if (n == 0) return JV_OK;
   const int threads = hidden >= 1024 ? 256 : 128;
-  JV_DISPATCH_DTYPE(dtype, T, (embed_gather_kernel<T><<<n, threads, 0, stream>>>(
-                                  (const T*)table, ids, out, hidden, vocab, status)));
-  return jv_check_launch();
+  JV_DISPATCH_DTYPE(dtype, T, return jv_launch(embed_gather_kernel<T>, dim3(n), dim3(threads), 0, stream,
+                                                (const T*)table, ids, out, hidden, vocab, status));
+  return JV_ERR_UNSUPPORTED;
 }

@@ -96,8 +96,10 @@ __global__ void __launch_bounds__(WARPS * 32, CTAS_PER_SM) skinny_kernel(const _
     }
     asm volatile("cp.async.commit_group;\n" ::);
   };
+  pdl_trigger();
 #pragma unroll
-  for (int i = 0; i < STAGES - 1; ++i) issue();
+  for (int i = 0; i < STAGES - 1; ++i) issue();   // weights: nobody writes them, so they are requested
+  pdl_wait();                                     // before the kernels that produce x have finished
 
   float acc[NB][4];
 #pragma unroll
@@ -176,11 +178,12 @@ int launch(const void* X, int ldx, const void* W, int ldw, void* Y, int ldy, int
     ready = true;
   }
   if (M <= 8)
-    skinny_kernel<1, TOut><<<blocks, WARPS * 32, smem_bytes<1>(), stream>>>(x, ldx, w, ldw, y, ldy, M, N, K, n_strips);
-  else if (M <= 16)
-    skinny_kernel<2, TOut><<<blocks, WARPS * 32, smem_bytes<2>(), stream>>>(x, ldx, w, ldw, y, ldy, M, N, K, n_strips);
-  else return JV_ERR_UNSUPPORTED;
-  return jv_check_launch();
+    return jv_launch(skinny_kernel<1, TOut>, dim3(blocks), dim3(WARPS * 32), smem_bytes<1>(), stream, x, ldx, w, ldw, y,
+                     ldy, M, N, K, n_strips);
+  if (M <= 16)
+    return jv_launch(skinny_kernel<2, TOut>, dim3(blocks), dim3(WARPS * 32), smem_bytes<2>(), stream, x, ldx, w, ldw, y,
+                     ldy, M, N, K, n_strips);
+  return JV_ERR_UNSUPPORTED;
 }
 }  // namespace
 

@@ -16,6 +16,8 @@ __global__ void rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__ del
                                TY* __restrict__ y, int hidden, float eps, int n_rows_total,
                                int* __restrict__ status) {
   __shared__ float scratch[33];
+  pdl_trigger();
+  pdl_wait();
   const int i = blockIdx.x;
   int r = i;
   if (rows != nullptr) {
@@ -80,6 +82,8 @@ __global__ void rmsnorm_vec_kernel(float* __restrict__ h, const TD* __restrict__
                                    TY* __restrict__ y, int hidden, float eps, int n_rows_total,
                                    int* __restrict__ status) {
   __shared__ float scratch[33];
+  pdl_trigger();
+  pdl_wait();
   const int i = blockIdx.x;
   int r = i;
   if (rows != nullptr) {
@@ -143,21 +147,23 @@ JV_EXPORT int jv_rmsnorm(float* h, const void* delta, int delta_dtype, const int
     int vthreads = ((vecs + iters - 1) / iters + 31) / 32 * 32;
     if (vthreads > 1024) vthreads = 1024;
     JV_DISPATCH_DTYPE(out_dtype, TY, JV_DISPATCH_DTYPE(weight_dtype, TW, JV_DISPATCH_DTYPE(delta_dtype, TD,
-        (rmsnorm_vec_kernel<TD, TW, TY><<<n_out, vthreads, 0, stream>>>(
-            h, (const TD*)delta, rows, (const TW*)weight, (TY*)y, hidden, eps, n_total, status)))));
-    return jv_check_launch();
+        return jv_launch(rmsnorm_vec_kernel<TD, TW, TY>, dim3(n_out), dim3(vthreads), 0, stream,
+                         h, (const TD*)delta, rows, (const TW*)weight, (TY*)y, hidden, eps, n_total, status))));
+    return JV_ERR_UNSUPPORTED;
   }
   int threads = 32;
   while (threads < 512 && threads * 4 < hidden) threads *= 2;
   JV_DISPATCH_DTYPE(out_dtype, TY, JV_DISPATCH_DTYPE(weight_dtype, TW, JV_DISPATCH_DTYPE(delta_dtype, TD,
-      (rmsnorm_kernel<TD, TW, TY><<<n_out, threads, 0, stream>>>(
-          h, (const TD*)delta, rows, (const TW*)weight, (TY*)y, hidden, eps, n_total, status)))));
-  return jv_check_launch();
+      return jv_launch(rmsnorm_kernel<TD, TW, TY>, dim3(n_out), dim3(threads), 0, stream,
+                       h, (const TD*)delta, rows, (const TW*)weight, (TY*)y, hidden, eps, n_total, status))));
+  return JV_ERR_UNSUPPORTED;
 }
 
 // Adds delta into the 32-bit stream without a norm: h[r, :] += delta[r, :].
 template <typename TD>
 __global__ void residual_add_kernel(float* __restrict__ h, const TD* __restrict__ delta, size_t n) {
+  pdl_trigger();
+  pdl_wait();
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   for (; i < n; i += stride) h[i] += to_f32(delta[i]);
@@ -168,7 +174,7 @@ JV_EXPORT int jv_residual_add(float* h, const void* delta, int delta_dtype, long
   if (n == 0) return JV_OK;
   long long blocks = (n + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
-  JV_DISPATCH_DTYPE(delta_dtype, TD, (residual_add_kernel<TD><<<(int)blocks, 256, 0, stream>>>(
-                                         h, (const TD*)delta, (size_t)n)));
-  return jv_check_launch();
+  JV_DISPATCH_DTYPE(delta_dtype, TD, return jv_launch(residual_add_kernel<TD>, dim3((int)blocks), dim3(256), 0, stream,
+                                                      h, (const TD*)delta, (size_t)n));
+  return JV_ERR_UNSUPPORTED;
 }

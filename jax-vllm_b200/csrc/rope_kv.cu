@@ -23,6 +23,8 @@ __global__ void rope_kv_kernel(T* __restrict__ qkv, int row_stride, const int* _
                                int n_kv_heads, int head_dim, int page_size, int num_pages,
                                int heads_to_do, int* __restrict__ status) {
   extern __shared__ float smem[];
+  pdl_trigger();
+  pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int warps = blockDim.x >> 5;
   const int n = blockIdx.x;
@@ -98,6 +100,8 @@ __global__ void rope_kv_fast_kernel(T* __restrict__ qkv, int row_stride, const i
                                     int n_kv_heads, int page_size, int num_pages, int heads_to_do,
                                     int* __restrict__ status) {
   constexpr int HALF = 32 * E, D = 2 * HALF;
+  pdl_trigger();
+  pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n = blockIdx.x;
   const int head = blockIdx.y * (blockDim.x >> 5) + warp;
@@ -177,20 +181,20 @@ JV_EXPORT int jv_rope_kv(void* qkv, int dtype, int row_stride, const int* positi
     const float* freq = rot_dim ? inv_freq : nullptr;
 #define JV_ROPE_FAST(EE)                                                                                   \
     JV_DISPATCH_DTYPE(dtype, T, JV_DISPATCH_DTYPE(w_dtype, TW,                                              \
-        (rope_kv_fast_kernel<T, TW, EE><<<grid, warps * 32, 0, stream>>>(                                   \
+        return jv_launch(rope_kv_fast_kernel<T, TW, EE>, grid, dim3(warps * 32), 0, stream,                \
             (T*)qkv, row_stride, positions, token_entry, block_table, table_width, freq, (const TW*)q_norm_w, \
             (const TW*)k_norm_w, eps, (T*)k_cache, (T*)v_cache, n_q_heads, n_kv_heads, page_size, num_pages, \
-            heads_to_do, status))))
+            heads_to_do, status)))
     if (E == 1) JV_ROPE_FAST(1); else if (E == 2) JV_ROPE_FAST(2); else JV_ROPE_FAST(4);
 #undef JV_ROPE_FAST
-    return jv_check_launch();
+    return JV_ERR_UNSUPPORTED;
   }
   const size_t smem = (size_t)warps * head_dim * sizeof(float);
   if (smem > 48 * 1024) return JV_ERR_UNSUPPORTED;
   JV_DISPATCH_DTYPE(dtype, T, JV_DISPATCH_DTYPE(w_dtype, TW,
-      (rope_kv_kernel<T, TW><<<grid, warps * 32, smem, stream>>>(
+      return jv_launch(rope_kv_kernel<T, TW>, grid, dim3(warps * 32), smem, stream,
           (T*)qkv, row_stride, positions, token_entry, block_table, table_width, inv_freq, rot_dim,
           (const TW*)q_norm_w, (const TW*)k_norm_w, eps, (T*)k_cache, (T*)v_cache, n_q_heads,
-          n_kv_heads, head_dim, page_size, num_pages, heads_to_do, status))));
-  return jv_check_launch();
+          n_kv_heads, head_dim, page_size, num_pages, heads_to_do, status)));
+  return JV_ERR_UNSUPPORTED;
 }

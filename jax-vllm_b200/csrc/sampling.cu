@@ -49,6 +49,8 @@ __global__ void sample_partial_kernel(const float* __restrict__ logits, int voca
                                       int* __restrict__ part_i) {
   __shared__ float sv[32];
   __shared__ int si[32];
+  pdl_trigger();
+  pdl_wait();
   const int row = blockIdx.y;
   const float* lr = logits + (size_t)row * vocab;
   const float temp = temperature[row];
@@ -72,6 +74,8 @@ __global__ void sample_partial_kernel(const float* __restrict__ logits, int voca
 // Stage 2: one warp per row over the chunk winners.
 __global__ void sample_final_kernel(const float* __restrict__ part_v, const int* __restrict__ part_i, int n_chunks,
                                     int* __restrict__ out) {
+  pdl_trigger();
+  pdl_wait();
   const int row = blockIdx.x;
   float bv = -INFINITY;
   int bi = 0x7fffffff;
@@ -96,9 +100,9 @@ JV_EXPORT int jv_sample(const float* logits, int rows, int vocab, const float* t
   if (rows == 0) return JV_OK;
   const int chunks = jv_sample_chunks(vocab);
   const int chunk = (vocab + chunks - 1) / chunks;
-  sample_partial_kernel<<<dim3(chunks, rows), 256, 0, stream>>>(logits, vocab, chunk, temperature, seeds, counters,
-                                                                part_v, part_i);
-  if (jv_check_launch() != JV_OK) return JV_ERR_LAUNCH;
-  sample_final_kernel<<<rows, 32, 0, stream>>>(part_v, part_i, chunks, out);
-  return jv_check_launch();
+  if (jv_launch(sample_partial_kernel, dim3(chunks, rows), dim3(256), 0, stream, logits, vocab, chunk, temperature,
+                seeds, counters, part_v, part_i) != JV_OK)
+    return JV_ERR_LAUNCH;
+  return jv_launch(sample_final_kernel, dim3(rows), dim3(32), 0, stream, (const float*)part_v, (const int*)part_i, chunks,
+                   out);
 }
