@@ -98,7 +98,7 @@ def test_gemm_simt(ops, dtype, m, n, k):
 
 
 @pytest.mark.parametrize("m", [1, 3, 8, 9, 16])
-@pytest.mark.parametrize("n,k", [(70, 96), (4096, 4096), (1000, 1536), (24, 8), (151, 4104), (24576, 512)])
+@pytest.mark.parametrize("n,k", [(70, 96), (4096, 4096), (1000, 1536), (24, 8), (151, 4104), (24576, 512), (4096, 12288), (50, 2056)])
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
 def test_linear_skinny(ops, m, n, k, out_dtype):
     g = torch.Generator().manual_seed(m * 1000 + n)
