@@ -158,15 +158,19 @@ def residual_add(h: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
 
 
 # ----------------------------------------------------------------------- activation
-def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
-    """silu(gate) * up for a packed [n, 2*inter] tensor (gate columns first)."""
+def swiglu(gate_up: torch.Tensor, block: int | None = None) -> torch.Tensor:
+    """silu(gate) * up for a packed [n, 2*inter] tensor: blocks of `block` gate columns, each followed
+    by the up columns of the same indices (default: all gate columns first)."""
     _cuda(gate_up, "gate_up")
     n, two_i = gate_up.shape
     if two_i % 2:
         raise KernelError("packed gate|up needs an even number of columns")
+    block = two_i // 2 if block is None else int(block)
+    if block < 1 or (two_i // 2) % block:
+        raise KernelError(f"gate|up block {block} does not divide {two_i // 2} columns")
     act = torch.empty((n, two_i // 2), dtype=gate_up.dtype, device=gate_up.device)
-    f = _fn("activation", "jv_swiglu", [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
-    _check(f(gate_up.data_ptr(), act.data_ptr(), _code(gate_up, "gate_up"), n, two_i // 2, _stream()), "swiglu")
+    f = _fn("activation", "jv_swiglu", [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    _check(f(gate_up.data_ptr(), act.data_ptr(), _code(gate_up, "gate_up"), n, two_i // 2, block, _stream()), "swiglu")
     return act
 
 
@@ -332,6 +336,31 @@ def linear_skinny(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype)
                                                   c_int, c_void_p])
     _check(f(x.data_ptr(), x.stride(0), weight.data_ptr(), weight.stride(0), y.data_ptr(), _code(y, "out"), y.stride(0),
              m, n, k, _stream()), "linear_skinny")
+    return y
+
+
+GEMM_EPILOGUES = {"bf16": 0, "f32": 1, "swiglu": 2}
+
+
+def gemm_tcgen05(x: torch.Tensor, weight: torch.Tensor, epilogue: str = "bf16") -> torch.Tensor:
+    """x [M, K] times weight [N, K] transposed on tcgen05 tensor cores with the accumulator in
+    tensor memory (csrc/gemm_tcgen05.cu).  epilogue "bf16" / "f32": the product in that type;
+    "swiglu": silu(gate) * up as [M, N/2] bfloat16, for a weight whose every 256 rows are 128 gate rows
+    followed by the 128 up rows of the same indices."""
+    _cuda(x, "x", torch.bfloat16, contiguous=False); _cuda(weight, "weight", torch.bfloat16, contiguous=False)
+    if x.dim() != 2 or weight.dim() != 2 or x.shape[1] != weight.shape[1] or x.stride(1) != 1 or weight.stride(1) != 1:
+        raise KernelError(f"gemm shapes {tuple(x.shape)} x {tuple(weight.shape)}^T do not fit")
+    m, k = x.shape
+    n = weight.shape[0]
+    code = GEMM_EPILOGUES[epilogue]
+    if epilogue == "swiglu":
+        y = torch.empty((m, n // 2), dtype=torch.bfloat16, device=x.device)
+    else:
+        y = torch.empty((m, n), dtype=torch.float32 if epilogue == "f32" else torch.bfloat16, device=x.device)
+    f = _fn("gemm_tcgen05", "jv_gemm_tcgen05", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
+                                                c_int, c_void_p, c_void_p])
+    _check(f(x.data_ptr(), x.stride(0), weight.data_ptr(), weight.stride(0), y.data_ptr(), y.stride(0), m, n, k, code,
+             status_word(x.device).data_ptr(), _stream()), "gemm_tcgen05")
     return y
 
 

@@ -1,6 +1,9 @@
 """Gated feed-forward: down(act(gate(x)) * up(x)), act = SiLU, no bias
-(jllm/model/common.py:75-76).  Gate and up matrices are stored packed, gate rows first,
-so that one product reads the input once."""
+(jllm/model/common.py:75-76).  Gate and up matrices are stored packed so that one product reads
+the input once: in bfloat16 with an intermediate size that is a multiple of 128, as blocks of 128
+gate rows followed by the 128 up rows of the same indices, which lets the tcgen05 product of prompt
+steps apply the gate in its epilogue (the [tokens, 2*intermediate] product never reaches memory);
+otherwise all gate rows, then all up rows."""
 
 from __future__ import annotations
 
@@ -13,13 +16,14 @@ from .registry import register_feed_forward
 
 class GatedMLP(Part):
     kernels = ("activation", "gemm_simt")
+    BLOCK = 128          # gate/up interleaving of the fused product (a tile of it is 256 columns wide)
 
     def __init__(self, spec, prefix, ctx):
         if spec.activation != "silu":
             raise ValueError(f"gated feed-forward: activation {spec.activation!r} is not built (silu is)")
         self.spec, self.ctx = spec, ctx
         self.prefix = f"{prefix}.{spec.prefix}" if spec.prefix else prefix
-        self.w_gate_up = self.w_down = None
+        self.w_gate_up = self.w_down = self.block = None
 
     def tensor_specs(self):
         p, s = self.prefix, self.spec
@@ -33,12 +37,23 @@ class GatedMLP(Part):
         u = self.compute_weight(tensors[f"{p}.up_proj.weight"], self.ctx)
         if g.dtype != u.dtype:
             g, u = g.float(), u.float()
-        self.w_gate_up = torch.cat([g, u], dim=0).contiguous()
+        inter, hidden = g.shape
+        self.block = None
+        if self.ctx.dtype == torch.bfloat16 and g.dtype == torch.bfloat16 and inter % self.BLOCK == 0 and hidden % 8 == 0:
+            self.block = self.BLOCK
+            self.kernels = ("activation", "gemm_simt", "gemm_tcgen05", "linear_skinny")
+            self.w_gate_up = torch.stack([g.reshape(-1, self.BLOCK, hidden), u.reshape(-1, self.BLOCK, hidden)],
+                                         dim=1).reshape(2 * inter, hidden).contiguous()
+        else:
+            self.w_gate_up = torch.cat([g, u], dim=0).contiguous()
         self.w_down = self.compute_weight(tensors[f"{p}.down_proj.weight"], self.ctx).contiguous()
 
     def forward(self, x, step):
         dt = self.ctx.dtype
-        act = ops.swiglu(ops.linear(x, self.w_gate_up, dt))
+        if self.block is not None and x.shape[0] > ops.SKINNY_MAX_ROWS:
+            act = ops.gemm_tcgen05(x, self.w_gate_up, "swiglu")
+        else:
+            act = ops.swiglu(ops.linear(x, self.w_gate_up, dt), self.block)
         return ops.linear(act, self.w_down, dt)
 
 

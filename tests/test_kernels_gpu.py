@@ -77,6 +77,11 @@ def test_residual_add_and_swiglu(ops, dtype):
     act = ops.swiglu(gu)
     gate, up = gu.float()[:, :56], gu.float()[:, 56:]
     torch.testing.assert_close(act.float(), torch.nn.functional.silu(gate) * up, **tol(dtype))
+    # blocks of 8 gate columns, each followed by its 8 up columns
+    blocked = torch.stack([gu[:, :56].reshape(23, 7, 8), gu[:, 56:].reshape(23, 7, 8)], dim=2).reshape(23, 112).contiguous()
+    torch.testing.assert_close(ops.swiglu(blocked, 8).float(), act.float(), atol=0, rtol=0)
+    with pytest.raises(ops.KernelError):
+        ops.swiglu(gu, 5)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -118,6 +123,37 @@ def test_linear_skinny(ops, m, n, k, out_dtype):
     wide = torch.randn(m, k + 16, generator=g).to(torch.bfloat16).to(DEV)
     y2 = ops.linear_skinny(wide[:, 8:8 + k], w, torch.float32)
     torch.testing.assert_close(y2.double(), wide[:, 8:8 + k].double() @ w.double().T, atol=1e-4, rtol=1e-4)
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (128, 256, 256), (256, 512, 128), (130, 300, 72), (5, 256, 64),
+                                   (2048, 1024, 4096), (300, 6144, 1024), (1000, 264, 4104)])
+@pytest.mark.parametrize("epilogue", ["bf16", "f32"])
+def test_gemm_tcgen05(ops, m, n, k, epilogue):
+    g = torch.Generator().manual_seed(m + n + k)
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(n, k, generator=g) / k ** 0.5).to(torch.bfloat16).to(DEV)
+    y = ops.gemm_tcgen05(x, w, epilogue)
+    ops.check_status()
+    want = x.double() @ w.double().T
+    if epilogue == "f32":
+        assert y.dtype == torch.float32
+        torch.testing.assert_close(y.double(), want, atol=2e-4, rtol=2e-4)
+    else:
+        torch.testing.assert_close(y.double(), want, atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("m,inter,k", [(128, 128, 64), (200, 256, 128), (2048, 1024, 512), (7, 384, 72)])
+def test_gemm_tcgen05_gated_epilogue(ops, m, inter, k):
+    g = torch.Generator().manual_seed(m + inter)
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16).to(DEV)
+    gate = (torch.randn(inter, k, generator=g) / k ** 0.5).to(torch.bfloat16)
+    up = (torch.randn(inter, k, generator=g) / k ** 0.5).to(torch.bfloat16)
+    packed = torch.stack([gate.reshape(-1, 128, k), up.reshape(-1, 128, k)], dim=1).reshape(2 * inter, k).to(DEV)
+    y = ops.gemm_tcgen05(x, packed, "swiglu")
+    ops.check_status()
+    xd = x.double().cpu()
+    want = torch.nn.functional.silu(xd @ gate.double().T) * (xd @ up.double().T)
+    torch.testing.assert_close(y.double().cpu(), want, atol=2e-2, rtol=2e-2)
 
 
 def test_linear_dispatch(ops):

@@ -135,6 +135,34 @@ def test_feed_forward_and_block_alone():
         parts.FEED_FORWARDS["gated_mlp"](config.GatedMLPSpec(40, 56, activation="gelu"), "L", ctx)
 
 
+@pytest.mark.parametrize("rows", [3, 16, 17, 150])
+def test_feed_forward_bf16_with_the_gate_in_the_product(rows):
+    """An intermediate size that is a multiple of 128 takes the interleaved gate|up weight: prompt steps apply
+    the gate in the epilogue of the tcgen05 product, small batches in the separate kernel; both equal plain."""
+    j, cache, config, engine, parts, weights = pkg()
+    ctx = parts.BuildContext(torch.bfloat16, DEV)
+    ff = parts.FEED_FORWARDS["gated_mlp"](config.GatedMLPSpec(72, 384), "L", ctx)
+    g = torch.Generator().manual_seed(8)
+    w = {n: (torch.randn(ts.shape, generator=g) * 0.2).to(torch.bfloat16) for n, ts in ff.tensor_specs().items()}
+    ff.bind({k: v.to(DEV) for k, v in w.items()})
+    assert ff.block == 128
+    x = torch.randn(rows, 72, generator=g).to(torch.bfloat16)
+    got = ff.forward(x.to(DEV), None).float().cpu()
+    # the plain formula with the engine's rounding points: the activations are bfloat16 where they reach
+    # memory (gate|up only on the small-batch path, silu(g) * u on both), sums are 32-bit or better
+    rnd = lambda t: t.to(torch.bfloat16).double()
+    wd = {k: v.double() for k, v in w.items()}
+    gate, up = x.double() @ wd["L.mlp.gate_proj.weight"].T, x.double() @ wd["L.mlp.up_proj.weight"].T
+    if rows <= 16:
+        gate, up = rnd(gate), rnd(up)
+    want = (rnd(torch.nn.functional.silu(gate) * up) @ wd["L.mlp.down_proj.weight"].T).float()
+    torch.testing.assert_close(got, want, atol=2e-2, rtol=1e-2)
+    loose = plain.swiglu(x.float(), {k: v.float() for k, v in w.items()}, "L.mlp")
+    assert (got - loose).abs().max().item() <= 0.02 * loose.abs().max().item()      # and near the unrounded formula
+    from jax_vllm_b200 import ops
+    ops.check_status()
+
+
 def test_kinds_are_looked_up_in_the_registries():
     j, cache, config, engine, parts, weights = pkg()
     spec = spec_b()
