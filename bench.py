@@ -242,7 +242,8 @@ def micro(spec: str, reps: int) -> int:
     gemm:<N>x<K>:<M>:<impl>  the prompt product, impl = tcgen05 | tcgen05_swiglu | library (cuBLAS)
     linear:<N>x<K>:<M>   the decode product of M rows with an [N, K] weight (several weights in turn)
     attn_decode:<B>:<CTX>   split decode attention of B requests with CTX cached tokens (8B head layout)
-    attn_prefill:<T>     prompt attention of one request of T tokens (8B head layout)"""
+    attn_prefill:<T>     prompt attention of one request of T tokens (8B head layout), mma.sync kernel
+    attn_prefill_tcgen05:<T>   the same with the tcgen05 kernel"""
     import torch
     from jax_vllm_b200 import ops
     kind, *rest = spec.split(":")
@@ -304,6 +305,10 @@ def micro(spec: str, reps: int) -> int:
             work = torch.tensor([[e, 0] for e in range(b)], dtype=torch.int32, device=dev)
             run = lambda i: ops.attn_mma(q, hq * d, out, *common, work, b, hq, hkv, d, 0, d ** -0.5, split_size=256,
                                          n_splits=-(-max(total) // 256))
+        elif kind == "attn_prefill_tcgen05":
+            tpt = ops.attn_tcgen05_tokens_per_tile(hq, hkv)
+            work = torch.tensor([[0, t] for t in range(0, q_lens[0], tpt)], dtype=torch.int32, device=dev)
+            run = lambda i: ops.attn_tcgen05(q, hq * d, out, *common, work, work.shape[0], hq, hkv, d, d ** -0.5)
         else:
             tpt = ops.attn_mma_tokens_per_tile(hq, hkv)
             work = torch.tensor([[0, t] for t in range(0, q_lens[0], tpt)], dtype=torch.int32, device=dev)

@@ -1,0 +1,493 @@
+// Paged causal attention of prompt portions on the 5th-generation tensor cores, for head size 128:
+// scores and output accumulate in tensor memory (TMEM), queries, keys and values come in by TMA in the
+// 128-byte-swizzle layout that tcgen05.mma reads.
+//
+// A block handles 128 rows = (token, query head) pairs of ONE kv head (row r -> token r / HPT, head
+// r % HPT, HPT = query heads per kv head, a power of two up to 16), against 128-key tiles:
+//   warp 0   producer: reads the block table, issues the TMA loads of the query tile (once) and of the key
+//            and value tiles (one 4-D box per page and half of the head: [page slots, 64] elements);
+//   warp 1   one thread issues S = Q K^T (8 x tcgen05.mma 128x128x16 over the head) into one of two score
+//            buffers in TMEM, and O += P V (8 x mma over the keys; V is the MN-major operand), after the
+//            softmax warps have written P (bfloat16) to shared memory;
+//   warps 2..5  softmax, one row per thread: read the scores from TMEM, mask, running (max, sum) in 32-bit,
+//            exp2, write P; when a row's maximum has moved, rescale O in TMEM first.  At the end O / sum is
+//            written out.
+// The score buffer of tile j+1 is filled while the softmax of tile j runs.  Every mbarrier wait is bounded
+// by a clock deadline and reports to the status word instead of spinning.
+//
+// Restrictions (the caller falls back to the mma.sync kernel otherwise): bfloat16, head size 128, no
+// window, HPT in {1, 2, 4, 8, 16}, page size a power of two from 8 to 128.
+#include "common.cuh"
+
+#include <cuda.h>
+#include <cudaTypedefs.h>
+#include <math.h>
+
+namespace {
+
+constexpr int D = 128, ROWS = 128, BN = 128;
+constexpr int TILE_BYTES = 128 * 128 * 2;       // a 128 x 128 bfloat16 tile: two halves of [128 rows][128 bytes]
+constexpr int HALF_BYTES = 128 * 128;            // one half: 128 rows of 128 bytes
+constexpr int KV_STAGES = 2;
+constexpr int THREADS = 192;
+constexpr int TMEM_COLS = 512;                   // S0: [0,128)  S1: [128,256)  O: [256,384)
+constexpr long long WAIT_CYCLES = 2000000000LL;
+constexpr float LOG2E = 1.4426950408889634f;
+
+struct Params {
+  __nv_bfloat16* out; int out_stride;
+  const int* block_table; int table_width;
+  const int* cu_seqlens; const int* start_pos; const int* work;
+  int n_q_heads, n_kv_heads, page_size, num_pages, hpt, tokens_per_tile;
+  float scale_log2;
+  int* status;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, int bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, int parity) {
+  const long long deadline = clock64() + WAIT_CYCLES;
+  while (true) {
+    uint32_t done;
+    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+                 : "=r"(done) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    if (done) return true;
+    if (clock64() > deadline) return false;
+  }
+}
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int x, int y, int z, uint64_t* bar) {
+  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];\n"
+               ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, int x, int y, int z, int w, uint64_t* bar) {
+  asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];\n"
+               ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(z), "r"(w), "r"(smem_u32(bar)) : "memory");
+}
+
+// Descriptor of a K-major operand tile (rows of 128 bytes along k, 8-row groups 1024 bytes apart, 128-byte swizzle).
+__device__ __forceinline__ uint64_t desc_k_major(uint32_t addr) {
+  return (uint64_t)((addr & 0x3FFFF) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
+         ((uint64_t)2 << 61);
+}
+// Descriptor of an MN-major operand tile: rows of 128 bytes run along n (64 elements), consecutive rows are
+// consecutive k, 8 rows = 1024 bytes (stride byte offset); the next 64 n are HALF_BYTES further (leading byte offset).
+__device__ __forceinline__ uint64_t desc_mn_major(uint32_t addr) {
+  return (uint64_t)((addr & 0x3FFFF) >> 4) | ((uint64_t)(HALF_BYTES >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) |
+         ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// bfloat16 x bfloat16 -> float, M = 128, N = 128; B K-major (S = Q K^T) or MN-major (O = P V).
+constexpr uint32_t IDESC_QK = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(128 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+constexpr uint32_t IDESC_PV = IDESC_QK | (1u << 16);
+
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+               "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+               ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+// The same without waiting: several loads can be in flight; tmem_ld_wait() before the values are used.
+__device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n"
+      ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
+        "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
+        "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+        "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])),
+        "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
+        "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
+        "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])),
+        "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+      : "memory");
+  asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
+#define TC_FENCE_BEFORE() asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory")
+#define TC_FENCE_AFTER() asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory")
+#define PROXY_FENCE() asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory")
+
+struct Shared {
+  uint64_t q_full, k_full[KV_STAGES], k_empty[KV_STAGES], v_full[KV_STAGES], v_empty[KV_STAGES];
+  uint64_t s_full[2], p_full[2], o_done[2];
+  uint32_t tmem_base;
+};
+
+__global__ void __launch_bounds__(THREADS, 1) attn_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map,
+                                                                  const __grid_constant__ CUtensorMap k_map,
+                                                                  const __grid_constant__ CUtensorMap v_map,
+                                                                  const Params p) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  unsigned char* q_s = base;                                   // [2 halves of d][128 rows][128 B]
+  unsigned char* k_s = q_s + TILE_BYTES;                       // [stages][2 halves of d][128 keys][128 B]
+  unsigned char* v_s = k_s + KV_STAGES * TILE_BYTES;           // [stages][2 halves of d][128 keys][128 B]
+  unsigned char* p_s = v_s + KV_STAGES * TILE_BYTES;           // [2 buffers][2 halves of keys][128 rows][128 B]
+  Shared* sh = reinterpret_cast<Shared*>(p_s + 2 * TILE_BYTES);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  // longest blocks first: the work list is in ascending order of the tile's first token
+  const int item = gridDim.x - 1 - blockIdx.x;
+  const int entry = p.work[2 * item], q_off = p.work[2 * item + 1];
+  const int kv_head = blockIdx.y;
+  const int G = p.n_q_heads / p.n_kv_heads, HPT = p.hpt;
+  const int q_begin = p.cu_seqlens[entry];
+  const int q_len = p.cu_seqlens[entry + 1] - q_begin;
+  const int ctx = p.start_pos[entry];
+  const int tokens_here = min(p.tokens_per_tile, q_len - q_off);
+  const int pos_first = ctx + q_off;
+  const int j_hi = pos_first + tokens_here;          // keys [0, j_hi) are visible to the last row
+  const int n_tiles = (j_hi + BN - 1) / BN;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&sh->q_full, 1);
+    for (int s = 0; s < KV_STAGES; ++s) {
+      mbar_init(&sh->k_full[s], 1); mbar_init(&sh->k_empty[s], 1);
+      mbar_init(&sh->v_full[s], 1); mbar_init(&sh->v_empty[s], 1);
+    }
+    mbar_init(&sh->s_full[0], 1); mbar_init(&sh->s_full[1], 1);
+    mbar_init(&sh->p_full[0], 128); mbar_init(&sh->p_full[1], 128);
+    mbar_init(&sh->o_done[0], 1); mbar_init(&sh->o_done[1], 1);
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  // value tiles start as zeros: a probability of exactly zero must never meet a NaN left in shared memory
+  for (int i = threadIdx.x; i < KV_STAGES * TILE_BYTES / 16; i += THREADS) reinterpret_cast<uint4*>(v_s)[i] = make_uint4(0, 0, 0, 0);
+  PROXY_FENCE();
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&sh->tmem_base)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+  TC_FENCE_BEFORE();
+  __syncthreads();
+  TC_FENCE_AFTER();
+  const uint32_t tmem = sh->tmem_base;
+  const uint32_t tmem_o = tmem + 256;
+
+  if (tokens_here > 0) {
+    if (warp == 0) {
+      // ---------------------------------------------------------------- producer
+      if (lane == 0) {
+        mbar_expect_tx(&sh->q_full, TILE_BYTES);
+        tma_load_3d(q_s, &q_map, 0, kv_head * G, q_begin + q_off, &sh->q_full);
+        tma_load_3d(q_s + HALF_BYTES, &q_map, 64, kv_head * G, q_begin + q_off, &sh->q_full);
+      }
+      const int P = p.page_size, pages_per_tile = BN / P;
+      bool ok = true;
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int s = j % KV_STAGES, ph = (j / KV_STAGES) & 1;
+        // page ids of this tile: lane i reads the i-th (a tile has at most 16 pages)
+        const int pi = j * pages_per_tile + lane;
+        int page = -1;
+        if (lane < pages_per_tile && pi * P < j_hi && pi < p.table_width) {
+          page = p.block_table[(size_t)entry * p.table_width + pi];
+          if (page < 0 || page >= p.num_pages) { atomicOr(p.status, JV_STATUS_BAD_PAGE); page = -1; }
+        }
+        const unsigned have = __ballot_sync(0xffffffffu, page >= 0);
+        const int n_pages = __popc(have);
+        for (int which = 0; which < 2 && ok; ++which) {       // keys, then values
+          uint64_t* full = which ? &sh->v_full[s] : &sh->k_full[s];
+          uint64_t* empty = which ? &sh->v_empty[s] : &sh->k_empty[s];
+          unsigned char* dst = (which ? v_s : k_s) + s * TILE_BYTES;
+          const CUtensorMap* map = which ? &v_map : &k_map;
+          if (lane == 0) {
+            ok = mbar_wait(empty, ph ^ 1);
+            if (ok) mbar_expect_tx(full, n_pages * P * 128 * 2);
+          }
+          ok = __shfl_sync(0xffffffffu, ok, 0);
+          for (int i = 0; i < pages_per_tile && ok; ++i) {
+            const int pg = __shfl_sync(0xffffffffu, page, i);
+            if (lane == 0 && pg >= 0) {
+              tma_load_4d(dst + i * P * 128, map, 0, kv_head, 0, pg, full);
+              tma_load_4d(dst + HALF_BYTES + i * P * 128, map, 64, kv_head, 0, pg, full);
+            }
+          }
+        }
+      }
+      if (!ok && lane == 0) atomicOr(p.status, JV_STATUS_WAIT_EXPIRED);
+    } else if (warp == 1) {
+      // -------------------------------------------------------------- mma issuer
+      if (lane == 0) {
+        bool ok = mbar_wait(&sh->q_full, 0);
+        const uint64_t q_desc0 = desc_k_major(smem_u32(q_s)), q_desc1 = desc_k_major(smem_u32(q_s + HALF_BYTES));
+        auto issue_qk = [&](int j) -> bool {                   // S[j % 2] = Q K_j^T
+          const int s = j % KV_STAGES;
+          if (!mbar_wait(&sh->k_full[s], (j / KV_STAGES) & 1)) return false;
+          TC_FENCE_AFTER();
+          const uint64_t k0 = desc_k_major(smem_u32(k_s + s * TILE_BYTES)), k1 = desc_k_major(smem_u32(k_s + s * TILE_BYTES + HALF_BYTES));
+          const uint32_t tmem_s = tmem + (j & 1) * 128;
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) umma(tmem_s, q_desc0 + 2 * kk, k0 + 2 * kk, IDESC_QK, kk != 0);
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) umma(tmem_s, q_desc1 + 2 * kk, k1 + 2 * kk, IDESC_QK, 1);
+          umma_commit(&sh->k_empty[s]);
+          umma_commit(&sh->s_full[j & 1]);
+          return true;
+        };
+        if (ok) ok = issue_qk(0);
+        for (int j = 0; j < n_tiles && ok; ++j) {
+          if (j + 1 < n_tiles) ok = issue_qk(j + 1);           // the next scores while this tile's softmax runs
+          if (!ok) break;
+          const int s = j % KV_STAGES;
+          if (!mbar_wait(&sh->p_full[j & 1], (j >> 1) & 1) || !mbar_wait(&sh->v_full[s], (j / KV_STAGES) & 1)) { ok = false; break; }
+          TC_FENCE_AFTER();
+          // O += P V_j : 8 steps of 16 keys; P K-major (keys along the 128-byte rows), V MN-major
+          const uint32_t v_addr = smem_u32(v_s + s * TILE_BYTES);
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk) {
+            const uint64_t a = desc_k_major(smem_u32(p_s + (j & 1) * TILE_BYTES + (kk >> 2) * HALF_BYTES)) + 2 * (kk & 3);
+            const uint64_t b = desc_mn_major(v_addr + kk * 16 * 128);
+            umma(tmem_o, a, b, IDESC_PV, (j | kk) != 0);
+          }
+          umma_commit(&sh->v_empty[s]);
+          umma_commit(&sh->o_done[j & 1]);
+        }
+        if (!ok) atomicOr(p.status, JV_STATUS_WAIT_EXPIRED);
+      }
+    } else {
+      // ----------------------------------------------------------------- softmax
+      const int quad = warp & 3;
+      const int r = quad * 32 + lane;                           // this thread's row of the tile
+      const int t = r / HPT, hh = r % HPT;
+      const bool row_ok = t < tokens_here && hh < G;
+      const int pos = row_ok ? pos_first + t : -1;
+      const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
+      // m_ref is the reference maximum that the exponentials are taken against.  It follows the true
+      // maximum lazily: only when the maximum has grown by more than 2^8 (in the exponent) is O rescaled,
+      // which is rare after the first tiles; until then probabilities may exceed 1 by at most that factor.
+      float m_ref = -INFINITY, l_run = 0.f;
+      constexpr float LAZY = 8.f;
+      bool ok = true;
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        if (!mbar_wait(&sh->s_full[j & 1], (j >> 1) & 1)) { ok = false; break; }
+        TC_FENCE_AFTER();
+        const uint32_t s_addr = tmem + lane_addr + (j & 1) * 128;
+        const int key0 = j * BN;
+        const bool need_mask = key0 + BN > j_hi || key0 + BN - 1 > pos_first;   // block-uniform
+        // ---- the whole row of scores into registers (four loads in flight, one wait)
+        uint32_t sr[4][32];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) tmem_ld32_issue(s_addr + c * 32, sr[c]);
+        tmem_ld_wait();
+        float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            if (need_mask) {
+              const int key = key0 + c * 32 + i;
+              if (!(key <= pos && key < j_hi)) sr[c][i] = __float_as_uint(-INFINITY);
+            }
+            mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(sr[c][i]));
+          }
+        const float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+        float alpha = 1.f;
+        if (m_tile != -INFINITY && (m_ref == -INFINITY || (m_tile - m_ref) * p.scale_log2 > LAZY)) {
+          alpha = (m_ref == -INFINITY) ? 0.f : fast_exp2((m_ref - m_tile) * p.scale_log2);
+          m_ref = m_tile;
+        }
+        const float m_scaled = (m_ref == -INFINITY) ? 0.f : m_ref * p.scale_log2;
+        // ---- O is rescaled only if some row of this warp moved its reference; the previous P V must be complete then
+        if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+          if (!mbar_wait(&sh->o_done[(j - 1) & 1], ((j - 1) >> 1) & 1)) { ok = false; break; }
+          TC_FENCE_AFTER();
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
+            float v[32];
+            tmem_ld32(tmem_o + lane_addr + c * 32, v);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] *= alpha;
+            tmem_st32(tmem_o + lane_addr + c * 32, v);
+          }
+        }
+        // ---- this tile's P buffer was read by the product of tile j-2
+        if (j >= 2 && !mbar_wait(&sh->o_done[j & 1], ((j - 2) >> 1) & 1)) { ok = false; break; }
+        // ---- probabilities, as bfloat16 into the swizzled K-major tile
+        float sum[4] = {0.f, 0.f, 0.f, 0.f};
+        unsigned char* p_tile = p_s + (j & 1) * TILE_BYTES;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          unsigned char* row_base = p_tile + (c >> 1) * HALF_BYTES + r * 128;
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint4 pk;
+            __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int i = q * 8 + e * 2;
+              const float p0 = fast_exp2(fmaf(__uint_as_float(sr[c][i]), p.scale_log2, -m_scaled));
+              const float p1 = fast_exp2(fmaf(__uint_as_float(sr[c][i + 1]), p.scale_log2, -m_scaled));
+              sum[e] += p0 + p1;
+              h2[e] = __floats2bfloat162_rn(p0, p1);
+            }
+            const int chunk = (c & 1) * 4 + q;                  // 16-byte chunk within the 128-byte row
+            *reinterpret_cast<uint4*>(row_base + ((chunk ^ (r & 7)) << 4)) = pk;
+          }
+        }
+        l_run = l_run * alpha + ((sum[0] + sum[1]) + (sum[2] + sum[3]));
+        // ---- in the last tile the value rows past the end become zero (they may hold anything)
+        if (j == n_tiles - 1 && j_hi < key0 + BN) {
+          const int s = j % KV_STAGES;
+          if (mbar_wait(&sh->v_full[s], (j / KV_STAGES) & 1)) {
+            for (int i = (threadIdx.x - 64); i < (key0 + BN - j_hi) * 16; i += 128) {
+              const int key_row = (j_hi - key0) + i / 16, part = i % 16;     // 16 chunks of 16 bytes per row (both halves)
+              *reinterpret_cast<uint4*>(v_s + s * TILE_BYTES + (part >> 3) * HALF_BYTES + key_row * 128 + (part & 7) * 16) =
+                  make_uint4(0, 0, 0, 0);
+            }
+          } else {
+            ok = false;
+          }
+        }
+        PROXY_FENCE();                                           // P (and the zeroed rows) visible to the tensor core
+        TC_FENCE_BEFORE();
+        mbar_arrive(&sh->p_full[j & 1]);
+      }
+      // ---- output: O / sum
+      if (ok && mbar_wait(&sh->o_done[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1)) {
+        TC_FENCE_AFTER();
+        const float inv = row_ok ? 1.f / l_run : 0.f;
+        __nv_bfloat16* dst = p.out + (size_t)(q_begin + q_off + t) * p.out_stride + (size_t)(kv_head * G + hh) * D;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          float v[32];
+          tmem_ld32(tmem_o + lane_addr + c * 32, v);
+          if (row_ok) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint4 pk;
+              __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+              for (int e = 0; e < 4; ++e) h2[e] = __floats2bfloat162_rn(v[q * 8 + 2 * e] * inv, v[q * 8 + 2 * e + 1] * inv);
+              *reinterpret_cast<uint4*>(dst + c * 32 + q * 8) = pk;
+            }
+          }
+        }
+      } else if (lane == 0) {
+        atomicOr(p.status, JV_STATUS_WAIT_EXPIRED);
+      }
+    }
+  }
+
+  TC_FENCE_BEFORE();
+  __syncthreads();
+  if (warp == 1) {
+    TC_FENCE_AFTER();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(ptr);
+  }
+  return fn;
+}
+}  // namespace
+
+// 1 if this kernel takes the case (else the caller uses the mma.sync kernel).
+JV_EXPORT int jv_attn_tcgen05_supports(int head_dim, int n_q_heads, int n_kv_heads, int page_size, int window) {
+  if (head_dim != 128 || window > 0 || n_kv_heads < 1 || n_q_heads % n_kv_heads) return 0;
+  const int G = n_q_heads / n_kv_heads;
+  if (!(G == 1 || G == 2 || G == 4 || G == 8 || G == 16)) return 0;
+  return page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64 || page_size == 128;
+}
+
+// Tokens per 128-row tile.
+JV_EXPORT int jv_attn_tcgen05_tokens_per_tile(int n_q_heads, int n_kv_heads) { return ROWS / (n_q_heads / n_kv_heads); }
+
+// q: [n_tokens, q_stride] bfloat16 with head h of a token at column h*128; out: [n_tokens, out_stride];
+// k_cache/v_cache: [num_pages, page_size, n_kv_heads, 128]; work: [n_work, 2] (entry, first token of the tile),
+// tiles of jv_attn_tcgen05_tokens_per_tile tokens, in ascending order of work.
+JV_EXPORT int jv_attn_tcgen05(const void* q, int q_stride, int n_tokens, void* out, int out_stride, const void* k_cache,
+                              const void* v_cache, const int* block_table, int table_width, const int* cu_seqlens,
+                              const int* start_pos, const int* work, int n_work, int n_q_heads, int n_kv_heads,
+                              int head_dim, int page_size, int num_pages, float scale, int* status, cudaStream_t stream) {
+  if (n_work == 0) return JV_OK;
+  if (!jv_attn_tcgen05_supports(head_dim, n_q_heads, n_kv_heads, page_size, 0)) return JV_ERR_UNSUPPORTED;
+  if ((q_stride % 8) || (out_stride % 8) || ((uintptr_t)q % 16) || ((uintptr_t)out % 16) || ((uintptr_t)k_cache % 16) ||
+      ((uintptr_t)v_cache % 16))
+    return JV_ERR_UNSUPPORTED;
+  auto fn = encode_fn();
+  if (fn == nullptr) return JV_ERR_UNSUPPORTED;
+  const int G = n_q_heads / n_kv_heads;
+  CUtensorMap q_map, k_map, v_map;
+  {
+    // queries: (d, head, token); a box is 64 d x G heads x (128 / G) tokens = 128 rows, head fastest
+    const cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)n_q_heads, (cuuint64_t)n_tokens};
+    const cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)q_stride * 2};
+    const cuuint32_t box[3] = {64, (cuuint32_t)G, (cuuint32_t)(ROWS / G)};
+    const cuuint32_t es[3] = {1, 1, 1};
+    if (fn(&q_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(q), dims, strides, box, es,
+           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return JV_ERR_UNSUPPORTED;
+  }
+  for (int which = 0; which < 2; ++which) {
+    // cache: (d, kv head, slot, page); a box is 64 d x 1 head x page_size slots x 1 page
+    const cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)n_kv_heads, (cuuint64_t)page_size, (cuuint64_t)num_pages};
+    const cuuint64_t strides[3] = {(cuuint64_t)D * 2, (cuuint64_t)n_kv_heads * D * 2, (cuuint64_t)page_size * n_kv_heads * D * 2};
+    const cuuint32_t box[4] = {64, 1, (cuuint32_t)page_size, 1};
+    const cuuint32_t es[4] = {1, 1, 1, 1};
+    if (fn(which ? &v_map : &k_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(which ? v_cache : k_cache), dims,
+           strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return JV_ERR_UNSUPPORTED;
+  }
+  Params p;
+  p.out = (__nv_bfloat16*)out; p.out_stride = out_stride; p.block_table = block_table; p.table_width = table_width;
+  p.cu_seqlens = cu_seqlens; p.start_pos = start_pos; p.work = work; p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads;
+  p.page_size = page_size; p.num_pages = num_pages; p.hpt = G; p.tokens_per_tile = ROWS / G;
+  p.scale_log2 = scale * LOG2E; p.status = status;
+  constexpr size_t smem = TILE_BYTES * (3 + 2 * KV_STAGES) + sizeof(Shared) + 1024;
+  static bool ready = false;
+  if (!ready) {
+    if (cudaFuncSetAttribute(attn_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+      return JV_ERR_UNSUPPORTED;
+    ready = true;
+  }
+  attn_tcgen05_kernel<<<dim3(n_work, n_kv_heads), THREADS, smem, stream>>>(q_map, k_map, v_map, p);
+  return jv_check_launch();
+}

@@ -304,6 +304,38 @@ def attn_mma(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cache: torch.T
              status_word(q.device).data_ptr(), _stream()), "attn_mma")
 
 
+def attn_tcgen05_supports(dtype: torch.dtype, head_dim: int, n_q_heads: int, n_kv_heads: int, page_size: int,
+                          window: int) -> bool:
+    """Whether the tcgen05 prompt-attention kernel takes the case (csrc/attn_tcgen05.cu)."""
+    g = n_q_heads // max(n_kv_heads, 1)
+    return (dtype == torch.bfloat16 and head_dim == 128 and not window and n_q_heads % n_kv_heads == 0
+            and g in (1, 2, 4, 8, 16) and page_size in (8, 16, 32, 64, 128))
+
+
+def attn_tcgen05_tokens_per_tile(n_q_heads: int, n_kv_heads: int) -> int:
+    return 128 // (n_q_heads // n_kv_heads)
+
+
+def attn_tcgen05(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                 block_table: torch.Tensor, cu_seqlens: torch.Tensor, start_pos: torch.Tensor, work: torch.Tensor,
+                 n_work: int, n_q_heads: int, n_kv_heads: int, head_dim: int, scale: float) -> None:
+    """Paged causal attention of prompt portions on tcgen05 tensor cores with scores and output in tensor
+    memory (csrc/attn_tcgen05.cu); `work` lists 128-row tiles of `attn_tcgen05_tokens_per_tile` tokens."""
+    for t, nm in ((q, "q"), (out, "out"), (k_cache, "k_cache"), (v_cache, "v_cache")):
+        _cuda(t, nm, torch.bfloat16, contiguous=(nm != "q"))
+    for t, nm in ((block_table, "block_table"), (cu_seqlens, "cu_seqlens"), (start_pos, "start_pos"), (work, "work")):
+        _cuda(t, nm, torch.int32)
+    if n_work == 0:
+        return
+    f = _fn("attn_tcgen05", "jv_attn_tcgen05", [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                                                c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                                c_float, c_void_p, c_void_p])
+    _check(f(q.data_ptr(), q_stride, q.shape[0], out.data_ptr(), out.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),
+             block_table.data_ptr(), block_table.shape[1], cu_seqlens.data_ptr(), start_pos.data_ptr(), work.data_ptr(),
+             n_work, n_q_heads, n_kv_heads, head_dim, k_cache.shape[1], k_cache.shape[0], float(scale),
+             status_word(q.device).data_ptr(), _stream()), "attn_tcgen05")
+
+
 # --------------------------------------------------------------------------- linear
 def gemm_simt(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
     """x [M, K] times weight [N, K] transposed, accumulated in float32 on CUDA cores."""

@@ -266,7 +266,8 @@ def dense_attention(q, k_all, v_all, q_pos, scale, window, g):
     return torch.einsum("hnl,lhd->nhd", torch.softmax(s, -1), v)
 
 
-def run_attention(ops, dtype, hq, hkv, d, page, q_lens, starts, window=0, split=0, seed=6, boost=None, mma=False):
+def run_attention(ops, dtype, hq, hkv, d, page, q_lens, starts, window=0, split=0, seed=6, boost=None, mma=False,
+                  tc5=False):
     g = torch.Generator().manual_seed(seed)
     G = hq // hkv
     R, n = len(q_lens), sum(q_lens)
@@ -303,7 +304,8 @@ def run_attention(ops, dtype, hq, hkv, d, page, q_lens, starts, window=0, split=
     out = torch.zeros(n, hq * d, dtype=dtype, device=DEV)
     common = (kc.to(dtype).to(DEV), vc.to(dtype).to(DEV), table.to(DEV), cu.to(DEV),
               torch.tensor(starts, dtype=torch.int32, device=DEV))
-    tpt = (ops.attn_mma_tokens_per_tile if mma else ops.attn_simt_tokens_per_tile)(hq, hkv)
+    tpt = (ops.attn_tcgen05_tokens_per_tile if tc5 else ops.attn_mma_tokens_per_tile if mma
+           else ops.attn_simt_tokens_per_tile)(hq, hkv)
     attn = ops.attn_mma if mma else ops.attn_simt
     if split:
         assert all(ql == 1 for ql in q_lens)
@@ -312,7 +314,10 @@ def run_attention(ops, dtype, hq, hkv, d, page, q_lens, starts, window=0, split=
              n_splits=-(-max(total) // split))
     else:
         work = torch.tensor([[e, t] for e in range(R) for t in range(0, q_lens[e], tpt)], dtype=torch.int32, device=DEV)
-        attn(dq, hq * d, out, *common, work, work.shape[0], hq, hkv, d, window, scale)
+        if tc5:
+            ops.attn_tcgen05(dq, hq * d, out, *common, work, work.shape[0], hq, hkv, d, scale)
+        else:
+            attn(dq, hq * d, out, *common, work, work.shape[0], hq, hkv, d, window, scale)
     ops.check_status()
     got = out.float().cpu().reshape(n, hq, d)
     assert not torch.isnan(got).any()
@@ -390,6 +395,35 @@ def test_mma_attention_finds_one_far_key_among_hundreds(ops, split, far):
     got, want = run_attention(ops, torch.bfloat16, 4, 2, 64, 16, q_lens=q_lens, starts=starts, split=split,
                               boost=(1, far), mma=True)
     torch.testing.assert_close(got, want, **BF16_TOL)
+
+
+# ---- the tcgen05 kernel (bfloat16, head size 128)
+@pytest.mark.parametrize("hq,hkv,page", [(4, 1, 16), (32, 8, 16), (8, 8, 8), (2, 1, 128), (16, 1, 32), (16, 2, 64)])
+def test_tcgen05_attention_portions_with_context(ops, hq, hkv, page):
+    got, want = run_attention(ops, torch.bfloat16, hq, hkv, 128, page, q_lens=[7, 300, 133, 2, 70], starts=[0, 50, 21, 64, 190],
+                              tc5=True)
+    torch.testing.assert_close(got, want, **BF16_TOL)
+
+
+@pytest.mark.parametrize("far", [0, 3, 130, 511])
+def test_tcgen05_attention_finds_one_far_key_among_hundreds(ops, far):
+    got, want = run_attention(ops, torch.bfloat16, 4, 2, 128, 16, q_lens=[3, 2], starts=[10, 598], boost=(1, far), tc5=True)
+    torch.testing.assert_close(got, want, **BF16_TOL)
+
+
+def test_tcgen05_attention_long_prompt(ops):
+    got, want = run_attention(ops, torch.bfloat16, 8, 2, 128, 16, q_lens=[1000], starts=[0], tc5=True)
+    torch.testing.assert_close(got, want, **BF16_TOL)
+
+
+def test_tcgen05_support_rules(ops):
+    from jax_vllm_b200.csrc import build
+    lib = build.load("attn_tcgen05")
+    for d, hq, hkv, page, window in [(128, 32, 8, 16, 0), (64, 32, 8, 16, 0), (128, 6, 1, 16, 0), (128, 32, 8, 4, 0),
+                                     (128, 32, 8, 16, 5), (128, 16, 1, 128, 0), (128, 20, 1, 16, 0)]:
+        assert bool(lib.jv_attn_tcgen05_supports(d, hq, hkv, page, window)) == \
+            ops.attn_tcgen05_supports(torch.bfloat16, d, hq, hkv, page, window)
+    assert lib.jv_attn_tcgen05_tokens_per_tile(32, 8) == ops.attn_tcgen05_tokens_per_tile(32, 8) == 32
 
 
 def test_mma_support_table_matches_the_library(ops):
