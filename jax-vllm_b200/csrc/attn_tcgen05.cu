@@ -29,7 +29,8 @@ constexpr int D = 128, ROWS = 128, BN = 128;
 constexpr int TILE_BYTES = 128 * 128 * 2;       // a 128 x 128 bfloat16 tile: two halves of [128 rows][128 bytes]
 constexpr int HALF_BYTES = 128 * 128;            // one half: 128 rows of 128 bytes
 constexpr int KV_STAGES = 2;
-constexpr int THREADS = 192;
+constexpr int THREADS = 320;                     // producer warp, mma warp, 8 softmax warps
+constexpr int SOFTMAX_THREADS = 256;
 constexpr int TMEM_COLS = 512;                   // S0: [0,128)  S1: [128,256)  O: [256,384)
 constexpr long long WAIT_CYCLES = 2000000000LL;
 constexpr float LOG2E = 1.4426950408889634f;
@@ -150,6 +151,7 @@ struct Shared {
   uint64_t q_full, k_full[KV_STAGES], k_empty[KV_STAGES], v_full[KV_STAGES], v_empty[KV_STAGES];
   uint64_t s_full[2], p_full[2], o_done[2];
   uint32_t tmem_base;
+  float xch[2][128];            // a row's two softmax threads exchange their maxima (and at the end their sums)
 };
 
 __global__ void __launch_bounds__(THREADS, 1) attn_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map,
@@ -185,7 +187,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tcgen05_kernel(const __grid_c
       mbar_init(&sh->v_full[s], 1); mbar_init(&sh->v_empty[s], 1);
     }
     mbar_init(&sh->s_full[0], 1); mbar_init(&sh->s_full[1], 1);
-    mbar_init(&sh->p_full[0], 128); mbar_init(&sh->p_full[1], 128);
+    mbar_init(&sh->p_full[0], SOFTMAX_THREADS); mbar_init(&sh->p_full[1], SOFTMAX_THREADS);
     mbar_init(&sh->o_done[0], 1); mbar_init(&sh->o_done[1], 1);
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
@@ -211,36 +213,50 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tcgen05_kernel(const __grid_c
         tma_load_3d(q_s + HALF_BYTES, &q_map, 64, kv_head * G, q_begin + q_off, &sh->q_full);
       }
       const int P = p.page_size, pages_per_tile = BN / P;
-      bool ok = true;
-      for (int j = 0; j < n_tiles && ok; ++j) {
-        const int s = j % KV_STAGES, ph = (j / KV_STAGES) & 1;
-        // page ids of this tile: lane i reads the i-th (a tile has at most 16 pages)
+      // page ids of a tile: lane i reads the i-th (a tile has at most 16 pages); -1 = no page needed or none there
+      auto tile_pages = [&](int j) -> int {
         const int pi = j * pages_per_tile + lane;
         int page = -1;
-        if (lane < pages_per_tile && pi * P < j_hi && pi < p.table_width) {
+        if (j < n_tiles && lane < pages_per_tile && pi * P < j_hi && pi < p.table_width) {
           page = p.block_table[(size_t)entry * p.table_width + pi];
           if (page < 0 || page >= p.num_pages) { atomicOr(p.status, JV_STATUS_BAD_PAGE); page = -1; }
         }
-        const unsigned have = __ballot_sync(0xffffffffu, page >= 0);
-        const int n_pages = __popc(have);
-        for (int which = 0; which < 2 && ok; ++which) {       // keys, then values
-          uint64_t* full = which ? &sh->v_full[s] : &sh->k_full[s];
-          uint64_t* empty = which ? &sh->v_empty[s] : &sh->k_empty[s];
-          unsigned char* dst = (which ? v_s : k_s) + s * TILE_BYTES;
-          const CUtensorMap* map = which ? &v_map : &k_map;
-          if (lane == 0) {
-            ok = mbar_wait(empty, ph ^ 1);
-            if (ok) mbar_expect_tx(full, n_pages * P * 128 * 2);
-          }
-          ok = __shfl_sync(0xffffffffu, ok, 0);
-          for (int i = 0; i < pages_per_tile && ok; ++i) {
-            const int pg = __shfl_sync(0xffffffffu, page, i);
-            if (lane == 0 && pg >= 0) {
-              tma_load_4d(dst + i * P * 128, map, 0, kv_head, 0, pg, full);
-              tma_load_4d(dst + HALF_BYTES + i * P * 128, map, 64, kv_head, 0, pg, full);
-            }
-          }
+        return page;
+      };
+      // one tile (keys or values) into its stage, once the stage is free
+      auto load_tile = [&](int j, int which, int page) -> bool {
+        const int s = j % KV_STAGES, ph = (j / KV_STAGES) & 1;
+        uint64_t* full = which ? &sh->v_full[s] : &sh->k_full[s];
+        uint64_t* empty = which ? &sh->v_empty[s] : &sh->k_empty[s];
+        unsigned char* dst = (which ? v_s : k_s) + s * TILE_BYTES;
+        const CUtensorMap* map = which ? &v_map : &k_map;
+        const int n_pages = __popc(__ballot_sync(0xffffffffu, page >= 0));
+        bool ok = true;
+        if (lane == 0) {
+          ok = mbar_wait(empty, ph ^ 1);
+          if (ok) mbar_expect_tx(full, n_pages * P * 128 * 2);
         }
+        ok = __shfl_sync(0xffffffffu, ok, 0);      // also orders the announcement before the copies
+        // lane i issues the two boxes of page i: the copies of a tile are started by one pair of instructions of
+        // the warp, not one after another by a single thread (which takes longer than the tile's mathematics)
+        if (ok && page >= 0) {
+          tma_load_4d(dst + lane * P * 128, map, 0, kv_head, 0, page, full);
+          tma_load_4d(dst + HALF_BYTES + lane * P * 128, map, 64, kv_head, 0, page, full);
+        }
+        return ok;
+      };
+      // keys run one tile ahead of values (the scores of tile j+1 are wanted while tile j is in its softmax),
+      // and the block-table entries of a tile are read while the tile before it is loaded
+      int pages_k = tile_pages(0);
+      bool ok = load_tile(0, 0, pages_k);
+      int pages_v = pages_k;
+      pages_k = tile_pages(1);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int pages_next = tile_pages(j + 2);
+        if (j + 1 < n_tiles) ok = load_tile(j + 1, 0, pages_k);
+        if (ok) ok = load_tile(j, 1, pages_v);
+        pages_v = pages_k;
+        pages_k = pages_next;
       }
       if (!ok && lane == 0) atomicOr(p.status, JV_STATUS_WAIT_EXPIRED);
     } else if (warp == 1) {
@@ -248,11 +264,23 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tcgen05_kernel(const __grid_c
       if (lane == 0) {
         bool ok = mbar_wait(&sh->q_full, 0);
         const uint64_t q_desc0 = desc_k_major(smem_u32(q_s)), q_desc1 = desc_k_major(smem_u32(q_s + HALF_BYTES));
+        uint64_t k_desc[KV_STAGES][2], v_desc[KV_STAGES], p_desc[2][2];
+#pragma unroll
+        for (int st = 0; st < KV_STAGES; ++st) {
+          k_desc[st][0] = desc_k_major(smem_u32(k_s + st * TILE_BYTES));
+          k_desc[st][1] = desc_k_major(smem_u32(k_s + st * TILE_BYTES + HALF_BYTES));
+          v_desc[st] = desc_mn_major(smem_u32(v_s + st * TILE_BYTES));
+        }
+#pragma unroll
+        for (int b = 0; b < 2; ++b) {
+          p_desc[b][0] = desc_k_major(smem_u32(p_s + b * TILE_BYTES));
+          p_desc[b][1] = desc_k_major(smem_u32(p_s + b * TILE_BYTES + HALF_BYTES));
+        }
         auto issue_qk = [&](int j) -> bool {                   // S[j % 2] = Q K_j^T
           const int s = j % KV_STAGES;
           if (!mbar_wait(&sh->k_full[s], (j / KV_STAGES) & 1)) return false;
           TC_FENCE_AFTER();
-          const uint64_t k0 = desc_k_major(smem_u32(k_s + s * TILE_BYTES)), k1 = desc_k_major(smem_u32(k_s + s * TILE_BYTES + HALF_BYTES));
+          const uint64_t k0 = k_desc[s][0], k1 = k_desc[s][1];
           const uint32_t tmem_s = tmem + (j & 1) * 128;
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk) umma(tmem_s, q_desc0 + 2 * kk, k0 + 2 * kk, IDESC_QK, kk != 0);
@@ -270,13 +298,9 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tcgen05_kernel(const __grid_c
           if (!mbar_wait(&sh->p_full[j & 1], (j >> 1) & 1) || !mbar_wait(&sh->v_full[s], (j / KV_STAGES) & 1)) { ok = false; break; }
           TC_FENCE_AFTER();
           // O += P V_j : 8 steps of 16 keys; P K-major (keys along the 128-byte rows), V MN-major
-          const uint32_t v_addr = smem_u32(v_s + s * TILE_BYTES);
 #pragma unroll
-          for (int kk = 0; kk < 8; ++kk) {
-            const uint64_t a = desc_k_major(smem_u32(p_s + (j & 1) * TILE_BYTES + (kk >> 2) * HALF_BYTES)) + 2 * (kk & 3);
-            const uint64_t b = desc_mn_major(v_addr + kk * 16 * 128);
-            umma(tmem_o, a, b, IDESC_PV, (j | kk) != 0);
-          }
+          for (int kk = 0; kk < 8; ++kk)   // 16 keys further: 32 bytes along P's rows, 16 rows (2048 bytes) down V
+            umma(tmem_o, p_desc[j & 1][kk >> 2] + 2 * (kk & 3), v_desc[s] + kk * (16 * 128 / 16), IDESC_PV, (j | kk) != 0);
           umma_commit(&sh->v_empty[s]);
           umma_commit(&sh->o_done[j & 1]);
         }
@@ -284,7 +308,10 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tcgen05_kernel(const __grid_c
       }
     } else {
       // ----------------------------------------------------------------- softmax
+      // Two threads per row: warps 2..5 take the first 64 keys of a tile (and the first 64 columns of O),
+      // warps 6..9 the other 64.  A warp reads the 32 TMEM lanes of its number modulo 4.
       const int quad = warp & 3;
+      const int half = (warp - 2) >> 2;
       const int r = quad * 32 + lane;                           // this thread's row of the tile
       const int t = r / HPT, hh = r % HPT;
       const bool row_ok = t < tokens_here && hh < G;
@@ -296,56 +323,68 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tcgen05_kernel(const __grid_c
       float m_ref = -INFINITY, l_run = 0.f;
       constexpr float LAZY = 8.f;
       bool ok = true;
-      for (int j = 0; j < n_tiles && ok; ++j) {
-        if (!mbar_wait(&sh->s_full[j & 1], (j >> 1) & 1)) { ok = false; break; }
-        TC_FENCE_AFTER();
-        const uint32_t s_addr = tmem + lane_addr + (j & 1) * 128;
-        const int key0 = j * BN;
-        const bool need_mask = key0 + BN > j_hi || key0 + BN - 1 > pos_first;   // block-uniform
-        // ---- the whole row of scores into registers (four loads in flight, one wait)
-        uint32_t sr[4][32];
+      // A wait that runs out makes `ok` false for the whole warp; the loop then only keeps its appointments at
+      // the named barrier (so that nobody is left waiting there) and does no further work.
+      for (int j = 0; j < n_tiles; ++j) {
+        if (ok) ok = mbar_wait(&sh->s_full[j & 1], (j >> 1) & 1);
+        ok = __all_sync(0xffffffffu, ok);
+        const uint32_t s_addr = tmem + lane_addr + (j & 1) * 128 + half * 64;
+        const int key0 = j * BN + half * 64;                     // first key of this thread's 64
+        const bool need_mask = j * BN + BN > j_hi || j * BN + BN - 1 > pos_first;   // block-uniform
+        uint32_t sr[2][32];
+        float my_max = -INFINITY;
+        if (ok) {
+          TC_FENCE_AFTER();
+          tmem_ld32_issue(s_addr, sr[0]);
+          tmem_ld32_issue(s_addr + 32, sr[1]);
+          tmem_ld_wait();
+          float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-        for (int c = 0; c < 4; ++c) tmem_ld32_issue(s_addr + c * 32, sr[c]);
-        tmem_ld_wait();
-        float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+          for (int c = 0; c < 2; ++c)
 #pragma unroll
-        for (int c = 0; c < 4; ++c)
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            if (need_mask) {
-              const int key = key0 + c * 32 + i;
-              if (!(key <= pos && key < j_hi)) sr[c][i] = __float_as_uint(-INFINITY);
+            for (int i = 0; i < 32; ++i) {
+              if (need_mask) {
+                const int key = key0 + c * 32 + i;
+                if (!(key <= pos && key < j_hi)) sr[c][i] = __float_as_uint(-INFINITY);
+              }
+              mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(sr[c][i]));
             }
-            mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(sr[c][i]));
-          }
-        const float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+          my_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+        }
+        // ---- the row's maximum over the tile: exchange with the thread that has the other 64 keys
+        sh->xch[half][r] = my_max;
+        asm volatile("bar.sync 1, 256;\n" ::: "memory");
+        const float m_tile = fmaxf(sh->xch[0][r], sh->xch[1][r]);
+        asm volatile("bar.sync 1, 256;\n" ::: "memory");          // both have read before the next tile writes
         float alpha = 1.f;
-        if (m_tile != -INFINITY && (m_ref == -INFINITY || (m_tile - m_ref) * p.scale_log2 > LAZY)) {
+        if (ok && m_tile != -INFINITY && (m_ref == -INFINITY || (m_tile - m_ref) * p.scale_log2 > LAZY)) {
           alpha = (m_ref == -INFINITY) ? 0.f : fast_exp2((m_ref - m_tile) * p.scale_log2);
           m_ref = m_tile;
         }
         const float m_scaled = (m_ref == -INFINITY) ? 0.f : m_ref * p.scale_log2;
         // ---- O is rescaled only if some row of this warp moved its reference; the previous P V must be complete then
-        if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
-          if (!mbar_wait(&sh->o_done[(j - 1) & 1], ((j - 1) >> 1) & 1)) { ok = false; break; }
-          TC_FENCE_AFTER();
+        if (ok && j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+          ok = __all_sync(0xffffffffu, mbar_wait(&sh->o_done[(j - 1) & 1], ((j - 1) >> 1) & 1));
+          if (ok) {
+            TC_FENCE_AFTER();
 #pragma unroll 1
-          for (int c = 0; c < 4; ++c) {
-            float v[32];
-            tmem_ld32(tmem_o + lane_addr + c * 32, v);
+            for (int c = 0; c < 2; ++c) {
+              float v[32];
+              tmem_ld32(tmem_o + lane_addr + half * 64 + c * 32, v);
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] *= alpha;
-            tmem_st32(tmem_o + lane_addr + c * 32, v);
+              for (int i = 0; i < 32; ++i) v[i] *= alpha;
+              tmem_st32(tmem_o + lane_addr + half * 64 + c * 32, v);
+            }
           }
         }
         // ---- this tile's P buffer was read by the product of tile j-2
-        if (j >= 2 && !mbar_wait(&sh->o_done[j & 1], ((j - 2) >> 1) & 1)) { ok = false; break; }
-        // ---- probabilities, as bfloat16 into the swizzled K-major tile
+        if (ok && j >= 2) ok = __all_sync(0xffffffffu, mbar_wait(&sh->o_done[j & 1], ((j - 2) >> 1) & 1));
+        if (!ok) continue;
+        // ---- probabilities, as bfloat16 into the swizzled K-major tile: this thread's 64 keys are one 128-byte row
         float sum[4] = {0.f, 0.f, 0.f, 0.f};
-        unsigned char* p_tile = p_s + (j & 1) * TILE_BYTES;
+        unsigned char* row_base = p_s + (j & 1) * TILE_BYTES + half * HALF_BYTES + r * 128;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          unsigned char* row_base = p_tile + (c >> 1) * HALF_BYTES + r * 128;
+        for (int c = 0; c < 2; ++c)
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
             uint4 pk;
@@ -358,37 +397,39 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tcgen05_kernel(const __grid_c
               sum[e] += p0 + p1;
               h2[e] = __floats2bfloat162_rn(p0, p1);
             }
-            const int chunk = (c & 1) * 4 + q;                  // 16-byte chunk within the 128-byte row
+            const int chunk = c * 4 + q;                         // 16-byte chunk within the 128-byte row
             *reinterpret_cast<uint4*>(row_base + ((chunk ^ (r & 7)) << 4)) = pk;
           }
-        }
         l_run = l_run * alpha + ((sum[0] + sum[1]) + (sum[2] + sum[3]));
         // ---- in the last tile the value rows past the end become zero (they may hold anything)
-        if (j == n_tiles - 1 && j_hi < key0 + BN) {
+        if (j == n_tiles - 1 && j_hi < j * BN + BN) {
           const int s = j % KV_STAGES;
-          if (mbar_wait(&sh->v_full[s], (j / KV_STAGES) & 1)) {
-            for (int i = (threadIdx.x - 64); i < (key0 + BN - j_hi) * 16; i += 128) {
-              const int key_row = (j_hi - key0) + i / 16, part = i % 16;     // 16 chunks of 16 bytes per row (both halves)
+          ok = __all_sync(0xffffffffu, mbar_wait(&sh->v_full[s], (j / KV_STAGES) & 1));
+          if (ok) {
+            for (int i = (threadIdx.x - 64); i < (j * BN + BN - j_hi) * 16; i += SOFTMAX_THREADS) {
+              const int key_row = (j_hi - j * BN) + i / 16, part = i % 16;     // 16 chunks of 16 bytes per row (both halves)
               *reinterpret_cast<uint4*>(v_s + s * TILE_BYTES + (part >> 3) * HALF_BYTES + key_row * 128 + (part & 7) * 16) =
                   make_uint4(0, 0, 0, 0);
             }
-          } else {
-            ok = false;
           }
         }
+        if (!ok) continue;
         PROXY_FENCE();                                           // P (and the zeroed rows) visible to the tensor core
         TC_FENCE_BEFORE();
         mbar_arrive(&sh->p_full[j & 1]);
       }
-      // ---- output: O / sum
+      // ---- output: O / sum, each thread its 64 columns; the row's sum is the two threads' together
+      sh->xch[half][r] = l_run;
+      asm volatile("bar.sync 1, 256;\n" ::: "memory");
+      const float l_row = sh->xch[0][r] + sh->xch[1][r];
       if (ok && mbar_wait(&sh->o_done[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1)) {
         TC_FENCE_AFTER();
-        const float inv = row_ok ? 1.f / l_run : 0.f;
-        __nv_bfloat16* dst = p.out + (size_t)(q_begin + q_off + t) * p.out_stride + (size_t)(kv_head * G + hh) * D;
+        const float inv = row_ok ? 1.f / l_row : 0.f;
+        __nv_bfloat16* dst = p.out + (size_t)(q_begin + q_off + t) * p.out_stride + (size_t)(kv_head * G + hh) * D + half * 64;
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < 2; ++c) {
           float v[32];
-          tmem_ld32(tmem_o + lane_addr + c * 32, v);
+          tmem_ld32(tmem_o + lane_addr + half * 64 + c * 32, v);
           if (row_ok) {
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
