@@ -41,8 +41,8 @@ class BatchLayout:
         add("logit_rows", n_rows)
         for g, w in enumerate(table_widths):
             add(f"table{g}", n_entries * w)
-        for tpt, n in tile_counts.items():
-            add(f"tiles{tpt}", 2 * n)
+        for cls, n in tile_counts.items():
+            add(f"tiles{cls}", 2 * n)
         add("decode", 2 * n_decode)
         self.total = max(off, 4)
         self.table_widths = list(table_widths)
@@ -54,9 +54,12 @@ class BatchLayout:
 
 
 class BatchBuilder:
-    def __init__(self, n_groups: int, page_size: int, tile_token_sizes, device):
+    def __init__(self, n_groups: int, page_size: int, tile_classes, device):
+        """`tile_classes`: the work lists that mixers want for entries of more than one token, each a
+        triple (tokens per tile, least number of new tokens, one more than the most): an entry of q new
+        tokens with least <= q < most is cut into tiles of that many tokens in that list."""
         self.n_groups, self.page_size = n_groups, page_size
-        self.tile_token_sizes = list(tile_token_sizes)
+        self.tile_token_sizes = [tuple(c) for c in tile_classes]
         self.device = torch.device(device)
         self._pinned = None
         self._copied = None           # event: the last copy out of the pinned buffer has finished
@@ -76,7 +79,7 @@ class BatchBuilder:
         cu, start, slots, rows = v("cu_seqlens"), v("start_pos"), v("state_slots"), v("logit_rows")
         n = r = 0
         cu[0] = 0
-        tiles = {tpt: [] for tpt in layout.tile_counts}
+        tiles = {cls: [] for cls in layout.tile_counts}
         decode = []
         for e, entry in enumerate(entries):
             q = len(entry.tokens)
@@ -95,8 +98,10 @@ class BatchBuilder:
             if q == 1:
                 decode.append((e, 0))
             else:
-                for tpt in tiles:
-                    tiles[tpt].extend((e, t) for t in range(0, q, tpt))
+                for cls in tiles:
+                    tpt, lo, hi = cls
+                    if lo <= q < hi:
+                        tiles[cls].extend((e, t) for t in range(0, q, tpt))
             for g in range(self.n_groups):
                 w = layout.table_widths[g]
                 row = layout.view(host, f"table{g}")[e * w:(e + 1) * w]
@@ -109,9 +114,9 @@ class BatchBuilder:
                     raise RuntimeError(f"block table of width {w} is too narrow for {need} pages")
                 row[:need] = t[:need]
                 row[need:] = -1
-        for tpt, lst in tiles.items():
+        for cls, lst in tiles.items():
             if lst:
-                layout.view(host, f"tiles{tpt}")[:] = np.asarray(lst, dtype=np.int32).reshape(-1)
+                layout.view(host, f"tiles{cls}")[:] = np.asarray(lst, dtype=np.int32).reshape(-1)
         if decode:
             v("decode")[:] = np.asarray(decode, dtype=np.int32).reshape(-1)
 
@@ -121,8 +126,8 @@ class BatchBuilder:
         n_rows = sum(len(e.want) for e in entries)
         widest = max([1] + [-(-(e.cache.num_tokens + len(e.tokens)) // P) for e in entries])
         w = table_width or widest
-        tile_counts = {tpt: sum(-(-len(e.tokens) // tpt) for e in entries if len(e.tokens) > 1)
-                       for tpt in self.tile_token_sizes}
+        tile_counts = {cls: sum(-(-len(e.tokens) // cls[0]) for e in entries if len(e.tokens) > 1 and cls[1] <= len(e.tokens) < cls[2])
+                       for cls in self.tile_token_sizes}
         n_decode = sum(1 for e in entries if len(e.tokens) == 1)
         return BatchLayout(n_tokens, len(entries), n_rows, [w] * self.n_groups, tile_counts, n_decode)
 
@@ -132,7 +137,7 @@ class BatchBuilder:
         n_rows = sum(len(e.want) for e in entries)
         R = len(entries)
         tables = [v(f"table{g}").view(R, layout.table_widths[g]) for g in range(self.n_groups)]
-        tile_work = {tpt: (v(f"tiles{tpt}").view(-1, 2), n) for tpt, n in layout.tile_counts.items()}
+        tile_work = {cls: (v(f"tiles{cls}").view(-1, 2), n) for cls, n in layout.tile_counts.items()}
         n_dec = layout.sections["decode"][1] // 2
         seq = max([1] + [e.cache.num_tokens + len(e.tokens) for e in entries])
         return StepContext(

@@ -45,7 +45,7 @@ class Runner:
         kernel_build.build_all(model.kernels() + ["sampling"])
         views = cache.allocate_storage(dtype, self.device)
         self.layer_caches = [views.get(k) for k in range(len(model.order))]
-        self.builder = BatchBuilder(len(cache.groups), cache.page_size, model.tile_token_sizes(), self.device)
+        self.builder = BatchBuilder(len(cache.groups), cache.page_size, model.tile_classes(cache.page_size), self.device)
         self.steps = 0
 
     @torch.no_grad()

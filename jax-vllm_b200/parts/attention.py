@@ -42,6 +42,8 @@ class Attention(Part):
         self.use_mma = ops.attn_mma_supports(ctx.dtype, self.d)
         if self.use_mma:
             self.kernels = ("rope_kv", "attn_mma", "gemm_simt", "linear_skinny")
+            if self.d == 128 and not self.window:
+                self.kernels += ("attn_tcgen05",)
         self.w_qkv = self.w_o = self.q_norm = self.k_norm = None
 
     # -------------------------------------------------------------------- weights
@@ -82,9 +84,16 @@ class Attention(Part):
     def cache_need(self):
         return PagedKVNeed(self.hkv, self.d, self.window or None)
 
-    def tile_tokens(self):
-        f = ops.attn_mma_tokens_per_tile if self.use_mma else ops.attn_simt_tokens_per_tile
-        return f(self.hq, self.hkv)
+    FOREVER = 1 << 30
+
+    def tile_classes(self, page_size: int):
+        """Entries of several tokens: tiles of the mma.sync (or CUDA-core) kernel, and for portions that fill
+        a 128-row tile of the tcgen05 kernel (head size 128, bfloat16, no window) tiles of that one."""
+        small = (ops.attn_mma_tokens_per_tile if self.use_mma else ops.attn_simt_tokens_per_tile)(self.hq, self.hkv)
+        if ops.attn_tcgen05_supports(self.ctx.dtype, self.d, self.hq, self.hkv, page_size, self.window):
+            big = ops.attn_tcgen05_tokens_per_tile(self.hq, self.hkv)
+            return [(small, 2, big), (big, big, self.FOREVER)]
+        return [(small, 2, self.FOREVER)]
 
     # ----------------------------------------------------------------------- step
     def forward(self, x, step, cache):
@@ -101,12 +110,18 @@ class Attention(Part):
         return ops.linear(out, self.w_o, dt)
 
     def attend(self, qkv, out, step, cache, table):
-        work, n_work = step.tile_work[self.tile_tokens()]
         common = (cache.k, cache.v, table, step.cu_seqlens, step.start_pos)
         kernel = ops.attn_mma if self.use_mma else ops.attn_simt
-        if n_work:
-            kernel(qkv, qkv.stride(0), out, *common, work, n_work, self.hq, self.hkv, self.d,
-                          self.window, self.spec.scale)
+        for cls in self.tile_classes(cache.k.shape[1]):
+            work, n_work = step.tile_work[cls]
+            if not n_work:
+                continue
+            if cls[2] == self.FOREVER and cls[1] > 2:      # the class of whole 128-row tiles
+                ops.attn_tcgen05(qkv, qkv.stride(0), out, *common, work, n_work, self.hq, self.hkv, self.d,
+                                 self.spec.scale)
+            else:
+                kernel(qkv, qkv.stride(0), out, *common, work, n_work, self.hq, self.hkv, self.d, self.window,
+                       self.spec.scale)
         dwork, n_dec = step.decode_work
         if n_dec:
             split = self.ctx.decode_split_size

@@ -10,7 +10,8 @@ which model it sits in.
                     frequencies); rot_dim
     Mixer           forward(x, step, cache) -> y        x, y: [tokens, hidden] compute dtype
                     cache_need() -> PagedKVNeed | FixedStateNeed | None
-                    tile_tokens() -> tokens per attention tile it wants work lists for, or None
+                    tile_classes() -> work lists it wants for entries of several tokens: triples
+                                      (tokens per tile, least new tokens, one more than the most)
     FeedForward     forward(x, step) -> y
     Block           forward(h, delta, step, cache) -> (h, delta)   delta: not yet added to h
 """
@@ -98,7 +99,7 @@ class StepContext:
     logit_rows: torch.Tensor      # [M] token rows whose logits are wanted
     n_logit_rows: int
     block_tables: list            # per cache group: [R, width] page ids (-1 = none)
-    tile_work: dict               # tokens per tile -> (work [n, 2] (entry, first token), n) for entries of >1 token
+    tile_work: dict               # tile class (tokens per tile, least, most+1 new tokens) -> (work [n, 2] (entry, first token), n)
     decode_work: tuple            # (work [n, 2], n) for entries of exactly one token
     max_seq_len: int              # longest start_pos + new tokens in the batch (or the engine's bound, in a graph)
     host_q_lens: list = field(default_factory=list)

@@ -73,13 +73,14 @@ class Model(Part):
         return [self.layers[i].mixer.cache_need() if self.place_cache[k] == k else None
                 for k, i in enumerate(self.order)]
 
-    def tile_token_sizes(self):
-        sizes = set()
+    def tile_classes(self, page_size: int):
+        """The attention work lists that the mixers of this model want (see BatchBuilder)."""
+        classes = set()
         for layer in self.layers:
-            f = getattr(layer.mixer, "tile_tokens", None)
-            if f is not None and f() is not None:
-                sizes.add(f())
-        return sorted(sizes)
+            f = getattr(layer.mixer, "tile_classes", None)
+            if f is not None:
+                classes.update(tuple(c) for c in f(page_size))
+        return sorted(classes)
 
     # ----------------------------------------------------------------------- step
     def forward(self, step, caches) -> torch.Tensor:

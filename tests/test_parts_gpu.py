@@ -95,7 +95,7 @@ def test_attention_mixer_alone(window):
     mixer.bind({k: v.to(DEV) for k, v in w.items()})
     cm = cache.CacheManager([mixer.cache_need()], 8, 16, 2, prefix_cache=False)
     views = cm.allocate_storage(torch.float32, DEV)
-    builder = engine.BatchBuilder(1, 8, [mixer.tile_tokens()], DEV)
+    builder = engine.BatchBuilder(1, 8, mixer.tile_classes(8), DEV)
     x = torch.randn(37, 40, generator=g)
     rc = cm.admit("r")
     outs, i = [], 0

@@ -18,7 +18,7 @@ from tests.util import PAGE_SIZE, TINY, collect, make_folder, portions, prefix_t
 
 pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parent.parent
-LENGTHS = {"a": [70, 45, 100, 33], "b": [90, 38, 64, 51]}
+LENGTHS = {"a": [70, 45, 100, 33], "b": [90, 38, 64, 51], "c": [200, 70, 300, 130]}
 
 
 def limits(dtype, want: torch.Tensor):
@@ -28,7 +28,7 @@ def limits(dtype, want: torch.Tensor):
     return (1e-4 if dtype == "float32" else 3e-2) * scale
 
 
-@pytest.fixture(scope="module", params=["a", "b"])
+@pytest.fixture(scope="module", params=["a", "b", "c"])
 def setup(request, tmp_path_factory):
     tag = request.param
     folder = make_folder(tmp_path_factory.mktemp(f"model_{tag}"), tag, seed=3)
@@ -70,7 +70,7 @@ def test_each_request_alone_and_whole(setup, dtype, tmp_path):
     for rid, toks in seqs.items():
         steps = whole(rid, toks)
         out = tmp_path / rid
-        replay(folder, tag, dtype, steps, out, max_tokens=128)
+        replay(folder, tag, dtype, steps, out, max_tokens=320)
         got, _ = compare(steps, out, TINY[tag]["vocab_size"], want, dtype)
         assert sorted(got[rid]) == list(range(len(toks)))
 
@@ -81,19 +81,22 @@ def test_last_32_tokens_one_by_one(setup, dtype, tmp_path):
     for rid, toks in list(seqs.items())[:3]:
         steps = prefix_then_single(rid, toks, tail=32)
         out = tmp_path / rid
-        replay(folder, tag, dtype, steps, out, max_tokens=128)
+        replay(folder, tag, dtype, steps, out, max_tokens=320)
         compare(steps, out, TINY[tag]["vocab_size"], want, dtype)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("sizes", [(7, 2, 13, 5, 2, 3), (2,), (16, 1, 15, 17), (31, 2, 33)])
+@pytest.mark.parametrize("sizes", [(7, 2, 13, 5, 2, 3), (2,), (16, 1, 15, 17), (31, 2, 33), (64, 3, 130, 2)])
 def test_portions_of_changing_size(setup, dtype, sizes, tmp_path):
     tag, folder, seqs, want = setup
     rid, toks = "r2", seqs["r2"]
     steps = portions(rid, toks, sizes)
-    replay(folder, tag, dtype, steps, tmp_path, max_tokens=128)
+    replay(folder, tag, dtype, steps, tmp_path, max_tokens=320)
     got, _ = compare(steps, tmp_path, TINY[tag]["vocab_size"], want, dtype)
     assert sorted(got[rid]) == list(range(len(toks)))
+
+
+REST = 1 << 20      # "all that is left of the request"
 
 
 def mixed_trace(seqs):
@@ -107,10 +110,10 @@ def mixed_trace(seqs):
         [("r0", 1), ("r1", 1), ("r2", 30), ("r3", 2)],
         [("r0", 24), ("r1", 1), ("r3", 7)],
         [("r0", 1), ("r1", 1), ("r2", 1), ("r3", 1)],
-        [("r1", 100), ("r0", 100)],              # both finish here: their pages go back
-        [("r2", 3), ("r3", 100), ("r4", 40)],    # r4 and r5 repeat r0 and r1 in reused pages
+        [("r1", REST), ("r0", REST)],            # both finish here: their pages go back
+        [("r2", 3), ("r3", REST), ("r4", 40)],   # r4 and r5 repeat r0 and r1 in reused pages
         [("r2", 1), ("r4", 1), ("r5", 2)],
-        [("r2", 100), ("r4", 100), ("r5", 100)],
+        [("r2", REST), ("r4", REST), ("r5", REST)],
     ]
     seqs = dict(seqs, r4=seqs["r0"], r5=seqs["r1"])
     fed.update(r4=0, r5=0)
@@ -153,8 +156,8 @@ def test_schedules_agree_with_each_other_in_32_bit(setup, tmp_path):
     tag, folder, seqs, want = setup
     rid, toks = "r0", seqs["r0"]
     vocab = TINY[tag]["vocab_size"]
-    a = whole(rid, toks); replay(folder, tag, "float32", a, tmp_path / "a", 128)
-    b = portions(rid, toks, (3, 2, 11)); replay(folder, tag, "float32", b, tmp_path / "b", 128)
+    a = whole(rid, toks); replay(folder, tag, "float32", a, tmp_path / "a", 320)
+    b = portions(rid, toks, (3, 2, 11)); replay(folder, tag, "float32", b, tmp_path / "b", 320)
     ga, gb = collect(a, tmp_path / "a", vocab)[rid], collect(b, tmp_path / "b", vocab)[rid]
     worst = max(np.abs(ga[p] - gb[p]).max() for p in ga)
     assert worst <= 2e-5 * max(1.0, want[rid].abs().max().item())

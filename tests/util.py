@@ -18,8 +18,13 @@ TINY_A = dict(architectures=["Qwen3ForCausalLM"], vocab_size=256, hidden_size=64
 TINY_B = dict(architectures=["Qwen3ForCausalLM"], vocab_size=384, hidden_size=96, intermediate_size=224,
               num_hidden_layers=3, num_attention_heads=6, num_key_value_heads=1, head_dim=32, rms_norm_eps=1e-5,
               rope_theta=1e6, max_position_embeddings=512, tie_word_embeddings=False)
-TINY = {"a": TINY_A, "b": TINY_B}
-PAGE_SIZE = {"a": 16, "b": 8}
+# A third one with the head size (128) and the feed-forward width (a multiple of 128) at which the bfloat16
+# path takes its tcgen05 kernels (prompt attention in tensor memory, the gate in the product's epilogue).
+TINY_C = dict(architectures=["Qwen3ForCausalLM"], vocab_size=300, hidden_size=192, intermediate_size=384,
+              num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=128, rms_norm_eps=1e-6,
+              rope_theta=5e5, max_position_embeddings=1024, tie_word_embeddings=False)
+TINY = {"a": TINY_A, "b": TINY_B, "c": TINY_C}
+PAGE_SIZE = {"a": 16, "b": 8, "c": 16}
 
 
 def tensor_shapes(c: dict) -> dict:
