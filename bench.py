@@ -241,7 +241,10 @@ def micro(spec: str, reps: int) -> int:
     """One kernel alone on data larger than the L2, for profiling:
     gemm:<N>x<K>:<M>:<impl>  the prompt product, impl = tcgen05 | tcgen05_swiglu | library (cuBLAS)
     linear:<N>x<K>:<M>   the decode product of M rows with an [N, K] weight (several weights in turn)
-    attn_decode:<B>:<CTX>   split decode attention of B requests with CTX cached tokens (8B head layout)
+    attn_decode:<B>:<CTX>[:<SPLIT>[:<PAGE>[:<KV HEADS>]]]   split decode attention of B requests with CTX cached tokens (8B head layout,
+                         several caches in turn so that none stays in the L2), mma.sync kernel
+    attn_decode_tcgen05:<B>:<CTX>[:<SPLIT>[:<PAGE>]]   the same with the tcgen05 kernel
+    (the decode kernels are timed as replays of a CUDA graph of one launch per cache, as the engine runs them)
     attn_prefill:<T>     prompt attention of one request of T tokens (8B head layout), mma.sync kernel
     attn_prefill_tcgen05:<T>   the same with the tcgen05 kernel"""
     import torch
@@ -280,8 +283,12 @@ def micro(spec: str, reps: int) -> int:
         nbytes = n * k * 2
     else:
         hq, hkv, d, page = 32, 8, 128, PAGE
-        if kind == "attn_decode":
+        if kind.startswith("attn_decode"):
             b, ctx = int(rest[0]), int(rest[1])
+            split = int(rest[2]) if len(rest) > 2 else 256
+            page = int(rest[3]) if len(rest) > 3 else PAGE
+            if len(rest) > 4:
+                hkv = int(rest[4]); hq = 4 * hkv
             q_lens = [1] * b
         else:
             b, ctx, q_lens = 1, 0, [int(rest[0])]
@@ -293,18 +300,25 @@ def micro(spec: str, reps: int) -> int:
         for e in range(b):
             for i in range(pages_per[e]):
                 table[e, i] = perm.pop()
-        kc = torch.randn(num_pages, page, hkv, d, device=dev).to(torch.bfloat16)
-        vc = torch.randn(num_pages, page, hkv, d, device=dev).to(torch.bfloat16)
+        copies = max(1, int(300e6 // (num_pages * page * hkv * d * 4))) + 1 if kind.startswith("attn_decode") else 1
+        kcs = [torch.randn(num_pages, page, hkv, d, device=dev).to(torch.bfloat16) for _ in range(copies)]
+        vcs = [torch.randn(num_pages, page, hkv, d, device=dev).to(torch.bfloat16) for _ in range(copies)]
+        kc, vc = kcs[0], vcs[0]
         n_tok = sum(q_lens)
         q = torch.randn(n_tok, hq * d, device=dev).to(torch.bfloat16)
         out = torch.empty_like(q)
         cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32, device=dev)
         st = torch.tensor([ctx] * b, dtype=torch.int32, device=dev)
         common = (kc, vc, table.to(dev), cu, st)
-        if kind == "attn_decode":
+        if kind.startswith("attn_decode"):
             work = torch.tensor([[e, 0] for e in range(b)], dtype=torch.int32, device=dev)
-            run = lambda i: ops.attn_mma(q, hq * d, out, *common, work, b, hq, hkv, d, 0, d ** -0.5, split_size=256,
-                                         n_splits=-(-max(total) // 256))
+            n_splits = -(-max(total) // split)
+            if kind == "attn_decode_tcgen05":
+                run = lambda i: ops.attn_decode_tcgen05(q, hq * d, out, kcs[i % copies], vcs[i % copies], *common[2:], work,
+                                                        b, hq, hkv, d, d ** -0.5)
+            else:
+                run = lambda i: ops.attn_mma(q, hq * d, out, kcs[i % copies], vcs[i % copies], *common[2:], work, b, hq,
+                                             hkv, d, 0, d ** -0.5, split_size=split, n_splits=n_splits)
         elif kind == "attn_prefill_tcgen05":
             tpt = ops.attn_tcgen05_tokens_per_tile(hq, hkv)
             work = torch.tensor([[0, t] for t in range(0, q_lens[0], tpt)], dtype=torch.int32, device=dev)
@@ -317,11 +331,25 @@ def micro(spec: str, reps: int) -> int:
     for i in range(3):
         run(i)
     torch.cuda.synchronize()
-    start.record()
-    for i in range(reps):
-        run(i)
-    end.record()
+    if kind.startswith("attn_decode"):
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for i in range(copies):
+                run(i)
+        graph.replay()
+        torch.cuda.synchronize()
+        start.record()
+        for i in range(reps):
+            graph.replay()
+        end.record()
+        reps *= copies
+    else:
+        start.record()
+        for i in range(reps):
+            run(i)
+        end.record()
     torch.cuda.synchronize()
+    ops.check_status()
     us = start.elapsed_time(end) / reps * 1e3
     print(json.dumps({"micro": spec, "us": round(us, 2), "GB/s": round(nbytes / us / 1e3, 1)}))
     return 0

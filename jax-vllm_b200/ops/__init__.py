@@ -336,6 +336,56 @@ def attn_tcgen05(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cache: tor
              status_word(q.device).data_ptr(), _stream()), "attn_tcgen05")
 
 
+DECODE_TCGEN05_MAX_REQUESTS = 512
+
+
+def attn_decode_tcgen05_supports(dtype: torch.dtype, head_dim: int, n_q_heads: int, n_kv_heads: int, page_size: int,
+                                 window: int, n_requests: int = 1) -> bool:
+    """Whether the tcgen05 decode-attention kernel takes the case (csrc/attn_decode_tcgen05.cu)."""
+    return (dtype == torch.bfloat16 and head_dim == 128 and not window and n_kv_heads > 0
+            and n_q_heads % n_kv_heads == 0 and n_q_heads // n_kv_heads <= 16
+            and n_requests <= DECODE_TCGEN05_MAX_REQUESTS and page_size in (8, 16, 32, 64, 128))
+
+
+_sm_count: dict = {}
+
+
+def _multiprocessors(device) -> int:
+    idx = torch.device(device).index or 0
+    if idx not in _sm_count:
+        _sm_count[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
+    return _sm_count[idx]
+
+
+def attn_decode_tcgen05(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                        block_table: torch.Tensor, cu_seqlens: torch.Tensor, start_pos: torch.Tensor,
+                        work: torch.Tensor, n_work: int, n_q_heads: int, n_kv_heads: int, head_dim: int,
+                        scale: float) -> None:
+    """Decode attention (single tokens) with the keys of a tile as tensor-core rows and scores and output in
+    tensor memory; one persistent launch shares the key tiles of all requests evenly among the
+    multiprocessors (csrc/attn_decode_tcgen05.cu).  `work`, `cu_seqlens`, `start_pos` as for `attn_mma`."""
+    for t, nm in ((q, "q"), (out, "out"), (k_cache, "k_cache"), (v_cache, "v_cache")):
+        _cuda(t, nm, torch.bfloat16, contiguous=(nm != "q"))
+    for t, nm in ((block_table, "block_table"), (cu_seqlens, "cu_seqlens"), (start_pos, "start_pos"), (work, "work")):
+        _cuda(t, nm, torch.int32)
+    if n_work == 0:
+        return
+    n_blocks = _multiprocessors(q.device)
+    slots = n_work * n_kv_heads + n_blocks
+    g = n_q_heads // max(n_kv_heads, 1)
+    part_o = torch.empty(slots * g * head_dim, dtype=torch.float32, device=q.device)
+    part_ml = torch.empty(slots * g * 2, dtype=torch.float32, device=q.device)
+    counters = _split_counters(q.device, n_work * n_kv_heads)
+    f = _fn("attn_decode_tcgen05", "jv_attn_decode_tcgen05",
+            [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+             c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p])
+    _check(f(q.data_ptr(), q_stride, q.shape[0], out.data_ptr(), out.stride(0), part_o.data_ptr(), part_ml.data_ptr(),
+             counters.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_table.data_ptr(), block_table.shape[1],
+             cu_seqlens.data_ptr(), start_pos.data_ptr(), work.data_ptr(), n_work, n_q_heads, n_kv_heads, head_dim,
+             k_cache.shape[1], k_cache.shape[0], float(scale), n_blocks, status_word(q.device).data_ptr(), _stream()),
+           "attn_decode_tcgen05")
+
+
 # --------------------------------------------------------------------------- linear
 def gemm_simt(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
     """x [M, K] times weight [N, K] transposed, accumulated in float32 on CUDA cores."""

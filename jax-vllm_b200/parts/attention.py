@@ -43,7 +43,7 @@ class Attention(Part):
         if self.use_mma:
             self.kernels = ("rope_kv", "attn_mma", "gemm_simt", "linear_skinny")
             if self.d == 128 and not self.window:
-                self.kernels += ("attn_tcgen05",)
+                self.kernels += ("attn_tcgen05", "attn_decode_tcgen05")
         self.w_qkv = self.w_o = self.q_norm = self.k_norm = None
 
     # -------------------------------------------------------------------- weights
@@ -123,7 +123,12 @@ class Attention(Part):
                 kernel(qkv, qkv.stride(0), out, *common, work, n_work, self.hq, self.hkv, self.d, self.window,
                        self.spec.scale)
         dwork, n_dec = step.decode_work
-        if n_dec:
+        if n_dec and ops.attn_decode_tcgen05_supports(self.ctx.dtype, self.d, self.hq, self.hkv, cache.k.shape[1],
+                                                      self.window, n_dec):
+            # single tokens, head size 128: one persistent launch over the key tiles of all requests
+            ops.attn_decode_tcgen05(qkv, qkv.stride(0), out, *common, dwork, n_dec, self.hq, self.hkv, self.d,
+                                    self.spec.scale)
+        elif n_dec:
             split = self.ctx.decode_split_size
             n_splits = max(1, -(-step.max_seq_len // split))
             kernel(qkv, qkv.stride(0), out, *common, dwork, n_dec, self.hq, self.hkv, self.d,

@@ -267,7 +267,7 @@ def dense_attention(q, k_all, v_all, q_pos, scale, window, g):
 
 
 def run_attention(ops, dtype, hq, hkv, d, page, q_lens, starts, window=0, split=0, seed=6, boost=None, mma=False,
-                  tc5=False):
+                  tc5=False, dec5=False, large=None):
     g = torch.Generator().manual_seed(seed)
     G = hq // hkv
     R, n = len(q_lens), sum(q_lens)
@@ -285,6 +285,8 @@ def run_attention(ops, dtype, hq, hkv, d, page, q_lens, starts, window=0, split=
         v = torch.randn(total[e], hkv, d, generator=g).to(dtype).float()
         if boost is not None and e == boost[0]:
             k[boost[1]] *= 6.0                                        # one far key that the last query must find
+        if large is not None and (large[0] is None or e == large[0]):
+            k[large[1]:] *= large[2]                                  # scores grow late: the running maximum must move
         ks.append(k); vs.append(v)
         for i in range(pages_per[e]):
             pg = perm.pop()
@@ -310,8 +312,11 @@ def run_attention(ops, dtype, hq, hkv, d, page, q_lens, starts, window=0, split=
     if split:
         assert all(ql == 1 for ql in q_lens)
         work = torch.tensor([[e, 0] for e in range(R)], dtype=torch.int32, device=DEV)
-        attn(dq, hq * d, out, *common, work, R, hq, hkv, d, window, scale, split_size=split,
-             n_splits=-(-max(total) // split))
+        if dec5:
+            ops.attn_decode_tcgen05(dq, hq * d, out, *common, work, R, hq, hkv, d, scale)
+        else:
+            attn(dq, hq * d, out, *common, work, R, hq, hkv, d, window, scale, split_size=split,
+                 n_splits=-(-max(total) // split))
     else:
         work = torch.tensor([[e, t] for e in range(R) for t in range(0, q_lens[e], tpt)], dtype=torch.int32, device=DEV)
         if tc5:
@@ -414,6 +419,57 @@ def test_tcgen05_attention_finds_one_far_key_among_hundreds(ops, far):
 def test_tcgen05_attention_long_prompt(ops):
     got, want = run_attention(ops, torch.bfloat16, 8, 2, 128, 16, q_lens=[1000], starts=[0], tc5=True)
     torch.testing.assert_close(got, want, **BF16_TOL)
+
+
+# ---- the tcgen05 decode kernel (bfloat16, head size 128, keys as tensor-core rows, persistent over all requests)
+@pytest.mark.parametrize("hq,hkv,page", [(4, 1, 16), (32, 8, 16), (8, 8, 8), (2, 1, 128), (16, 1, 32), (6, 2, 64), (5, 1, 16),
+                                         (12, 1, 16)])
+def test_tcgen05_decode_attention(ops, hq, hkv, page):
+    got, want = run_attention(ops, torch.bfloat16, hq, hkv, 128, page, q_lens=[1, 1, 1, 1, 1, 1],
+                              starts=[0, 31, 300, 127, 1500, 1023], split=1, dec5=True)
+    torch.testing.assert_close(got, want, **BF16_TOL)
+
+
+@pytest.mark.parametrize("starts", [[5], [127], [128], [40000], [20000, 3, 0, 129]])
+def test_tcgen05_decode_attention_short_and_long(ops, starts):
+    # one tile for the whole launch, one more key than a tile, and pairs that span many blocks
+    got, want = run_attention(ops, torch.bfloat16, 8, 2, 128, 16, q_lens=[1] * len(starts), starts=starts, split=1, dec5=True)
+    torch.testing.assert_close(got, want, **BF16_TOL)
+
+
+@pytest.mark.parametrize("far", [0, 3, 130, 511, 1290])
+def test_tcgen05_decode_attention_finds_one_far_key(ops, far):
+    got, want = run_attention(ops, torch.bfloat16, 4, 2, 128, 16, q_lens=[1, 1], starts=[10, 1299], split=1,
+                              boost=(1, far), dec5=True)
+    torch.testing.assert_close(got, want, **BF16_TOL)
+
+
+@pytest.mark.parametrize("from_key", [100, 128, 200, 700])
+def test_tcgen05_decode_attention_moves_its_reference_when_scores_grow_late(ops, from_key):
+    # keys from `from_key` on are four times larger, so scores there exceed the first tiles' maxima by far more
+    # than the slack of the lazy rescaling: the accumulated output and the sums must be rescaled.  One kv head
+    # and few requests make a block's run of tiles long enough to hold the change.
+    got, want = run_attention(ops, torch.bfloat16, 8, 1, 128, 16, q_lens=[1] * 150, starts=[899] * 150, split=1,
+                              large=(None, from_key, 4.0), dec5=True)
+    torch.testing.assert_close(got, want, **BF16_TOL)
+
+
+def test_tcgen05_decode_attention_twice_in_a_row_and_many_requests(ops):
+    starts = [(37 * i) % 700 for i in range(300)]
+    for seed in (1, 2):
+        got, want = run_attention(ops, torch.bfloat16, 8, 2, 128, 16, q_lens=[1] * 300, starts=starts, split=1, seed=seed,
+                                  dec5=True)
+        torch.testing.assert_close(got, want, **BF16_TOL)
+
+
+def test_tcgen05_decode_support_rules(ops):
+    from jax_vllm_b200.csrc import build
+    lib = build.load("attn_decode_tcgen05")
+    for d, hq, hkv, page, window, n in [(128, 32, 8, 16, 0, 8), (64, 32, 8, 16, 0, 8), (128, 6, 1, 16, 0, 1),
+                                        (128, 32, 8, 4, 0, 8), (128, 32, 8, 16, 5, 8), (128, 16, 1, 128, 0, 512),
+                                        (128, 20, 1, 16, 0, 8), (128, 32, 8, 16, 0, 513)]:
+        assert bool(lib.jv_attn_decode_tcgen05_supports(d, hq, hkv, page, window, n)) == \
+            ops.attn_decode_tcgen05_supports(torch.bfloat16, d, hq, hkv, page, window, n)
 
 
 def test_tcgen05_support_rules(ops):
