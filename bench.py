@@ -240,7 +240,7 @@ def time_e2e(model, batch, steps, warmup, ctx=CONTEXT):
 def micro(spec: str, reps: int) -> int:
     """One kernel alone on data larger than the L2, for profiling:
     gemm:<N>x<K>:<M>:<impl>  the prompt product, impl = tcgen05 | tcgen05_swiglu | library (cuBLAS)
-    linear:<N>x<K>:<M>   the decode product of M rows with an [N, K] weight (several weights in turn)
+    linear:<N>x<K>:<M>[:parts]   the decode product of M rows with an [N, K] weight (several weights in turn)
     attn_decode:<B>:<CTX>[:<SPLIT>[:<PAGE>[:<KV HEADS>]]]   split decode attention of B requests with CTX cached tokens (8B head layout,
                          several caches in turn so that none stays in the L2), mma.sync kernel
     attn_decode_tcgen05:<B>:<CTX>[:<SPLIT>[:<PAGE>]]   the same with the tcgen05 kernel
@@ -279,7 +279,8 @@ def micro(spec: str, reps: int) -> int:
         copies = max(2, int(400e6 // (n * k * 2)) + 1)
         ws = [(torch.randn(n, k, device=dev) * 0.02).to(torch.bfloat16) for _ in range(copies)]
         x = torch.randn(m, k, device=dev).to(torch.bfloat16)
-        run = lambda i: ops.linear(x, ws[i % copies])
+        parts_ok = len(rest) > 2 and rest[2] == "parts"       # let the kernel cut k and leave the parts of a sum
+        run = lambda i: ops.linear(x, ws[i % copies], parts_ok=parts_ok)
         nbytes = n * k * 2
     else:
         hq, hkv, d, page = 32, 8, 128, PAGE
@@ -331,7 +332,7 @@ def micro(spec: str, reps: int) -> int:
     for i in range(3):
         run(i)
     torch.cuda.synchronize()
-    if kind.startswith("attn_decode"):
+    if kind.startswith("attn_decode") or kind == "linear":
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
             for i in range(copies):

@@ -50,11 +50,53 @@ __global__ void swiglu_vec_kernel(const T* __restrict__ gu, T* __restrict__ act,
   }
 }
 
+// The same for a gate|up given as `parts` 32-bit tensors [n, 2*inter] `part_stride` elements apart, whose sum it is
+// (the sums over the parts of k that a split product leaves), four columns per thread and pass.
+template <typename T>
+__global__ void swiglu_parts_kernel(const float* __restrict__ gu, T* __restrict__ act, int inter, int block, size_t total_vec,
+                                    int parts, size_t part_stride) {
+  pdl_trigger();
+  pdl_wait();
+  const int vec_per_row = inter / 4;
+  size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; idx < total_vec; idx += stride) {
+    const size_t n = idx / vec_per_row;
+    const int i = (int)(idx - n * vec_per_row) * 4;
+    const size_t col = (size_t)(i / block) * 2 * block + (i % block);
+    const float* src = gu + n * 2 * inter + col;
+    float4 g = *reinterpret_cast<const float4*>(src), u = *reinterpret_cast<const float4*>(src + block);
+    for (int s = 1; s < parts; ++s) {
+      const float4 g2 = *reinterpret_cast<const float4*>(src + s * part_stride);
+      const float4 u2 = *reinterpret_cast<const float4*>(src + s * part_stride + block);
+      g.x += g2.x; g.y += g2.y; g.z += g2.z; g.w += g2.w;
+      u.x += u2.x; u.y += u2.y; u.z += u2.z; u.w += u2.w;
+    }
+    T* dst = act + n * inter + i;
+    dst[0] = from_f32<T>(g.x / (1.f + expf(-g.x)) * u.x);
+    dst[1] = from_f32<T>(g.y / (1.f + expf(-g.y)) * u.y);
+    dst[2] = from_f32<T>(g.z / (1.f + expf(-g.z)) * u.z);
+    dst[3] = from_f32<T>(g.w / (1.f + expf(-g.w)) * u.w);
+  }
+}
+
 // gu: [n, 2*inter]; act: [n, inter]; both of dtype `dtype`; block: see above (a divisor of inter).
-JV_EXPORT int jv_swiglu(const void* gu, void* act, int dtype, int n, int inter, int block, cudaStream_t stream) {
+// parts > 1: gu is `parts` float tensors [n, 2*inter], part_stride elements apart, and act is of dtype `dtype`
+// (block and part_stride multiples of 4, gu 16-byte aligned).
+JV_EXPORT int jv_swiglu(const void* gu, void* act, int dtype, int n, int inter, int block, int parts, long long part_stride,
+                        cudaStream_t stream) {
   const size_t total = (size_t)n * inter;
   if (total == 0) return JV_OK;
-  if (block < 1 || inter % block) return JV_ERR_UNSUPPORTED;
+  if (block < 1 || inter % block || parts < 1) return JV_ERR_UNSUPPORTED;
+  if (parts > 1) {
+    if ((block % 4) || (part_stride % 4) || ((uintptr_t)gu % 16)) return JV_ERR_UNSUPPORTED;
+    const size_t total_vec = total / 4;
+    size_t blocks = (total_vec + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    JV_DISPATCH_DTYPE(dtype, T, return jv_launch(swiglu_parts_kernel<T>, dim3((int)blocks), dim3(256), 0, stream,
+                                                  (const float*)gu, (T*)act, inter, block, total_vec, parts, (size_t)part_stride));
+    return JV_ERR_UNSUPPORTED;
+  }
   const int vec = dtype == 0 ? 4 : 8;
   if (block % vec == 0 && ((uintptr_t)gu % 16) == 0 && ((uintptr_t)act % 16) == 0) {
     const size_t total_vec = total / vec;

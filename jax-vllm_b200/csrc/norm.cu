@@ -1,7 +1,9 @@
 // RMSNorm over rows of the 32-bit residual stream, optionally fused with the residual
 // sum that precedes it and with a row gather.
 //
-//   h[r, :] += delta[r, :]           (if delta is given; the sum is kept in 32-bit)
+//   h[r, :] += delta[r, :]           (if delta is given; the sum is kept in 32-bit.  delta may come as
+//                                     `parts` tensors `part_stride` elements apart, added in order: the
+//                                     sums over the parts of k that a split product leaves)
 //   y[i, :]  = h[r, :] * rsqrt(mean(h[r, :]^2) + eps) * weight[:]
 //
 // with r = rows[i] if `rows` is given, else r = i.  When `rows` is given the sum is
@@ -14,7 +16,7 @@ template <typename TD, typename TW, typename TY>
 __global__ void rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__ delta,
                                const int* __restrict__ rows, const TW* __restrict__ weight,
                                TY* __restrict__ y, int hidden, float eps, int n_rows_total,
-                               int* __restrict__ status) {
+                               int* __restrict__ status, int parts, size_t part_stride) {
   __shared__ float scratch[33];
   pdl_trigger();
   pdl_wait();
@@ -32,9 +34,14 @@ __global__ void rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__ del
   const TD* dr = delta ? delta + (size_t)r * hidden : nullptr;
   const bool write_back = (dr != nullptr) && (rows == nullptr);
   float ss = 0.f;
+  auto delta_at = [&](int c) {
+    float d = to_f32(dr[c]);
+    for (int s = 1; s < parts; ++s) d += to_f32(dr[s * part_stride + c]);
+    return d;
+  };
   for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
     float v = hr[c];
-    if (dr) v += to_f32(dr[c]);
+    if (dr) v += delta_at(c);
     if (write_back) hr[c] = v;
     ss += v * v;
   }
@@ -43,7 +50,7 @@ __global__ void rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__ del
   TY* yr = y + (size_t)i * hidden;
   for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
     float v = hr[c];                          // this thread's own write, if any
-    if (dr && !write_back) v += to_f32(dr[c]);
+    if (dr && !write_back) v += delta_at(c);
     yr[c] = from_f32<TY>(v * inv * to_f32(weight[c]));
   }
 }
@@ -80,7 +87,7 @@ template <typename TD, typename TW, typename TY>
 __global__ void rmsnorm_vec_kernel(float* __restrict__ h, const TD* __restrict__ delta,
                                    const int* __restrict__ rows, const TW* __restrict__ weight,
                                    TY* __restrict__ y, int hidden, float eps, int n_rows_total,
-                                   int* __restrict__ status) {
+                                   int* __restrict__ status, int parts, size_t part_stride) {
   __shared__ float scratch[33];
   pdl_trigger();
   pdl_wait();
@@ -107,6 +114,12 @@ __global__ void rmsnorm_vec_kernel(float* __restrict__ h, const TD* __restrict__
       if (dr) {
         float d[8];
         load8<TD>(dr + c, d);
+        for (int s = 1; s < parts; ++s) {
+          float e[8];
+          load8<TD>(dr + s * part_stride + c, e);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) d[k] += e[k];
+        }
 #pragma unroll
         for (int k = 0; k < 8; ++k) v[it][k] += d[k];
         if (write_back) store8<float>(hr + c, v[it]);
@@ -132,12 +145,17 @@ __global__ void rmsnorm_vec_kernel(float* __restrict__ h, const TD* __restrict__
 }
 
 // h: [n_total, hidden] float (updated in place when delta is given and rows is null);
-// delta: [n_total, hidden] of dtype `delta_dtype` or null; rows: [n_out] int32 or null;
+// delta: [n_total, hidden] of dtype `delta_dtype` or null, or `delta_parts` such tensors `delta_part_stride`
+// elements apart whose sum it is; rows: [n_out] int32 or null;
 // weight: [hidden] of dtype `weight_dtype`; y: [n_out, hidden] of dtype `out_dtype`.
 JV_EXPORT int jv_rmsnorm(float* h, const void* delta, int delta_dtype, const int* rows,
                          const void* weight, int weight_dtype, void* y, int out_dtype, int n_out,
-                         int n_total, int hidden, float eps, int* status, cudaStream_t stream) {
+                         int n_total, int hidden, float eps, int delta_parts, long long delta_part_stride, int* status,
+                         cudaStream_t stream) {
   if (n_out == 0) return JV_OK;
+  if (delta_parts < 1 || (delta_part_stride % 8)) return JV_ERR_UNSUPPORTED;
+  const int parts = delta_parts;
+  const size_t part_stride = (size_t)delta_part_stride;
   const bool aligned = ((uintptr_t)h % 16) == 0 && ((uintptr_t)delta % 16) == 0 && ((uintptr_t)weight % 16) == 0 &&
                        ((uintptr_t)y % 16) == 0;
   if (hidden % 8 == 0 && hidden <= 1024 * 8 * RM_ITERS && aligned) {
@@ -148,33 +166,41 @@ JV_EXPORT int jv_rmsnorm(float* h, const void* delta, int delta_dtype, const int
     if (vthreads > 1024) vthreads = 1024;
     JV_DISPATCH_DTYPE(out_dtype, TY, JV_DISPATCH_DTYPE(weight_dtype, TW, JV_DISPATCH_DTYPE(delta_dtype, TD,
         return jv_launch(rmsnorm_vec_kernel<TD, TW, TY>, dim3(n_out), dim3(vthreads), 0, stream,
-                         h, (const TD*)delta, rows, (const TW*)weight, (TY*)y, hidden, eps, n_total, status))));
+                         h, (const TD*)delta, rows, (const TW*)weight, (TY*)y, hidden, eps, n_total, status, parts, part_stride))));
     return JV_ERR_UNSUPPORTED;
   }
   int threads = 32;
   while (threads < 512 && threads * 4 < hidden) threads *= 2;
   JV_DISPATCH_DTYPE(out_dtype, TY, JV_DISPATCH_DTYPE(weight_dtype, TW, JV_DISPATCH_DTYPE(delta_dtype, TD,
       return jv_launch(rmsnorm_kernel<TD, TW, TY>, dim3(n_out), dim3(threads), 0, stream,
-                       h, (const TD*)delta, rows, (const TW*)weight, (TY*)y, hidden, eps, n_total, status))));
+                       h, (const TD*)delta, rows, (const TW*)weight, (TY*)y, hidden, eps, n_total, status, parts, part_stride))));
   return JV_ERR_UNSUPPORTED;
 }
 
 // Adds delta into the 32-bit stream without a norm: h[r, :] += delta[r, :].
 template <typename TD>
-__global__ void residual_add_kernel(float* __restrict__ h, const TD* __restrict__ delta, size_t n) {
+__global__ void residual_add_kernel(float* __restrict__ h, const TD* __restrict__ delta, size_t n, int parts,
+                                    size_t part_stride) {
   pdl_trigger();
   pdl_wait();
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
-  for (; i < n; i += stride) h[i] += to_f32(delta[i]);
+  for (; i < n; i += stride) {
+    float d = to_f32(delta[i]);
+    for (int s = 1; s < parts; ++s) d += to_f32(delta[s * part_stride + i]);
+    h[i] += d;
+  }
 }
 
-JV_EXPORT int jv_residual_add(float* h, const void* delta, int delta_dtype, long long n,
-                              cudaStream_t stream) {
+// delta as for jv_rmsnorm: one tensor (delta_parts 1) or the parts of a sum.
+JV_EXPORT int jv_residual_add(float* h, const void* delta, int delta_dtype, long long n, int delta_parts,
+                              long long delta_part_stride, cudaStream_t stream) {
   if (n == 0) return JV_OK;
+  if (delta_parts < 1) return JV_ERR_UNSUPPORTED;
   long long blocks = (n + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
   JV_DISPATCH_DTYPE(delta_dtype, TD, return jv_launch(residual_add_kernel<TD>, dim3((int)blocks), dim3(256), 0, stream,
-                                                      h, (const TD*)delta, (size_t)n));
+                                                      h, (const TD*)delta, (size_t)n, delta_parts,
+                                                      (size_t)delta_part_stride));
   return JV_ERR_UNSUPPORTED;
 }

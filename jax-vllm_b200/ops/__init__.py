@@ -26,6 +26,29 @@ class KernelError(RuntimeError):
     pass
 
 
+class PartialSum:
+    """A result [n, width] that is given as `parts` [S, n, width] float32 and is their sum over S: what a
+    product leaves whose k was cut into S parts for an even load (`linear(..., parts_ok=True)`).  `rmsnorm`
+    and `residual_add` take it as `delta` and `swiglu` as its input and add the parts, in order, as they
+    read them; `tensor()` adds them up for any other reader."""
+
+    def __init__(self, parts: torch.Tensor):
+        self.parts = parts
+
+    @property
+    def shape(self):
+        return self.parts.shape[1:]
+
+    @property
+    def device(self):
+        return self.parts.device
+
+    def tensor(self, dtype: torch.dtype = torch.float32) -> torch.Tensor:
+        out = torch.zeros(tuple(self.shape), dtype=torch.float32, device=self.device)
+        residual_add(out, self)
+        return out if dtype == torch.float32 else out.to(dtype)
+
+
 _fn_cache: dict[tuple[str, str], object] = {}
 launch_count = 0     # kernels of this package launched so far (library products are not counted)
 _status: dict[int, torch.Tensor] = {}
@@ -131,46 +154,70 @@ def rmsnorm(h: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.
     n_total, hidden = h.shape
     if weight.shape != (hidden,):
         raise KernelError(f"norm weight has shape {tuple(weight.shape)}, rows have {hidden} elements")
-    if delta is not None:
-        _cuda(delta, "delta")
-        if delta.shape != h.shape:
-            raise KernelError("delta and h differ in shape")
+    delta, n_parts, part_stride = _delta_parts(delta, h)
     if rows is not None:
         _cuda(rows, "rows", torch.int32)
     n_out = n_total if rows is None else rows.numel()
     y = torch.empty((n_out, hidden), dtype=out_dtype, device=h.device)
     f = _fn("norm", "jv_rmsnorm", [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int,
-                                   c_int, c_int, c_int, c_float, c_void_p, c_void_p])
+                                   c_int, c_int, c_int, c_float, c_int, c_longlong, c_void_p, c_void_p])
     _check(f(h.data_ptr(), _ptr(delta), 0 if delta is None else _code(delta, "delta"), _ptr(rows),
              weight.data_ptr(), _code(weight, "weight"), y.data_ptr(), _code(y, "out"), n_out, n_total, hidden,
-             float(eps), status_word(h.device).data_ptr(), _stream()), "rmsnorm")
+             float(eps), n_parts, part_stride, status_word(h.device).data_ptr(), _stream()), "rmsnorm")
     return y
 
 
-def residual_add(h: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
-    """h += delta, the sum kept in float32."""
-    _cuda(h, "h", torch.float32); _cuda(delta, "delta")
+def _delta_parts(delta, h: torch.Tensor):
+    """(tensor, parts, elements between parts) for a `delta` that is a tensor, a PartialSum or None."""
+    if delta is None:
+        return None, 1, 0
+    if isinstance(delta, PartialSum):
+        parts = _cuda(delta.parts, "delta parts", torch.float32)
+        if tuple(parts.shape[1:]) != tuple(h.shape):
+            raise KernelError("delta and h differ in shape")
+        return parts, parts.shape[0], parts.stride(0)
+    _cuda(delta, "delta")
     if delta.shape != h.shape:
         raise KernelError("delta and h differ in shape")
-    f = _fn("norm", "jv_residual_add", [c_void_p, c_void_p, c_int, c_longlong, c_void_p])
-    _check(f(h.data_ptr(), delta.data_ptr(), _code(delta, "delta"), h.numel(), _stream()), "residual_add")
+    return delta, 1, 0
+
+
+def residual_add(h: torch.Tensor, delta) -> torch.Tensor:
+    """h += delta (a tensor or a PartialSum), the sum kept in float32."""
+    _cuda(h, "h", torch.float32)
+    delta, n_parts, part_stride = _delta_parts(delta, h)
+    f = _fn("norm", "jv_residual_add", [c_void_p, c_void_p, c_int, c_longlong, c_int, c_longlong, c_void_p])
+    _check(f(h.data_ptr(), delta.data_ptr(), _code(delta, "delta"), h.numel(), n_parts, part_stride, _stream()),
+           "residual_add")
     return h
 
 
 # ----------------------------------------------------------------------- activation
-def swiglu(gate_up: torch.Tensor, block: int | None = None) -> torch.Tensor:
+def swiglu(gate_up, block: int | None = None, out_dtype: torch.dtype | None = None) -> torch.Tensor:
     """silu(gate) * up for a packed [n, 2*inter] tensor: blocks of `block` gate columns, each followed
-    by the up columns of the same indices (default: all gate columns first)."""
-    _cuda(gate_up, "gate_up")
-    n, two_i = gate_up.shape
+    by the up columns of the same indices (default: all gate columns first).  The input may be a
+    PartialSum; the result then has `out_dtype`."""
+    n_parts, part_stride = 1, 0
+    if isinstance(gate_up, PartialSum):
+        if out_dtype is None:
+            raise KernelError("swiglu of a PartialSum needs out_dtype")
+        gate_up = _cuda(gate_up.parts, "gate_up parts", torch.float32)
+        n_parts, part_stride = gate_up.shape[0], gate_up.stride(0)
+        n, two_i = gate_up.shape[1:]
+        act_dtype = out_dtype
+    else:
+        _cuda(gate_up, "gate_up")
+        n, two_i = gate_up.shape
+        act_dtype = gate_up.dtype
     if two_i % 2:
         raise KernelError("packed gate|up needs an even number of columns")
     block = two_i // 2 if block is None else int(block)
     if block < 1 or (two_i // 2) % block:
         raise KernelError(f"gate|up block {block} does not divide {two_i // 2} columns")
-    act = torch.empty((n, two_i // 2), dtype=gate_up.dtype, device=gate_up.device)
-    f = _fn("activation", "jv_swiglu", [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
-    _check(f(gate_up.data_ptr(), act.data_ptr(), _code(gate_up, "gate_up"), n, two_i // 2, block, _stream()), "swiglu")
+    act = torch.empty((n, two_i // 2), dtype=act_dtype, device=gate_up.device)
+    f = _fn("activation", "jv_swiglu", [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_longlong, c_void_p])
+    _check(f(gate_up.data_ptr(), act.data_ptr(), _code(act, "act"), n, two_i // 2, block, n_parts, part_stride, _stream()),
+           "swiglu")
     return act
 
 
@@ -405,20 +452,44 @@ def gemm_simt(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype) -> 
 SKINNY_MAX_ROWS = 16      # batches up to this many rows take the kernel that is bound by reading the weight
 
 
-def linear_skinny(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+_skinny_plans: dict = {}      # (device, N, K) -> parts of k per strip
+
+
+def linear_skinny_splits(device, n: int, k: int) -> int:
+    """Into how many parts of k the kernel would best cut the strips of an [n, k] weight on this device
+    (1: not at all): few strips, or strips that load the multiprocessors unevenly, are cut."""
+    key = (torch.device(device).index or 0, n, k)
+    plan = _skinny_plans.get(key)
+    if plan is None:
+        f = _build.load("linear_skinny").jv_linear_skinny_plan
+        f.argtypes = [c_int, c_int]
+        f.restype = c_int
+        with torch.cuda.device(key[0]):
+            plan = _skinny_plans[key] = int(f(n, k))
+    return plan
+
+
+def linear_skinny(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype, parts_ok: bool = False):
     """x [M <= 16, K] times weight [N, K] transposed, bfloat16 operands, 32-bit accumulation
-    (csrc/linear_skinny.cu); the result is bfloat16 or float32."""
+    (csrc/linear_skinny.cu); the result is bfloat16 or float32, or with `parts_ok`, where the kernel
+    cuts k for an even load, a PartialSum for a reader that adds the parts."""
     _cuda(x, "x", torch.bfloat16, contiguous=False); _cuda(weight, "weight", torch.bfloat16, contiguous=False)
     if x.dim() != 2 or weight.dim() != 2 or x.shape[1] != weight.shape[1] or x.stride(1) != 1 or weight.stride(1) != 1:
         raise KernelError(f"linear shapes {tuple(x.shape)} x {tuple(weight.shape)}^T do not fit")
     m, k = x.shape
     n = weight.shape[0]
-    y = torch.empty((m, n), dtype=out_dtype, device=x.device)
+    splits = linear_skinny_splits(x.device, n, k) if parts_ok else 1
+    if splits > 1:
+        parts = torch.empty((splits, m, n), dtype=torch.float32, device=x.device)
+        y = None
+    else:
+        parts = None
+        y = torch.empty((m, n), dtype=out_dtype, device=x.device)
     f = _fn("linear_skinny", "jv_linear_skinny", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
-                                                  c_int, c_void_p])
-    _check(f(x.data_ptr(), x.stride(0), weight.data_ptr(), weight.stride(0), y.data_ptr(), _code(y, "out"), y.stride(0),
-             m, n, k, _stream()), "linear_skinny")
-    return y
+                                                  c_int, c_void_p, c_int, c_void_p])
+    _check(f(x.data_ptr(), x.stride(0), weight.data_ptr(), weight.stride(0), _ptr(y), DTYPE_CODE[out_dtype],
+             n if y is None else y.stride(0), m, n, k, _ptr(parts), splits, _stream()), "linear_skinny")
+    return y if parts is None else PartialSum(parts)
 
 
 GEMM_EPILOGUES = {"bf16": 0, "f32": 1, "swiglu": 2}
@@ -451,8 +522,9 @@ def _skinny_ok(x: torch.Tensor, weight: torch.Tensor) -> bool:
             and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0 and x.stride(1) == 1)
 
 
-def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
-    """y = x @ weight.T.
+def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None = None, parts_ok: bool = False):
+    """y = x @ weight.T.  With `parts_ok` the result may be a PartialSum (the caller hands it to `rmsnorm`,
+    `residual_add` or `swiglu`, which add its parts as they read them).
 
     float32 weights: the CUDA-core product of this package in true 32-bit (16-bit
     activations are read as they are and widened inside).  bfloat16 weights and
@@ -464,7 +536,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None 
         return gemm_simt(x, weight, out_dtype)
     _cuda(x, "x", torch.bfloat16, contiguous=False); _cuda(weight, "weight", torch.bfloat16)
     if _skinny_ok(x, weight):
-        return linear_skinny(x, weight, out_dtype)
+        return linear_skinny(x, weight, out_dtype, parts_ok)
     if out_dtype == torch.bfloat16:
         return torch.mm(x, weight.t())
     return torch.mm(x, weight.t(), out_dtype=out_dtype)

@@ -107,7 +107,7 @@ class Attention(Part):
                     cache.k if writes else None, cache.v if writes else None, self.hq, self.hkv, self.d)
         out = torch.empty((step.n_tokens, self.hq * self.d), dtype=dt, device=x.device)
         self.attend(qkv, out, step, cache, table)
-        return ops.linear(out, self.w_o, dt)
+        return ops.linear(out, self.w_o, dt, parts_ok=True)    # maybe the parts of a sum, for the next norm to add
 
     def attend(self, qkv, out, step, cache, table):
         common = (cache.k, cache.v, table, step.cu_seqlens, step.start_pos)

@@ -5,7 +5,8 @@
 
 The stream `h` is float32 in every mode.  A block hands back its last branch output as
 `delta`, not yet added, so that the next norm (of the next block, or the final one) adds
-and normalises in one pass over the stream.
+and normalises in one pass over the stream.  A branch output is a tensor [n, hidden] or an
+`ops.PartialSum` (the parts of a product whose k was cut); the norms take either.
 """
 
 from __future__ import annotations

@@ -53,8 +53,9 @@ class GatedMLP(Part):
         if self.block is not None and x.shape[0] > ops.SKINNY_MAX_ROWS:
             act = ops.gemm_tcgen05(x, self.w_gate_up, "swiglu")
         else:
-            act = ops.swiglu(ops.linear(x, self.w_gate_up, dt), self.block)
-        return ops.linear(act, self.w_down, dt)
+            act = ops.swiglu(ops.linear(x, self.w_gate_up, dt, parts_ok=True), self.block, out_dtype=dt)
+        # a few rows: the product may come as the parts of a sum, which the next norm adds as it reads them
+        return ops.linear(act, self.w_down, dt, parts_ok=True)
 
 
 register_feed_forward("gated_mlp", GatedMLP)

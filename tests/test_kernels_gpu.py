@@ -125,6 +125,66 @@ def test_linear_skinny(ops, m, n, k, out_dtype):
     torch.testing.assert_close(y2.double(), wide[:, 8:8 + k].double() @ w.double().T, atol=1e-4, rtol=1e-4)
 
 
+def test_linear_skinny_cuts_k_when_strips_are_few(ops):
+    # few strips of a long k are cut into parts that other blocks take; many strips, or a short k, are not
+    assert ops.linear_skinny_splits(DEV, 4096, 12288) > 1
+    assert ops.linear_skinny_splits(DEV, 1024, 2048) > 1
+    assert ops.linear_skinny_splits(DEV, 151936, 4096) == 1
+    assert ops.linear_skinny_splits(DEV, 4096, 64) == 1
+
+
+@pytest.mark.parametrize("m", [1, 5, 8, 13, 16])
+@pytest.mark.parametrize("n,k", [(4096, 12288), (4096, 4096), (1024, 2048), (1000, 2056), (151, 4104)])
+def test_linear_skinny_parts_of_a_sum(ops, m, n, k):
+    g = torch.Generator().manual_seed(m * 1000 + n)
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(n, k, generator=g) / k ** 0.5).to(torch.bfloat16).to(DEV)
+    y = ops.linear_skinny(x, w, torch.bfloat16, parts_ok=True)
+    assert isinstance(y, ops.PartialSum) and y.parts.shape == (ops.linear_skinny_splits(DEV, n, k), m, n)
+    assert tuple(y.shape) == (m, n)
+    want = x.double() @ w.double().T
+    torch.testing.assert_close(y.tensor().double(), want, atol=1e-4, rtol=1e-4)
+    torch.testing.assert_close(y.parts.double().sum(0), want, atol=1e-4, rtol=1e-4)
+    # the parts of a row do not depend on the rest of the batch
+    ys = ops.linear_skinny(x[m // 2:m // 2 + 1].contiguous(), w, torch.bfloat16, parts_ok=True)
+    assert torch.equal(ys.parts[:, 0], y.parts[:, m // 2])
+    # and through the dispatcher
+    assert isinstance(ops.linear(x, w, torch.bfloat16, parts_ok=True), ops.PartialSum)
+    assert isinstance(ops.linear(x, w, torch.bfloat16), torch.Tensor)
+
+
+@pytest.mark.parametrize("n,hidden,parts", [(3, 96, 2), (8, 4096, 4), (5, 1000, 3), (2, 20000, 2)])
+def test_readers_add_the_parts_of_a_sum(ops, n, hidden, parts):
+    g = torch.Generator().manual_seed(parts + hidden)
+    ps = torch.randn(parts, n, hidden, generator=g).to(DEV)
+    whole = ps[0].clone()
+    for s in range(1, parts):
+        whole += ps[s]                                   # the same order of additions as the kernels
+    weight = (1 + 0.1 * torch.randn(hidden, generator=g)).to(torch.bfloat16).to(DEV)
+    h0 = torch.randn(n, hidden, generator=g).to(DEV)
+    # norm with the residual sum, in place and gathered
+    h1, h2 = h0.clone(), h0.clone()
+    y1 = ops.rmsnorm(h1, weight, 1e-6, torch.bfloat16, delta=ops.PartialSum(ps))
+    y2 = ops.rmsnorm(h2, weight, 1e-6, torch.bfloat16, delta=whole)
+    assert torch.equal(y1, y2) and torch.equal(h1, h2)
+    rows = torch.tensor([n - 1, 0], dtype=torch.int32, device=DEV)
+    y1 = ops.rmsnorm(h0.clone(), weight, 1e-6, torch.float32, delta=ops.PartialSum(ps), rows=rows)
+    y2 = ops.rmsnorm(h0.clone(), weight, 1e-6, torch.float32, delta=whole, rows=rows)
+    assert torch.equal(y1, y2)
+    # the plain residual sum, and the sum alone
+    assert torch.equal(ops.residual_add(h0.clone(), ops.PartialSum(ps)), ops.residual_add(h0.clone(), whole))
+    assert torch.equal(ops.PartialSum(ps).tensor(), whole)
+    # the gated activation (a gate|up of hidden columns, in blocks where they divide)
+    if hidden % 8 == 0:
+        for block in (None, hidden // 8 if hidden % 64 == 0 else None):
+            a1 = ops.swiglu(ops.PartialSum(ps), block, out_dtype=torch.bfloat16)
+            a2 = ops.swiglu(whole, block).to(torch.bfloat16)
+            torch.testing.assert_close(a1.float(), a2.float(), atol=1e-2, rtol=1e-2)
+            gate, up = (whole[:, :hidden // 2], whole[:, hidden // 2:]) if block is None else \
+                (whole.view(n, -1, 2, block)[:, :, 0].reshape(n, -1), whole.view(n, -1, 2, block)[:, :, 1].reshape(n, -1))
+            torch.testing.assert_close(a1.float(), torch.nn.functional.silu(gate) * up, atol=2e-2, rtol=2e-2)
+
+
 @pytest.mark.parametrize("m,n,k", [(128, 256, 64), (128, 256, 256), (256, 512, 128), (130, 300, 72), (5, 256, 64),
                                    (2048, 1024, 4096), (300, 6144, 1024), (1000, 264, 4104)])
 @pytest.mark.parametrize("epilogue", ["bf16", "f32"])

@@ -163,6 +163,36 @@ def test_feed_forward_bf16_with_the_gate_in_the_product(rows):
     ops.check_status()
 
 
+@pytest.mark.parametrize("rows", [1, 7, 16])
+def test_feed_forward_bf16_whose_down_product_comes_as_the_parts_of_a_sum(rows):
+    """A feed-forward wide enough that the decode kernel cuts the k of the down product (few strips, long k):
+    the part hands back the parts of a sum, which the next norm adds to the stream as it reads them."""
+    j, cache, config, engine, parts, weights = pkg()
+    from jax_vllm_b200 import ops
+    ctx = parts.BuildContext(torch.bfloat16, DEV)
+    ff = parts.FEED_FORWARDS["gated_mlp"](config.GatedMLPSpec(1024, 2048), "L", ctx)
+    g = torch.Generator().manual_seed(9)
+    w = {n: (torch.randn(ts.shape, generator=g) * 0.05).to(torch.bfloat16) for n, ts in ff.tensor_specs().items()}
+    ff.bind({k: v.to(DEV) for k, v in w.items()})
+    x = torch.randn(rows, 1024, generator=g).to(torch.bfloat16)
+    got = ff.forward(x.to(DEV), None)
+    assert isinstance(got, ops.PartialSum) and got.parts.shape[0] == ops.linear_skinny_splits(DEV, 1024, 2048) > 1
+    rnd = lambda t: t.to(torch.bfloat16).double()
+    wd = {k: v.double() for k, v in w.items()}
+    gate, up = x.double() @ wd["L.mlp.gate_proj.weight"].T, x.double() @ wd["L.mlp.up_proj.weight"].T
+    want = (rnd(torch.nn.functional.silu(rnd(gate)) * rnd(up)) @ wd["L.mlp.down_proj.weight"].T).float()
+    torch.testing.assert_close(got.tensor().cpu(), want, atol=2e-2, rtol=1e-2)
+    # through a norm: norm(h + delta) with the stream updated in place
+    norm = parts.NORMS["rmsnorm"](config.NormSpec(1024, 1e-6, "weight"), "N", ctx)
+    norm.bind({"N.weight": torch.ones(1024, dtype=torch.bfloat16, device=DEV)})
+    h = torch.randn(rows, 1024, generator=g)
+    hd = h.to(DEV)
+    y = norm.norm(hd, got).float().cpu()
+    torch.testing.assert_close(hd.cpu(), h + want, atol=2e-2, rtol=1e-2)
+    torch.testing.assert_close(y, plain.rms_norm(h + want, torch.ones(1024), 1e-6), atol=3e-2, rtol=2e-2)
+    ops.check_status()
+
+
 def test_kinds_are_looked_up_in_the_registries():
     j, cache, config, engine, parts, weights = pkg()
     spec = spec_b()
