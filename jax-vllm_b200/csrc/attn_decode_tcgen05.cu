@@ -36,7 +36,7 @@ constexpr int HALF_BYTES = 128 * 128;
 constexpr int SMALL_BYTES = NH * 128 * 2;        // a 16 x 128 tile (Q, P^T): two halves of [16 rows][128 bytes]
 constexpr int SMALL_HALF = NH * 128;
 constexpr int STAGES = 3;
-constexpr int THREADS = 224;                      // warps: keys+query producer, mma issuer, 4 x softmax, values producer
+constexpr int THREADS = 256;                      // warps: keys producer, mma issuer, 4 x softmax, values producer, query producer
 constexpr int TMEM_COLS = 64;                    // S^T buffers at columns 0 and 16, O^T buffers at 32 and 48
 constexpr int MAX_WORK = 512;                    // requests in one launch
 constexpr long long WAIT_CYCLES = 2000000000LL;
@@ -288,11 +288,13 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_tcgen05_kernel(const _
     }
   };
 
-  pdl_wait();                    // the query and this step's keys and values come from the kernel before
-
+  // The kernel before this one wrote the query and the new token's key and value.  Every other key and value
+  // is from earlier steps, so the producers stream them at once, under the kernels before, and wait for those
+  // only when they come to a pair's last tile (which holds the new token); the query producer waits first.
   if (warp == 0 || warp == 6) {
-    // ------------------------------------------------------------------ producers: warp 0 keys and queries, warp 6 values
+    // ------------------------------------------------------------------ producers: warp 0 keys, warp 6 values
     const int which = warp == 6;
+    bool waited = false;
     const int P = p.page_size, pages_per_tile = BN / P;
     auto tile_pages = [&](const Cursor& c, bool wanted) -> int {   // lane l: the l-th page of the tile, -1 = none
       int page = -1;
@@ -331,9 +333,21 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_tcgen05_kernel(const _
       Cursor n = c;
       advance(n);
       const int pages_next = tile_pages(n, t + 1 < ntb);
-      if (which == 0 && (t == 0 || c.j == 0)) {   // a segment begins: its query (the buffer was last read two segments ago)
-        const int sp = c.seg & 1;
-        if (lane == 0) {
+      if (!waited && c.j == c.nt - 1) { pdl_wait(); waited = true; }
+      if (ok) ok = load_tile(t, pages, c.head);
+      pages = pages_next;
+      c = n;
+    }
+    if (!ok && lane == 0) atomicOr(p.status, JV_STATUS_WAIT_EXPIRED);
+  } else if (warp == 7) {
+    // ------------------------------------------------------------------ query producer: one load per segment
+    if (lane == 0) {
+      pdl_wait();
+      Cursor c = c0;
+      bool ok = true;
+      for (int t = 0; t < ntb && ok; ++t) {
+        if (t == 0 || c.j == 0) {               // a segment begins (the buffer was last read two segments ago)
+          const int sp = c.seg & 1;
           if (c.seg >= 2) ok = mbar_wait(&sh->q_empty[sp], ((c.seg >> 1) - 1) & 1);
           if (ok) {
             mbar_expect_tx(&sh->q_full[sp], G * 128 * 2);
@@ -341,13 +355,10 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_tcgen05_kernel(const _
             tma_load_3d(q_s + sp * SMALL_BYTES + SMALL_HALF, &q_map, 64, c.head * G, sh->token[c.i], &sh->q_full[sp]);
           }
         }
-        ok = __shfl_sync(0xffffffffu, ok, 0);
+        advance(c);
       }
-      if (ok) ok = load_tile(t, pages, c.head);
-      pages = pages_next;
-      c = n;
+      if (!ok) atomicOr(p.status, JV_STATUS_WAIT_EXPIRED);
     }
-    if (!ok && lane == 0) atomicOr(p.status, JV_STATUS_WAIT_EXPIRED);
   } else if (warp == 1) {
     // ---------------------------------------------------------------- mma issuer
     if (lane == 0) {

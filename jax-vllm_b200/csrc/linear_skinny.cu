@@ -217,7 +217,7 @@ int choose_splits(int n_strips, int K, int sms) {
   };
   int best = 1;
   double best_eff = efficiency(1);
-  const double floor_gain = best_eff * 1.10;
+  const double floor_gain = best_eff * 1.03;
   for (int s = 2; s <= 8; ++s) {
     if (chunks < s * WARPS * 2) break;
     const double e = efficiency(s);
