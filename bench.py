@@ -237,7 +237,7 @@ def time_e2e(model, batch, steps, warmup, ctx=CONTEXT):
     return emitted / dt, h2d, d2h
 
 
-def micro(spec: str, reps: int) -> int:
+def micro(spec: str, reps: int, eager: bool = False) -> int:
     """One kernel alone on data larger than the L2, for profiling:
     gemm:<N>x<K>:<M>:<impl>  the prompt product, impl = tcgen05 | tcgen05_swiglu | library (cuBLAS)
     linear:<N>x<K>:<M>[:parts]   the decode product of M rows with an [N, K] weight (several weights in turn)
@@ -332,7 +332,7 @@ def micro(spec: str, reps: int) -> int:
     for i in range(3):
         run(i)
     torch.cuda.synchronize()
-    if kind.startswith("attn_decode") or kind == "linear":
+    if (kind.startswith("attn_decode") or kind == "linear") and not eager:
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
             for i in range(copies):
@@ -375,11 +375,13 @@ def main():
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64, and the prefill")
     ap.add_argument("--only-prefill", action="store_true", help="time the 2,048-token prefill alone (for profiling)")
     ap.add_argument("--micro", default=None, help="run one kernel alone, e.g. linear:24576x4096:8 (see micro())")
+    ap.add_argument("--micro-eager", action="store_true",
+                    help="with --micro: plain launches instead of replays of a CUDA graph (for a profiler)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
     if args.micro:
-        return micro(args.micro, max(1, args.steps))
+        return micro(args.micro, max(1, args.steps), args.micro_eager)
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
