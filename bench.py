@@ -226,11 +226,14 @@ def time_e2e(model, batch, steps, warmup, ctx=CONTEXT):
         if best is None or emitted / dt > best[0] / best[1]:
             best = (emitted, dt)
     emitted, dt = best
-    layout_bytes = 0
-    g = driver.runner.graphs.get(batch)
+    # one copy per step: the batch description (tokens, positions, block tables, work lists) and, behind it in
+    # the same buffer, seeds, counters and temperatures of the sampler
+    g = driver.runner.graphs_sampled.get(batch)
     if g is not None:
-        layout_bytes = g.layout.total * 4
-    h2d = layout_bytes + batch * (4 + 16)        # batch description; temperatures, seeds and counters
+        h2d = g.total * 4
+    else:
+        g = driver.runner.graphs.get(batch)
+        h2d = (g.layout.total * 4 if g is not None else 0) + batch * (4 + 16)
     d2h = (batch + 1) * 4                        # sampled tokens and the kernels' status word
     del driver
     torch.cuda.empty_cache()

@@ -54,6 +54,8 @@ class Driver:
         self.stop_event = threading.Event()
         self.thread: Optional[threading.Thread] = None
         self.thread_error: Optional[str] = None
+        self.ahead = None                  # the next step's plan, made while the device ran the last one
+        self.host_tokens = None            # pinned memory that the sampled tokens come back to
 
 
 def make_driver(model, max_num_seqs: int = 4, max_model_len: int = 2048, max_prefill_len: Optional[int] = None,
@@ -107,23 +109,46 @@ def step(driver: Driver) -> list:
 
 def _step_locked(driver: Driver) -> list:
     sched = driver.scheduler
-    plan = sched.schedule()
+    ahead, driver.ahead = driver.ahead, None
+    plan = sched.take_ahead(ahead) or sched.schedule()
     if not plan:
         return []
     entries = [StepEntry(driver.cache.live[s.request.request_id], s.tokens, (len(s.tokens) - 1,) if s.wants_logits else ())
                for s in plan]
-    logits = driver.runner.step(entries)
-    sched.committed(plan)
-    driver.stats.steps += 1
     sampled = [s for s in plan if s.wants_logits]
-    events: list = []
-    if not sampled:
-        return events
     temps = [s.request.sampling.temperature for s in sampled]
     seeds = [s.request.sampling.seed if s.request.sampling.seed is not None else s.request.request_id for s in sampled]
     counters = [len(s.request.output_ids) for s in sampled]
-    tokens = driver.sampler.sample(logits, temps, seeds, counters)
-    both = torch.cat([tokens, driver.runner.status_word()]).tolist()     # one copy back, which also synchronises
+    # a decode-only step samples inside its replayed graph; any other step hands back logits for the sampler
+    fused = getattr(driver.runner, "step_sampled", None)
+    both = fused(entries, temps, seeds, counters) if fused is not None and len(sampled) == len(plan) else None
+    logits = driver.runner.step(entries) if both is None else None
+    sched.committed(plan)
+    driver.stats.steps += 1
+    events: list = []
+    if not sampled:
+        return events
+    if both is None:
+        tokens = driver.sampler.sample(logits, temps, seeds, counters)
+        both = torch.cat([tokens, driver.runner.status_word()])          # one copy back
+    arrived = None
+    if both.is_cuda:
+        # the copy is on its way while the host plans the next step; waiting for it also synchronises
+        if driver.host_tokens is None or driver.host_tokens.numel() < both.numel():
+            driver.host_tokens = torch.empty(max(both.numel(), 64), dtype=both.dtype, pin_memory=True)
+        back = driver.host_tokens[:both.numel()]
+        back.copy_(both, non_blocking=True)
+        arrived = torch.cuda.Event()
+        arrived.record()
+        both = back
+    driver.ahead = sched.plan_ahead(plan)
+    if driver.ahead is not None and fused is not None:
+        # its layout goes into the staging buffer now too; only the tokens are missing
+        driver.runner.prefill_ahead([StepEntry(driver.cache.live[s.request.request_id], [0], (0,)) for s in driver.ahead[1]],
+                                    temps, seeds, [c + 1 for c in counters])
+    if arrived is not None:
+        arrived.synchronize()
+    both = both.tolist()
     toks, status = both[:-1], both[-1]
     if status:
         driver.runner.clear_status()

@@ -19,10 +19,15 @@ from .batch import BatchBuilder, StepEntry
 
 
 class _DecodeGraph:
-    """A captured step for `n` single-token entries: fixed buffers, fixed launch sizes."""
+    """A captured step for `n` single-token entries: fixed buffers, fixed launch sizes.  With sampling in
+    the graph, `out` holds the sampled tokens followed by the kernels' status word, and the sampling
+    parameters lie behind the batch in the same buffer, from `samp_off` on: n seeds and n counters (64-bit),
+    then n temperatures."""
 
-    def __init__(self, layout, dev, logits, graph, launches):
+    def __init__(self, layout, dev, logits, graph, launches, out=None, samp_off=0):
         self.layout, self.dev, self.logits, self.graph, self.launches = layout, dev, logits, graph, launches
+        self.out, self.samp_off = out, samp_off
+        self.total = layout.total if out is None else samp_off + 5 * layout.sections["token_ids"][1]
 
 
 class Runner:
@@ -37,7 +42,9 @@ class Runner:
         self.cuda_graphs = bool(cuda_graphs) and max_model_len is not None
         self.max_graph_batch = max_graph_batch
         self.graphs: dict[int, _DecodeGraph] = {}
+        self.graphs_sampled: dict[int, _DecodeGraph] = {}
         self.graph_warm: set[int] = set()
+        self._ahead = None                 # (requests and lengths, graph) of a batch already laid out in the staging buffer
         self.launches_last_step = 0
         self.device, self.dtype = torch.device(device), dtype
         if self.device.type != "cuda":
@@ -56,6 +63,7 @@ class Runner:
         and of their `want`."""
         if not entries:
             return torch.empty((0, self.model.spec.vocab_size), dtype=torch.float32, device=self.device)
+        self._ahead = None                 # the staging buffer is about to be written
         with torch.cuda.device(self.device):
             if self._graphable(entries):
                 logits = self._step_graph(entries)
@@ -114,6 +122,88 @@ class Runner:
         g.graph.replay()
         ops.launch_count += g.launches
         return g.logits
+
+    # ------------------------------------------- captured decode steps that also sample
+    @staticmethod
+    def _key(entries):
+        return tuple((e.cache.request_id, e.cache.num_tokens) for e in entries)
+
+    def _fill_sampling(self, host, g: _DecodeGraph, temps, seeds, counters) -> None:
+        n = len(temps)
+        wide = host[g.samp_off:g.samp_off + 4 * n].view("int64")
+        wide[:n] = [s & ((1 << 63) - 1) for s in seeds]
+        wide[n:2 * n] = counters
+        host[g.samp_off + 4 * n:g.samp_off + 5 * n].view("float32")[:] = temps
+
+    @torch.no_grad()
+    def step_sampled(self, entries: list, temps, seeds, counters):
+        """A decode-only step with the sampling inside the replayed graph: returns the sampled tokens followed
+        by the kernels' status word (int32, on the device), or None if this batch has to go the ordinary way
+        (`step`, then the sampler): not all single tokens, or the first time at this batch size."""
+        n = len(entries)
+        if not self._graphable(entries) or n not in self.graph_warm:
+            return None
+        b = self.builder
+        with torch.cuda.device(self.device):
+            g = self.graphs_sampled.get(n)
+            if g is None:
+                layout = self._graph_layout(entries)
+                samp_off = (layout.total + 1) // 2 * 2
+                dev = torch.zeros(samp_off + 5 * n, dtype=torch.int32, device=self.device)
+                out = torch.zeros(n + 1, dtype=torch.int32, device=self.device)
+                g = _DecodeGraph(layout, dev, None, None, 0, out=out, samp_off=samp_off)
+                pinned = b._staging(g.total)
+                host = pinned.numpy()[:g.total]
+                b.fill(entries, host, layout)
+                self._fill_sampling(host, g, temps, seeds, counters)
+                dev.copy_(pinned[:g.total], non_blocking=True)
+                torch.cuda.current_stream().synchronize()
+                ctx = b.context(entries, layout, dev, max_seq_len=self.max_model_len)
+                seeds_d = dev[samp_off:samp_off + 2 * n].view(torch.int64)
+                counters_d = dev[samp_off + 2 * n:samp_off + 4 * n].view(torch.int64)
+                temps_d = dev[samp_off + 4 * n:samp_off + 5 * n].view(torch.float32)
+                graph = torch.cuda.CUDAGraph()
+                before = ops.launch_count
+                with torch.cuda.graph(graph):
+                    logits = self.model.forward(ctx, self.layer_caches)
+                    out[:n].copy_(ops.sample(logits, temps_d, seeds_d, counters_d))
+                    out[n:].copy_(ops.status_word(self.device))
+                g.logits, g.graph, g.launches = logits, graph, ops.launch_count - before
+                ops.launch_count = before       # nothing ran yet: a replay counts them
+                self.graphs_sampled[n] = g
+                self._ahead = None
+            ahead, self._ahead = self._ahead, None
+            pinned = b._pinned
+            if ahead is not None and ahead[1] is g and ahead[0] == self._key(entries):
+                # the batch was laid out while the device ran the last step: only the tokens are new
+                host = pinned.numpy()[:g.total]
+                g.layout.view(host, "token_ids")[:] = [e.tokens[0] for e in entries]
+            else:
+                pinned = b._staging(g.total)
+                host = pinned.numpy()[:g.total]
+                b.fill(entries, host, g.layout)
+                self._fill_sampling(host, g, temps, seeds, counters)
+            g.dev.copy_(pinned[:g.total], non_blocking=True)
+            b._copied = torch.cuda.Event(); b._copied.record()
+            g.graph.replay()
+            ops.launch_count += g.launches
+        self.steps += 1
+        return g.out
+
+    def prefill_ahead(self, entries: list, temps, seeds, counters) -> None:
+        """Lays out the next decode step (tokens not known yet) in the staging buffer while the device runs
+        this one.  `entries` carry the lengths that the requests will have then; `step_sampled` uses the
+        layout if it is called with exactly these requests at these lengths."""
+        self._ahead = None
+        g = self.graphs_sampled.get(len(entries))
+        if g is None or not self._graphable(entries):
+            return
+        b = self.builder
+        pinned = b._staging(g.total)          # waits until the last copy out of it has finished
+        host = pinned.numpy()[:g.total]
+        b.fill(entries, host, g.layout)
+        self._fill_sampling(host, g, temps, seeds, counters)
+        self._ahead = (self._key(entries), g)
 
     def run(self, entries: list) -> torch.Tensor:
         """grow -> step -> commit, for callers that do not schedule (replay, tests)."""

@@ -44,6 +44,7 @@ class Scheduler:
         self.waiting: deque = deque()
         self.running: list = []            # in order of admission
         self.stats = stats or EngineStats()
+        self.version = 0                   # changes whenever the set of waiting or running requests does
 
     # --------------------------------------------------------------------- intake
     def validate(self, prompt_ids, sampling) -> None:
@@ -61,12 +62,14 @@ class Scheduler:
     def add(self, request: Request) -> None:
         self.validate(request.prompt_ids, request.sampling)
         self.waiting.append(request)
+        self.version += 1
 
     def has_work(self) -> bool:
         return bool(self.waiting) or bool(self.running)
 
     # ------------------------------------------------------------------- planning
     def _preempt(self, victim: Request) -> None:
+        self.version += 1
         self.cache.release(victim.request_id)
         self.running.remove(victim)
         victim.slot = None
@@ -135,6 +138,7 @@ class Scheduler:
                 break
             self.waiting.popleft()
             self.running.append(req)
+            self.version += 1
             req.slot = rc.slot
             self.stats.admissions += 1
             self.stats.cache_hit_blocks += len(rc.hashes)
@@ -164,7 +168,39 @@ class Scheduler:
             else:
                 self.stats.prefill_tokens += len(s.tokens)
 
+    def plan_ahead(self, plan: list):
+        """While the device runs `plan` (already committed): the plan of the next step if that is sure to be
+        one more token for every running request - nobody waits, all of them are decoding and the pages are
+        there without taking any from another.  The tokens are not known yet (`tokens` is None); `take_ahead`
+        fills them in.  Returns None when the next step has to be planned in the ordinary way."""
+        if self.waiting or len(plan) != len(self.running):
+            return None
+        for s, req in zip(plan, self.running):
+            if s.request is not req or not s.wants_logits:
+                return None
+        cache = self.cache
+        for req in self.running:
+            rc = cache.live[req.request_id]
+            if rc.num_tokens + 1 > self.max_model_len or not cache.can_grow(rc, rc.num_tokens + 1):
+                return None                # pages grown so far stay: the ordinary plan would grow them too
+            cache.grow(rc, rc.num_tokens + 1)
+        return (self.version, [Scheduled(req, None, True) for req in self.running])
+
+    def take_ahead(self, ahead):
+        """The plan made by `plan_ahead`, with each request's newest token, if nothing has changed since
+        (no request came, finished or was preempted) and every request has exactly that one token pending."""
+        if ahead is None or ahead[0] != self.version or self.waiting:
+            return None
+        plan = ahead[1]
+        for s in plan:
+            if s.request.finished or self._pending(s.request) != 1:
+                return None
+            s.tokens = [s.request.output_ids[-1]]        # pending == 1: the token sampled last
+        self.stats.scheduler_loops += 1
+        return plan
+
     def finish(self, req: Request) -> None:
+        self.version += 1
         req.finished = True
         req.slot = None
         self.cache.release(req.request_id)

@@ -161,6 +161,50 @@ def test_pages_run_out_youngest_is_preempted_and_tokens_stay_the_same(prefix_cac
     assert fed_first == 6 + 10 - 1
 
 
+def test_the_next_decode_step_is_planned_under_the_running_one():
+    d, r = driver(max_num_seqs=3, max_model_len=64, block_size=4, prefix_cache=False)
+    sched = d.scheduler
+    a = add_request(d, [1, 2, 3], SamplingParams(max_new_tokens=6))
+    b = add_request(d, [4, 5, 6, 7, 8], SamplingParams(max_new_tokens=3))
+    step(d)                                         # both prompts; both decode next and nobody waits
+    assert d.ahead is not None and [s.request.request_id for s in d.ahead[1]] == [a, b]
+    assert all(s.tokens is None for s in d.ahead[1])
+    loops = d.stats.scheduler_loops
+    step(d)
+    assert r.batches[-1] == [(a, 1, (0,)), (b, 1, (0,))] and d.stats.scheduler_loops == loops + 1
+    # a request that arrives makes the plan stale: the step is planned in the ordinary way, with the newcomer
+    stale = d.ahead
+    c = add_request(d, [9, 9], SamplingParams(max_new_tokens=2))
+    assert sched.take_ahead(stale) is None
+    step(d)
+    assert r.batches[-1] == [(a, 1, (0,)), (b, 1, (0,)), (c, 2, (1,))]
+    # b has its three tokens now: a request that finishes drops the plan too
+    assert d.requests[b].finished and d.ahead is not None and sched.take_ahead(d.ahead) is None
+    while has_work(d):
+        step(d)
+    assert d.requests[a].output_ids == expected([1, 2, 3], 6)
+    assert d.requests[b].output_ids == expected([4, 5, 6, 7, 8], 3)
+    assert d.requests[c].output_ids == expected([9, 9], 2)
+    d.cache.check()
+    assert not d.cache.live
+
+
+def test_no_plan_ahead_when_it_would_take_pages_from_another():
+    # 4 pages of 4 tokens; two requests at 8 tokens each hold them all, the ninth token needs a fifth page
+    d, r = driver(max_num_seqs=2, max_model_len=16, block_size=4, num_blocks=4, prefix_cache=False)
+    prompts = [[1] * 7, [2] * 7]
+    ids = [add_request(d, p, SamplingParams(max_new_tokens=6)) for p in prompts]
+    step(d)                                         # prompts: 7 tokens each, 2 pages each, the 8th fits
+    assert d.ahead is not None
+    step(d)                                         # 8 tokens each: the next token needs a page that is not there
+    assert d.ahead is None and d.stats.preemptions == 0
+    while has_work(d):
+        step(d)
+    assert d.stats.preemptions >= 1                 # decided by the ordinary plan, not by the one made ahead
+    assert [d.requests[i].output_ids for i in ids] == [expected(p, 6) for p in prompts]
+    d.cache.check()
+
+
 def test_prompt_portion_waits_for_pages_instead_of_preempting():
     d, r = driver(max_num_seqs=2, max_model_len=24, block_size=4, num_blocks=6, max_tokens_per_step=64,
                   prefix_cache=False)
