@@ -158,6 +158,83 @@ __global__ void rope_kv_fast_kernel(T* __restrict__ qkv, int row_stride, const i
   *reinterpret_cast<V*>(dst + HALF + d0) = hi;
 }
 
+// The same for many tokens (prompt portions): one block per token takes all its heads, so the token's
+// cosines and sines are computed once (not once per head) and its page is looked up once.
+template <typename T, typename TW, int E>
+__global__ void __launch_bounds__(256) rope_kv_token_kernel(
+    T* __restrict__ qkv, int row_stride, const int* __restrict__ positions, const int* __restrict__ token_entry,
+    const int* __restrict__ block_table, int table_width, const float* __restrict__ inv_freq,
+    const TW* __restrict__ q_norm_w, const TW* __restrict__ k_norm_w, float eps, T* __restrict__ k_cache,
+    T* __restrict__ v_cache, int n_q_heads, int n_kv_heads, int page_size, int num_pages, int heads_to_do,
+    int* __restrict__ status) {
+  constexpr int HALF = 32 * E, D = 2 * HALF;
+  __shared__ float cs_s[HALF], sn_s[HALF];
+  pdl_trigger();
+  pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
+  const int n = blockIdx.x;
+  const int pos = positions[n];
+  for (int i = threadIdx.x; i < HALF; i += blockDim.x) {
+    float sn = 0.f, cs = 1.f;
+    if (inv_freq != nullptr) sincosf((float)pos * inv_freq[i], &sn, &cs);
+    cs_s[i] = cs; sn_s[i] = sn;
+  }
+  size_t slot = 0;                       // the token's row in the cache, in units of heads
+  bool have_slot = false;
+  if (heads_to_do > n_q_heads) {
+    const int entry = token_entry[n];
+    const int page_idx = pos / page_size;
+    const int page = (page_idx < table_width) ? block_table[(size_t)entry * table_width + page_idx] : -1;
+    if (page < 0 || page >= num_pages) {
+      if (threadIdx.x == 0) atomicOr(status, JV_STATUS_BAD_PAGE);
+    } else {
+      slot = ((size_t)page * page_size + (pos - page_idx * page_size)) * n_kv_heads;
+      have_slot = true;
+    }
+  }
+  __syncthreads();
+  using V = VecE<T, E>;
+  const int d0 = lane * E;
+  for (int head = warp; head < heads_to_do; head += n_warps) {
+    const bool is_q = head < n_q_heads;
+    const bool is_k = !is_q && head < n_q_heads + n_kv_heads;
+    if (!is_q && !have_slot) continue;
+    const int kv_head = is_q ? 0 : (is_k ? head - n_q_heads : head - n_q_heads - n_kv_heads);
+    T* src = qkv + (size_t)n * row_stride + (size_t)head * D;
+    T* dst = is_q ? src : (is_k ? k_cache : v_cache) + (slot + kv_head) * D;
+    V lo = *reinterpret_cast<const V*>(src + d0), hi = *reinterpret_cast<const V*>(src + HALF + d0);
+    if (!is_q && !is_k) {
+      *reinterpret_cast<V*>(dst + d0) = lo;
+      *reinterpret_cast<V*>(dst + HALF + d0) = hi;
+      continue;
+    }
+    float a[E], b[E], ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < E; ++i) {
+      a[i] = to_f32(lo.v[i]); b[i] = to_f32(hi.v[i]);
+      ss += a[i] * a[i] + b[i] * b[i];
+    }
+    const TW* w = is_q ? q_norm_w : k_norm_w;
+    if (w != nullptr) {
+      ss = warp_sum(ss);
+      const float inv = rsqrtf(ss / (float)D + eps);
+#pragma unroll
+      for (int i = 0; i < E; ++i) {
+        a[i] = a[i] * inv * to_f32(w[d0 + i]);
+        b[i] = b[i] * inv * to_f32(w[HALF + d0 + i]);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < E; ++i) {
+      const float cs = cs_s[d0 + i], sn = sn_s[d0 + i];
+      lo.v[i] = from_f32<T>(a[i] * cs - b[i] * sn);
+      hi.v[i] = from_f32<T>(b[i] * cs + a[i] * sn);
+    }
+    *reinterpret_cast<V*>(dst + d0) = lo;
+    *reinterpret_cast<V*>(dst + HALF + d0) = hi;
+  }
+}
+
 // qkv: [n, row_stride] of `dtype`; positions, token_entry: [n] int32; block_table:
 // [entries, table_width] int32; inv_freq: [rot_dim/2] float; q_norm_w/k_norm_w: [head_dim]
 // of `w_dtype` or null; k_cache/v_cache: [num_pages, page_size, n_kv_heads, head_dim] of
@@ -185,6 +262,17 @@ JV_EXPORT int jv_rope_kv(void* qkv, int dtype, int row_stride, const int* positi
             (T*)qkv, row_stride, positions, token_entry, block_table, table_width, freq, (const TW*)q_norm_w, \
             (const TW*)k_norm_w, eps, (T*)k_cache, (T*)v_cache, n_q_heads, n_kv_heads, page_size, num_pages, \
             heads_to_do, status)))
+    if (n >= 64) {                       // many tokens: a block per token, the angles once per token
+#define JV_ROPE_TOKEN(EE)                                                                                  \
+      JV_DISPATCH_DTYPE(dtype, T, JV_DISPATCH_DTYPE(w_dtype, TW,                                            \
+          return jv_launch(rope_kv_token_kernel<T, TW, EE>, dim3(n), dim3(256), 0, stream,                 \
+              (T*)qkv, row_stride, positions, token_entry, block_table, table_width, freq, (const TW*)q_norm_w, \
+              (const TW*)k_norm_w, eps, (T*)k_cache, (T*)v_cache, n_q_heads, n_kv_heads, page_size, num_pages, \
+              heads_to_do, status)))
+      if (E == 1) JV_ROPE_TOKEN(1); else if (E == 2) JV_ROPE_TOKEN(2); else JV_ROPE_TOKEN(4);
+#undef JV_ROPE_TOKEN
+      return JV_ERR_UNSUPPORTED;
+    }
     if (E == 1) JV_ROPE_FAST(1); else if (E == 2) JV_ROPE_FAST(2); else JV_ROPE_FAST(4);
 #undef JV_ROPE_FAST
     return JV_ERR_UNSUPPORTED;

@@ -242,9 +242,10 @@ def test_linear_uses_true_float32(ops):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("hq,hkv,d,page", [(4, 2, 16, 16), (6, 1, 32, 8), (3, 3, 48, 4), (8, 2, 128, 16), (5, 5, 64, 8),
                                            (2, 1, 256, 16)])
-def test_rope_kv(ops, dtype, hq, hkv, d, page):
+@pytest.mark.parametrize("q_lens,starts", [([5, 1, 9], [3, 40, 0]), ([30, 1, 47], [3, 40, 0])],
+                         ids=["few tokens", "many tokens (a block per token)"])
+def test_rope_kv(ops, dtype, hq, hkv, d, page, q_lens, starts):
     g = torch.Generator().manual_seed(4)
-    q_lens, starts = [5, 1, 9], [3, 40, 0]
     n = sum(q_lens)
     qkv = torch.randn(n, (hq + 2 * hkv) * d, generator=g).to(dtype)
     positions = torch.cat([torch.arange(s, s + q) for s, q in zip(starts, q_lens)]).to(torch.int32)
