@@ -337,3 +337,146 @@ def test_toy_mixer_with_own_state_registers_builds_and_steps():
     assert (lb[:13] - want_other[7:]).abs().max().item() <= lim
     assert (lb[13] - want[11]).abs().max().item() <= lim
     runner.check_kernels()
+
+
+# ------------------------------------- a toy feed-forward with routing, defined here
+@dataclass(frozen=True)
+class RoutedSpec:
+    hidden_size: int
+    intermediate_size: int
+    num_experts: int
+    prefix: str = "moe"
+    kind: str = "toy_routed"
+
+
+def register_toy_routed():
+    j, cache, config, engine, parts, weights = pkg()
+
+    class Top1Experts(parts.Part):
+        """Every token goes to the expert with the largest router logit (32-bit), whose gated feed-forward
+        output is scaled by that expert's softmax weight (torch ops: a toy for this test)."""
+
+        def __init__(self, spec, prefix, ctx):
+            self.spec, self.p, self.ctx = spec, f"{prefix}.{spec.prefix}", ctx
+
+        def tensor_specs(self):
+            s, out = self.spec, {f"{self.p}.router.weight": parts.TensorSpec((self.spec.num_experts, self.spec.hidden_size))}
+            for e in range(s.num_experts):
+                out[f"{self.p}.experts.{e}.gate_up.weight"] = parts.TensorSpec((2 * s.intermediate_size, s.hidden_size))
+                out[f"{self.p}.experts.{e}.down.weight"] = parts.TensorSpec((s.hidden_size, s.intermediate_size))
+            return out
+
+        def bind(self, tensors):
+            self.t = {k: v.float() for k, v in tensors.items() if k.startswith(self.p + ".")}
+
+        def forward(self, x, step):
+            xf = x.float()
+            probs = torch.softmax(xf @ self.t[f"{self.p}.router.weight"].T, dim=-1)
+            weight, expert = probs.max(dim=-1)
+            out = torch.zeros_like(xf)
+            for e in range(self.spec.num_experts):
+                rows = (expert == e).nonzero().flatten()
+                if rows.numel():
+                    gu = xf[rows] @ self.t[f"{self.p}.experts.{e}.gate_up.weight"].T
+                    g, u = gu.chunk(2, dim=-1)
+                    out[rows] = (torch.nn.functional.silu(g) * u) @ self.t[f"{self.p}.experts.{e}.down.weight"].T
+            return (out * weight[:, None]).to(x.dtype)
+
+    parts.register_feed_forward("toy_routed", Top1Experts)
+
+
+def plain_routed(x, w, p, n_experts):
+    probs = torch.softmax(x @ w[f"{p}.router.weight"].T, dim=-1)
+    weight, expert = probs.max(dim=-1)
+    ys = []
+    for t in range(x.shape[0]):
+        e = int(expert[t])
+        g, u = (w[f"{p}.experts.{e}.gate_up.weight"] @ x[t]).chunk(2)
+        ys.append(weight[t] * (w[f"{p}.experts.{e}.down.weight"] @ (torch.nn.functional.silu(g) * u)))
+    return torch.stack(ys)
+
+
+def test_toy_feed_forward_with_routing_registers_builds_and_steps():
+    j, cache, config, engine, parts, weights = pkg()
+    register_toy_routed()
+    spec = spec_b()
+    layers = list(spec.layers)
+    layers[2] = replace(layers[2], feed_forward=RoutedSpec(spec.hidden_size, 40, 3))
+    spec = replace(spec, layers=tuple(layers))
+    runner, w = make_runner(spec, seed=11)
+    assert any(".moe.experts.2.down.weight" in n for n in w) and not any("layers.2.mlp" in n for n in w)
+    cfg = qwen_cfg(TINY_B)
+    toks = random_tokens(41, TINY_B["vocab_size"], seed=12)
+    ids, T, eps = torch.as_tensor(toks), len(toks), cfg["rms_norm_eps"]
+    h = plain.embedding(w["model.embed_tokens.weight"], ids)
+    for i in range(cfg["num_hidden_layers"]):
+        p = f"model.layers.{i}"
+        h = h + plain.attention_block(plain.rms_norm(h, w[f"{p}.input_layernorm.weight"], eps), w, f"{p}.self_attn", cfg,
+                                      torch.arange(T))
+        x = plain.rms_norm(h, w[f"{p}.post_attention_layernorm.weight"], eps)
+        h = h + (plain_routed(x, w, f"{p}.moe", 3) if i == 2 else plain.swiglu(x, w, f"{p}.mlp"))
+    want = plain.linear(plain.rms_norm(h, w["model.norm.weight"], eps), w["lm_head.weight"])
+    lim = 1e-4 * max(1.0, want.abs().max().item())
+    for cuts in [(41,), (5, 1, 1, 13, 2)]:
+        got = run_cut(runner, toks, cuts)
+        assert (got - want).abs().max().item() <= lim, cuts
+
+
+# --------------------------------------- another position encoding, defined here
+@dataclass(frozen=True)
+class HarmonicSpec:
+    dim: int                       # rotated elements of a head (here fewer than the head has)
+    base: float
+    kind: str = "toy_harmonic"
+
+
+def register_toy_position():
+    j, cache, config, engine, parts, weights = pkg()
+
+    class Harmonic(parts.Part):
+        """Angles position * base / (j + 1) instead of the geometric table: only the table differs, the
+        rotation kernel is the same."""
+
+        def __init__(self, spec, prefix, ctx):
+            self.dim = int(spec.dim)
+            self.freq = (float(spec.base) / torch.arange(1, self.dim // 2 + 1, dtype=torch.float32)).to(ctx.device)
+
+        def table(self):
+            return self.freq
+
+    parts.register_position("toy_harmonic", Harmonic)
+
+
+def test_toy_position_encoding_registers_builds_and_steps():
+    j, cache, config, engine, parts, weights = pkg()
+    register_toy_position()
+    spec = spec_b()
+    D = TINY_B["head_dim"]
+    rot = D // 2                   # half of the head rotates, the rest passes
+    layers = tuple(replace(l, mixer=replace(l.mixer, position=HarmonicSpec(rot, 0.7))) for l in spec.layers)
+    spec = replace(spec, layers=layers)
+    runner, w = make_runner(spec, seed=13)
+    cfg = qwen_cfg(TINY_B)
+    toks = random_tokens(37, TINY_B["vocab_size"], seed=14)
+    ids, T, eps = torch.as_tensor(toks), len(toks), cfg["rms_norm_eps"]
+    Hq, Hkv = cfg["num_heads"], cfg["num_kv_heads"]
+    ang = torch.arange(T, dtype=torch.float32)[:, None] * (0.7 / torch.arange(1, rot // 2 + 1, dtype=torch.float32))[None]
+    cos, sin = torch.cos(torch.cat([ang, ang], -1)), torch.sin(torch.cat([ang, ang], -1))
+    rotate = lambda u: torch.cat([plain.apply_rope(u[..., :rot], cos, sin), u[..., rot:]], dim=-1)
+    h = plain.embedding(w["model.embed_tokens.weight"], ids)
+    for i in range(cfg["num_hidden_layers"]):
+        p = f"model.layers.{i}"
+        x = plain.rms_norm(h, w[f"{p}.input_layernorm.weight"], eps)
+        q = plain.linear(x, w[f"{p}.self_attn.q_proj.weight"]).reshape(T, Hq, D).transpose(0, 1)
+        k = plain.linear(x, w[f"{p}.self_attn.k_proj.weight"]).reshape(T, Hkv, D).transpose(0, 1)
+        v = plain.linear(x, w[f"{p}.self_attn.v_proj.weight"]).reshape(T, Hkv, D).transpose(0, 1)
+        q = rotate(plain.rms_norm(q, w[f"{p}.self_attn.q_norm.weight"], eps))
+        k = rotate(plain.rms_norm(k, w[f"{p}.self_attn.k_norm.weight"], eps))
+        o = plain.causal_attention(q, k, v, Hq, Hkv, D).transpose(0, 1).reshape(T, Hq * D)
+        h = h + plain.linear(o, w[f"{p}.self_attn.o_proj.weight"])
+        h = h + plain.swiglu(plain.rms_norm(h, w[f"{p}.post_attention_layernorm.weight"], eps), w, f"{p}.mlp")
+    want = plain.linear(plain.rms_norm(h, w["model.norm.weight"], eps), w["lm_head.weight"])
+    lim = 1e-4 * max(1.0, want.abs().max().item())
+    for cuts in [(37,), (4, 1, 9, 2)]:
+        got = run_cut(runner, toks, cuts)
+        assert (got - want).abs().max().item() <= lim, cuts
