@@ -135,10 +135,10 @@ def test_feed_forward_and_block_alone():
         parts.FEED_FORWARDS["gated_mlp"](config.GatedMLPSpec(40, 56, activation="gelu"), "L", ctx)
 
 
-@pytest.mark.parametrize("rows", [3, 16, 17, 150])
+@pytest.mark.parametrize("rows", [3, 16, 17, 150, 1100])
 def test_feed_forward_bf16_with_the_gate_in_the_product(rows):
     """An intermediate size that is a multiple of 128 takes the interleaved gate|up weight: prompt steps apply
-    the gate in the epilogue of the tcgen05 product, small batches in the separate kernel; both equal plain."""
+    the gate in the epilogue of the tcgen05 product (from 1,024 rows on), smaller batches in the separate kernel; both equal plain."""
     j, cache, config, engine, parts, weights = pkg()
     ctx = parts.BuildContext(torch.bfloat16, DEV)
     ff = parts.FEED_FORWARDS["gated_mlp"](config.GatedMLPSpec(72, 384), "L", ctx)
@@ -153,7 +153,7 @@ def test_feed_forward_bf16_with_the_gate_in_the_product(rows):
     rnd = lambda t: t.to(torch.bfloat16).double()
     wd = {k: v.double() for k, v in w.items()}
     gate, up = x.double() @ wd["L.mlp.gate_proj.weight"].T, x.double() @ wd["L.mlp.up_proj.weight"].T
-    if rows <= 16:
+    if rows < ff.FUSED_GATE_ROWS:
         gate, up = rnd(gate), rnd(up)
     want = (rnd(torch.nn.functional.silu(gate) * up) @ wd["L.mlp.down_proj.weight"].T).float()
     torch.testing.assert_close(got, want, atol=2e-2, rtol=1e-2)

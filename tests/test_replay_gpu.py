@@ -36,7 +36,15 @@ def setup(request, tmp_path_factory):
     seqs = {f"r{i}": random_tokens(n, TINY[tag]["vocab_size"], seed=10 + i) for i, n in enumerate(LENGTHS[tag])}
     want = {rid: plain.logits(t) for rid, t in seqs.items()}
     assert all(w.abs().max() > 1.0 for w in want.values())     # logits of order one, not a flat model
-    return tag, folder, seqs, want
+    if tag == "c":
+        # the product with the gate in its epilogue is taken from 1,024 rows on; these prompts are shorter, so
+        # for this configuration the bar is lowered and portions of 17 tokens or more go through it
+        from jax_vllm_b200.parts.feed_forward import GatedMLP
+        before, GatedMLP.FUSED_GATE_ROWS = GatedMLP.FUSED_GATE_ROWS, 17
+        yield tag, folder, seqs, want
+        GatedMLP.FUSED_GATE_ROWS = before
+        return
+    yield tag, folder, seqs, want
 
 
 def replay(folder, tag, dtype, steps, out_dir, max_tokens):
