@@ -12,7 +12,7 @@ from tests.util import PAGE_SIZE, TINY, make_folder, random_tokens
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(scope="module", params=["a", "b"])
+@pytest.fixture(scope="module", params=["a", "b", "d"])
 def setup(request, tmp_path_factory):
     tag = request.param
     folder = make_folder(tmp_path_factory.mktemp(f"gen_{tag}"), tag, seed=5)
@@ -72,7 +72,7 @@ def test_preemption_and_prefix_reuse_leave_tokens_unchanged(setup):
     tag, folder, plain = setup
     vocab, P = TINY[tag]["vocab_size"], PAGE_SIZE[tag]
     shared = random_tokens(2 * P, vocab, seed=70)
-    prompts = [shared + random_tokens(5, vocab, seed=71), shared + random_tokens(9, vocab, seed=72),
+    prompts = [shared + random_tokens(P // 2 + 1, vocab, seed=71), shared + random_tokens(P + 1, vocab, seed=72),
                random_tokens(2 * P + 3, vocab, seed=73)]
     want = [plain.greedy(p, 2 * P) for p in prompts]
     model = load(folder, "fp32")

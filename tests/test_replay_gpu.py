@@ -18,7 +18,7 @@ from tests.util import PAGE_SIZE, TINY, collect, make_folder, portions, prefix_t
 
 pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parent.parent
-LENGTHS = {"a": [70, 45, 100, 33], "b": [90, 38, 64, 51], "c": [200, 70, 300, 130]}
+LENGTHS = {"a": [70, 45, 100, 33], "b": [90, 38, 64, 51], "c": [200, 70, 300, 130], "d": [61, 40, 83, 35]}
 
 
 def limits(dtype, want: torch.Tensor):
@@ -28,7 +28,7 @@ def limits(dtype, want: torch.Tensor):
     return (1e-4 if dtype == "float32" else 3e-2) * scale
 
 
-@pytest.fixture(scope="module", params=["a", "b", "c"])
+@pytest.fixture(scope="module", params=["a", "b", "c", "d"])
 def setup(request, tmp_path_factory):
     tag = request.param
     folder = make_folder(tmp_path_factory.mktemp(f"model_{tag}"), tag, seed=3)

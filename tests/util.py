@@ -23,8 +23,14 @@ TINY_B = dict(architectures=["Qwen3ForCausalLM"], vocab_size=384, hidden_size=96
 TINY_C = dict(architectures=["Qwen3ForCausalLM"], vocab_size=300, hidden_size=192, intermediate_size=384,
               num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=128, rms_norm_eps=1e-6,
               rope_theta=5e5, max_position_embeddings=1024, tie_word_embeddings=False)
-TINY = {"a": TINY_A, "b": TINY_B, "c": TINY_C}
-PAGE_SIZE = {"a": 16, "b": 8, "c": 16}
+# A fourth one with sizes that are not even multiples of 16: width 120, 5 heads without grouping, head size 48
+# (the tensor-core kernels do not take it: the bfloat16 path then runs the CUDA-core attention), one layer,
+# an odd vocabulary, pages of 4 tokens.
+TINY_D = dict(architectures=["Qwen3ForCausalLM"], vocab_size=301, hidden_size=120, intermediate_size=136,
+              num_hidden_layers=1, num_attention_heads=5, num_key_value_heads=5, head_dim=48, rms_norm_eps=3e-6,
+              rope_theta=2e4, max_position_embeddings=512, tie_word_embeddings=True)
+TINY = {"a": TINY_A, "b": TINY_B, "c": TINY_C, "d": TINY_D}
+PAGE_SIZE = {"a": 16, "b": 8, "c": 16, "d": 4}
 
 
 def tensor_shapes(c: dict) -> dict:
