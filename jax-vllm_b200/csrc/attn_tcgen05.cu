@@ -54,15 +54,18 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, int bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
+__device__ __forceinline__ bool mbar_try(uint64_t* bar, int parity) {
+  uint32_t done;
+  asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+               : "=r"(done) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return done != 0;
+}
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, int parity) {
+  if (mbar_try(bar, parity)) return true;          // the usual case costs no reading of the clock
   const long long deadline = clock64() + WAIT_CYCLES;
-  while (true) {
-    uint32_t done;
-    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
-                 : "=r"(done) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-    if (done) return true;
+  while (!mbar_try(bar, parity))
     if (clock64() > deadline) return false;
-  }
+  return true;
 }
 __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int x, int y, int z, uint64_t* bar) {
   asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];\n"
@@ -146,6 +149,14 @@ __device__ __forceinline__ float fast_exp2(float x) {
 #define TC_FENCE_BEFORE() asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory")
 #define TC_FENCE_AFTER() asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory")
 #define PROXY_FENCE() asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory")
+
+// Barrier of the 256 softmax threads that also tells every one of them whether any had `flag` set.
+__device__ __forceinline__ bool softmax_barrier_or(bool flag) {
+  uint32_t any;
+  asm volatile("{\n.reg .pred p, q;\nsetp.ne.b32 q, %1, 0;\nbar.red.or.pred p, 1, 256, q;\nselp.u32 %0, 1, 0, p;\n}\n"
+               : "=r"(any) : "r"((uint32_t)flag) : "memory");
+  return any != 0;
+}
 
 struct Shared {
   uint64_t q_full, k_full[KV_STAGES], k_empty[KV_STAGES], v_full[KV_STAGES], v_empty[KV_STAGES];
@@ -351,15 +362,20 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tcgen05_kernel(const __grid_c
             }
           my_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
         }
-        // ---- the row's maximum over the tile: exchange with the thread that has the other 64 keys
-        sh->xch[half][r] = my_max;
-        asm volatile("bar.sync 1, 256;\n" ::: "memory");
-        const float m_tile = fmaxf(sh->xch[0][r], sh->xch[1][r]);
-        asm volatile("bar.sync 1, 256;\n" ::: "memory");          // both have read before the next tile writes
+        // ---- the reference moves only if some score of the tile has outgrown it (always in a row's first tile
+        // with keys, rarely later): one barrier tells all 256 threads whether any row is in that case, and only
+        // then do the two threads of a row exchange their maxima
+        const bool outgrown = ok && my_max != -INFINITY && (m_ref == -INFINITY || (my_max - m_ref) * p.scale_log2 > LAZY);
         float alpha = 1.f;
-        if (ok && m_tile != -INFINITY && (m_ref == -INFINITY || (m_tile - m_ref) * p.scale_log2 > LAZY)) {
-          alpha = (m_ref == -INFINITY) ? 0.f : fast_exp2((m_ref - m_tile) * p.scale_log2);
-          m_ref = m_tile;
+        if (softmax_barrier_or(outgrown)) {
+          sh->xch[half][r] = my_max;
+          asm volatile("bar.sync 1, 256;\n" ::: "memory");
+          const float m_tile = fmaxf(sh->xch[0][r], sh->xch[1][r]);
+          asm volatile("bar.sync 1, 256;\n" ::: "memory");          // both have read before a later tile writes
+          if (ok && m_tile != -INFINITY && (m_ref == -INFINITY || (m_tile - m_ref) * p.scale_log2 > LAZY)) {
+            alpha = (m_ref == -INFINITY) ? 0.f : fast_exp2((m_ref - m_tile) * p.scale_log2);
+            m_ref = m_tile;
+          }
         }
         const float m_scaled = (m_ref == -INFINITY) ? 0.f : m_ref * p.scale_log2;
         // ---- O is rescaled only if some row of this warp moved its reference; the previous P V must be complete then
