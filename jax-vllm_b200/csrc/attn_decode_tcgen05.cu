@@ -20,6 +20,13 @@
 // ascending order (nobody waits).  Every mbarrier wait is bounded by a clock deadline and reports to the
 // status word.
 //
+// Two ways in: after a kernel that has normed and rotated the queries and written the new token's key and value
+// into the cache (csrc/rope_kv.cu: steps that mix prompt portions and single tokens), or, for steps of single
+// tokens only, straight after the product q|k|v: a warp of this kernel then norms and rotates the segment's
+// queries into the operand tile, and the block that holds a pair's last tile does the same for the new key,
+// writes key and value to the cache, and adds the new token to the softmax as one more key at the pair's end.
+// Nothing that this kernel streams depends on the kernel before it then: only that warp waits for it.
+//
 // Restrictions (the caller falls back to the mma.sync kernel): bfloat16, head size 128, no window, at most
 // 16 query heads per kv head, page size a power of two from 8 to 128, at most 512 requests.
 #include "common.cuh"
@@ -51,6 +58,13 @@ struct Params {
   int n_work, n_q_heads, n_kv_heads, page_size, num_pages;
   float scale_log2;
   int* status;
+  // with the preparation of queries, keys and values in this kernel (FUSED): the product q|k|v as it comes
+  // (rows of qkv_stride elements: query heads, key heads, value heads), the tables and weights of the per-head
+  // norm and the rotation, and the caches to write the new token's key and value to
+  const __nv_bfloat16* qkv; int qkv_stride;
+  const float* inv_freq;                      // [64] or null (no rotation)
+  const void* q_norm_w; const void* k_norm_w; int norm_w_f32; float eps;    // null: no norm
+  __nv_bfloat16* k_cache; __nv_bfloat16* v_cache;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -170,6 +184,8 @@ struct Shared {
   float m_ref[NH];               // reference maxima of the running segment (raw score units)
   float alpha[NH];
   float red[4][NH];              // per-warp partial maxima / sums
+  float s_new[2][NH];            // FUSED: raw scores of the new token's key, per segment buffer
+  float v_new[2][D];             // FUSED: the new token's value
   int entry[MAX_WORK];           // request of work item i
   int pos[MAX_WORK];             // its query position (= number of keys before it)
   int token[MAX_WORK];           // its row in q and out
@@ -179,7 +195,11 @@ struct Shared {
 // Where a role stands in the list of tiles: work item, kv head, tile of the pair, tiles of the pair, segment number.
 struct Cursor { int i, head, j, nt, seg; };
 
-template <int GP>                 // query heads per kv head, rounded up to 4, 8 or 16
+// FUSED: the kernel takes q|k|v as the product leaves it and does the per-head norm, the rotation and the write
+// of the new token's key and value itself; the new token (not in the cache while the kernel streams it) joins
+// the softmax as one more key at the end of the pair's last tile.  Otherwise a kernel before this one has done
+// all that, and the new token's key and value are read from the cache like the others.
+template <int GP, bool FUSED>     // GP: query heads per kv head, rounded up to 4, 8 or 16
 __global__ void __launch_bounds__(THREADS, 1) attn_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map,
                                                                          const __grid_constant__ CUtensorMap k_map,
                                                                          const __grid_constant__ CUtensorMap v_map,
@@ -300,7 +320,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_tcgen05_kernel(const _
       int page = -1;
       if (wanted && lane < pages_per_tile) {
         const int pi = c.j * pages_per_tile + lane;
-        if (pi * P <= sh->pos[c.i] && pi < p.table_width) {
+        if (pi * P < sh->pos[c.i] + (FUSED ? 0 : 1) && pi < p.table_width) {
           page = p.block_table[(size_t)sh->entry[c.i] * p.table_width + pi];
           if (page < 0 || page >= p.num_pages) { atomicOr(p.status, JV_STATUS_BAD_PAGE); page = -1; }
         }
@@ -333,31 +353,143 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_tcgen05_kernel(const _
       Cursor n = c;
       advance(n);
       const int pages_next = tile_pages(n, t + 1 < ntb);
-      if (!waited && c.j == c.nt - 1) { pdl_wait(); waited = true; }
+      if (!FUSED && !waited && c.j == c.nt - 1) { pdl_wait(); waited = true; }
       if (ok) ok = load_tile(t, pages, c.head);
       pages = pages_next;
       c = n;
     }
     if (!ok && lane == 0) atomicOr(p.status, JV_STATUS_WAIT_EXPIRED);
   } else if (warp == 7) {
-    // ------------------------------------------------------------------ query producer: one load per segment
-    if (lane == 0) {
+    // ------------------------------------------------------------------ query producer: once per segment
+    if constexpr (!FUSED) {
+      if (lane == 0) {
+        pdl_wait();
+        Cursor c = c0;
+        bool ok = true;
+        for (int t = 0; t < ntb && ok; ++t) {
+          if (t == 0 || c.j == 0) {               // a segment begins (the buffer was last read two segments ago)
+            const int sp = c.seg & 1;
+            if (c.seg >= 2) ok = mbar_wait(&sh->q_empty[sp], ((c.seg >> 1) - 1) & 1);
+            if (ok) {
+              mbar_expect_tx(&sh->q_full[sp], G * 128 * 2);
+              tma_load_3d(q_s + sp * SMALL_BYTES, &q_map, 0, c.head * G, sh->token[c.i], &sh->q_full[sp]);
+              tma_load_3d(q_s + sp * SMALL_BYTES + SMALL_HALF, &q_map, 64, c.head * G, sh->token[c.i], &sh->q_full[sp]);
+            }
+          }
+          advance(c);
+        }
+        if (!ok) atomicOr(p.status, JV_STATUS_WAIT_EXPIRED);
+      }
+    } else {
+      // The whole warp prepares the segment's queries from q|k|v as the product left it: per-head norm and
+      // rotation in 32-bit, rounded to bfloat16 into the swizzled operand tile.  Lane l has the elements
+      // 2l, 2l+1 of a head and their rotation partners 64+2l, 64+2l+1.  The block that holds a pair's last tile
+      // does the same for the new token's key, writes key and value to the cache (for later steps), and leaves
+      // the new key's scores and the value in shared memory for the softmax warps.
       pdl_wait();
+      auto weight = [&](const void* w, int i) -> float {
+        return p.norm_w_f32 ? reinterpret_cast<const float*>(w)[i] : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(w)[i]);
+      };
+      // norm and rotation of one head whose four elements of this lane are (lo, hi); the result is rounded as the
+      // operand will be
+      auto prepare = [&](__nv_bfloat162 lo2, __nv_bfloat162 hi2, const void* w, const float (&cs)[2], const float (&sn)[2],
+                         float (&out)[4]) {
+        const float2 lo = __bfloat1622float2(lo2), hi = __bfloat1622float2(hi2);
+        float a[2] = {lo.x, lo.y}, b[2] = {hi.x, hi.y};
+        if (w != nullptr) {
+          float ss = (a[0] * a[0] + b[0] * b[0]) + (a[1] * a[1] + b[1] * b[1]);
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+          const float inv = rsqrtf(ss / (float)D + p.eps);
+#pragma unroll
+          for (int i = 0; i < 2; ++i) { a[i] = a[i] * inv * weight(w, 2 * lane + i); b[i] = b[i] * inv * weight(w, 64 + 2 * lane + i); }
+        }
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          out[i] = __bfloat162float(__float2bfloat16_rn(a[i] * cs[i] - b[i] * sn[i]));
+          out[2 + i] = __bfloat162float(__float2bfloat16_rn(b[i] * cs[i] + a[i] * sn[i]));
+        }
+      };
       Cursor c = c0;
       bool ok = true;
       for (int t = 0; t < ntb && ok; ++t) {
-        if (t == 0 || c.j == 0) {               // a segment begins (the buffer was last read two segments ago)
-          const int sp = c.seg & 1;
-          if (c.seg >= 2) ok = mbar_wait(&sh->q_empty[sp], ((c.seg >> 1) - 1) & 1);
+        if (t == 0 || c.j == 0) {
+          const int sp = c.seg & 1, pos = sh->pos[c.i];
+          const bool has_last = t + (c.nt - 1 - c.j) < ntb;          // the pair's last tile is in this block's range
+          // ---- all loads first, so that they are under way together
+          const __nv_bfloat16* row = p.qkv + (size_t)sh->token[c.i] * p.qkv_stride;
+          __nv_bfloat162 q_lo[GP], q_hi[GP], k_lo, k_hi, v_lo, v_hi;
+#pragma unroll
+          for (int h = 0; h < GP; ++h) {
+            if (h < G) {
+              const __nv_bfloat16* src = row + (size_t)(c.head * G + h) * D;
+              q_lo[h] = *reinterpret_cast<const __nv_bfloat162*>(src + 2 * lane);
+              q_hi[h] = *reinterpret_cast<const __nv_bfloat162*>(src + 64 + 2 * lane);
+            }
+          }
+          int page = -1;
+          if (has_last) {
+            const __nv_bfloat16* k_src = row + (size_t)(p.n_q_heads + c.head) * D;
+            const __nv_bfloat16* v_src = row + (size_t)(p.n_q_heads + Hkv + c.head) * D;
+            k_lo = *reinterpret_cast<const __nv_bfloat162*>(k_src + 2 * lane);
+            k_hi = *reinterpret_cast<const __nv_bfloat162*>(k_src + 64 + 2 * lane);
+            v_lo = *reinterpret_cast<const __nv_bfloat162*>(v_src + 2 * lane);
+            v_hi = *reinterpret_cast<const __nv_bfloat162*>(v_src + 64 + 2 * lane);
+            const int pi = pos / p.page_size;
+            if (pi < p.table_width) page = p.block_table[(size_t)sh->entry[c.i] * p.table_width + pi];
+          }
+          float cs[2] = {1.f, 1.f}, sn[2] = {0.f, 0.f};
+          if (p.inv_freq != nullptr) {
+#pragma unroll
+            for (int i = 0; i < 2; ++i) sincosf((float)pos * p.inv_freq[2 * lane + i], &sn[i], &cs[i]);
+          }
+          if (lane == 0 && c.seg >= 2)                               // buffers of the segment before the last one:
+            ok = mbar_wait(&sh->q_empty[sp], ((c.seg >> 1) - 1) & 1) &&      // its products have read the queries,
+                 mbar_wait(&sh->o_free[sp], ((c.seg >> 1) - 1) & 1);         // its softmax the new key's scores and value
+          ok = __shfl_sync(0xffffffffu, ok, 0);
           if (ok) {
-            mbar_expect_tx(&sh->q_full[sp], G * 128 * 2);
-            tma_load_3d(q_s + sp * SMALL_BYTES, &q_map, 0, c.head * G, sh->token[c.i], &sh->q_full[sp]);
-            tma_load_3d(q_s + sp * SMALL_BYTES + SMALL_HALF, &q_map, 64, c.head * G, sh->token[c.i], &sh->q_full[sp]);
+            float kr[4] = {0.f, 0.f, 0.f, 0.f};
+            if (has_last) {
+              prepare(k_lo, k_hi, p.k_norm_w, cs, sn, kr);
+              if (page >= 0 && page < p.num_pages) {
+                const size_t slot = (((size_t)page * p.page_size + (pos % p.page_size)) * Hkv + c.head) * D;
+                *reinterpret_cast<__nv_bfloat162*>(p.k_cache + slot + 2 * lane) = __floats2bfloat162_rn(kr[0], kr[1]);
+                *reinterpret_cast<__nv_bfloat162*>(p.k_cache + slot + 64 + 2 * lane) = __floats2bfloat162_rn(kr[2], kr[3]);
+                *reinterpret_cast<__nv_bfloat162*>(p.v_cache + slot + 2 * lane) = v_lo;
+                *reinterpret_cast<__nv_bfloat162*>(p.v_cache + slot + 64 + 2 * lane) = v_hi;
+              } else if (lane == 0) {
+                atomicOr(p.status, JV_STATUS_BAD_PAGE);
+              }
+              const float2 vl = __bfloat1622float2(v_lo), vh = __bfloat1622float2(v_hi);
+              sh->v_new[sp][2 * lane] = vl.x; sh->v_new[sp][2 * lane + 1] = vl.y;
+              sh->v_new[sp][64 + 2 * lane] = vh.x; sh->v_new[sp][64 + 2 * lane + 1] = vh.y;
+            }
+            unsigned char* qt = q_s + sp * SMALL_BYTES;
+#pragma unroll
+            for (int h = 0; h < GP; ++h) {
+              if (h < G) {
+                float qr[4];
+                prepare(q_lo[h], q_hi[h], p.q_norm_w, cs, sn, qr);
+                // element d of head h: half d / 64, row h of 128 bytes, 16-byte chunk (d % 64) / 8 swizzled with the row
+                const int off = h * 128 + ((((2 * lane) >> 3) ^ (h & 7)) << 4) + ((2 * lane) & 7) * 2;
+                *reinterpret_cast<__nv_bfloat162*>(qt + off) = __floats2bfloat162_rn(qr[0], qr[1]);
+                *reinterpret_cast<__nv_bfloat162*>(qt + SMALL_HALF + off) = __floats2bfloat162_rn(qr[2], qr[3]);
+                if (has_last) {
+                  float dot = qr[0] * kr[0] + qr[1] * kr[1] + qr[2] * kr[2] + qr[3] * kr[3];
+#pragma unroll
+                  for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+                  if (lane == 0) sh->s_new[sp][h] = dot;
+                }
+              }
+            }
+            PROXY_FENCE();                        // the queries are read by the tensor core
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sh->q_full[sp]);
           }
         }
         advance(c);
       }
-      if (!ok) atomicOr(p.status, JV_STATUS_WAIT_EXPIRED);
+      if (!ok && lane == 0) atomicOr(p.status, JV_STATUS_WAIT_EXPIRED);
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------------- mma issuer
@@ -411,6 +543,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_tcgen05_kernel(const _
     const int row = quad * 32 + lane;                            // key row of the tile, and d for O^T
     const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
     float l_part[GP];
+    int seg_j0 = 0;                                              // first tile (of its pair) of the running segment
     Cursor c = c0;
     bool ok = true;
     for (int t = 0; t < ntb; ++t) {
@@ -418,13 +551,15 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_tcgen05_kernel(const _
       const int sp = c.seg & 1, pos = sh->pos[c.i];
       const uint32_t tmem_o = tmem + 32 + sp * NH + lane_addr;
       if (first) {
+        seg_j0 = c.j;
 #pragma unroll
         for (int h = 0; h < GP; ++h) l_part[h] = 0.f;
       }
       if (ok) ok = mbar_wait(&sh->s_full[t & 1], (t >> 1) & 1);
       ok = __all_sync(0xffffffffu, ok);
       float sc[GP];
-      const bool valid = c.j * BN + row <= pos;                  // only a pair's last tile has keys past the end
+      const int n_keys = FUSED ? pos : pos + 1;                  // keys of the pair that are in the cache
+      const bool valid = c.j * BN + row < n_keys;                // only a pair's last tile has keys past the end
       bool exceeds = false;
       if (ok) {
         TC_FENCE_AFTER();
@@ -483,11 +618,11 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_tcgen05_kernel(const _
           }
         }
         // ---- in a pair's last tile the value rows past the end become zero (they may hold anything)
-        if (c.j == c.nt - 1 && pos + 1 < (c.j + 1) * BN) {
+        if (c.j == c.nt - 1 && n_keys < (c.j + 1) * BN) {
           const int s = t % STAGES;
           ok = __all_sync(0xffffffffu, mbar_wait(&sh->v_full[s], (t / STAGES) & 1));
           if (ok) {
-            const int from = pos + 1 - c.j * BN;
+            const int from = n_keys - c.j * BN;
             for (int i = (threadIdx.x - 64); i < (BN - from) * 16; i += 128) {
               const int key_row = from + i / 16, part = i % 16;
               *reinterpret_cast<uint4*>(v_s + s * TILE_BYTES + (part >> 3) * HALF_BYTES + key_row * 128 + (part & 7) * 16) =
@@ -522,10 +657,33 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_tcgen05_kernel(const _
         ok = __all_sync(0xffffffffu, ok);
         if (ok) {
           TC_FENCE_AFTER();
-          float o[GP];
+          float o[GP], m_out[GP];
           tmem_ld<GP>(tmem_o, o);
+#pragma unroll
+          for (int h = 0; h < GP; ++h) m_out[h] = sh->m_ref[h];
+          if constexpr (FUSED) {
+            if (c.j == c.nt - 1) {
+              // ---- the pair ends here: the new token, whose key and value are not in the cache yet, is one more
+              // key, with its raw scores and its value left in shared memory by the query producer
+              const bool had_keys = seg_j0 * BN < n_keys;            // else this segment is an empty last tile
+              const float v = sh->v_new[sp][row];
+#pragma unroll
+              for (int h = 0; h < GP; ++h) {
+                if (h < G) {
+                  const float s_h = sh->s_new[sp][h];
+                  const float ref = had_keys ? m_out[h] : -INFINITY;
+                  const float m_fin = fmaxf(ref, s_h);
+                  const float keep = (ref == -INFINITY) ? 0.f : fast_exp2((ref - m_fin) * p.scale_log2);
+                  const float p_new = fast_exp2((s_h - m_fin) * p.scale_log2);
+                  o[h] = o[h] * keep + p_new * v;
+                  l_all[h] = l_all[h] * keep + p_new;
+                  m_out[h] = m_fin;
+                }
+              }
+            }
+          }
           TC_FENCE_BEFORE();
-          mbar_arrive(&sh->o_free[sp]);
+          mbar_arrive(&sh->o_free[sp]);            // (after the reads above: the next but one segment may overwrite them)
           if (b_first == b_last) {              // the whole pair was this block's: normalise and write it
 #pragma unroll
             for (int h = 0; h < GP; ++h)
@@ -538,7 +696,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_tcgen05_kernel(const _
               if (h < G) {
                 p.part_o[(slot + h) * D + row] = o[h];
                 if (row == 0) {
-                  p.part_ml[(slot + h) * 2] = sh->m_ref[h] * p.scale_log2;
+                  p.part_ml[(slot + h) * 2] = m_out[h] * p.scale_log2;
                   p.part_ml[(slot + h) * 2 + 1] = l_all[h];
                 }
               }
@@ -627,17 +785,18 @@ PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
 
 constexpr size_t SMEM_BYTES = 2 * STAGES * TILE_BYTES + 4 * SMALL_BYTES + sizeof(Shared) + 1024;
 
-template <int GP>
+template <int GP, bool FUSED>
 int launch(int n_blocks, cudaStream_t stream, const CUtensorMap& q_map, const CUtensorMap& k_map, const CUtensorMap& v_map,
            const Params& p) {
   static bool ready = false;
   if (!ready) {
-    if (cudaFuncSetAttribute(attn_decode_tcgen05_kernel<GP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES) !=
-        cudaSuccess)
+    if (cudaFuncSetAttribute(attn_decode_tcgen05_kernel<GP, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)SMEM_BYTES) != cudaSuccess)
       return JV_ERR_UNSUPPORTED;
     ready = true;
   }
-  return jv_launch(attn_decode_tcgen05_kernel<GP>, dim3(n_blocks), dim3(THREADS), SMEM_BYTES, stream, q_map, k_map, v_map, p);
+  return jv_launch(attn_decode_tcgen05_kernel<GP, FUSED>, dim3(n_blocks), dim3(THREADS), SMEM_BYTES, stream, q_map, k_map, v_map,
+                   p);
 }
 }  // namespace
 
@@ -660,11 +819,18 @@ JV_EXPORT void jv_attn_decode_tcgen05_scratch(int n_work, int n_q_heads, int n_k
 // q [n_tokens, q_stride]; part_o and part_ml: scratch of the sizes that jv_attn_decode_tcgen05_scratch gives;
 // counters [n_work * n_kv_heads], zero before the first launch (a launch leaves them zero); n_blocks: the
 // size of the grid, best the number of multiprocessors.
+//
+// fused != 0: `q` is the product q|k|v as it comes ([n_tokens, q_stride]: query heads, key heads, value heads);
+// the kernel applies the per-head norm (weights q_norm_w, k_norm_w of head_dim elements, float if norm_w_f32
+// else bfloat16; null: no norm) and the rotation (inv_freq [head_dim/2] float; null: none) at position
+// start_pos[.], and writes the new token's key and value into the caches itself.
 JV_EXPORT int jv_attn_decode_tcgen05(const void* q, int q_stride, int n_tokens, void* out, int out_stride, float* part_o,
-                                     float* part_ml, int* counters, const void* k_cache, const void* v_cache,
+                                     float* part_ml, int* counters, void* k_cache, void* v_cache,
                                      const int* block_table, int table_width, const int* cu_seqlens, const int* start_pos,
                                      const int* work, int n_work, int n_q_heads, int n_kv_heads, int head_dim, int page_size,
-                                     int num_pages, float scale, int n_blocks, int* status, cudaStream_t stream) {
+                                     int num_pages, float scale, int n_blocks, int fused, const float* inv_freq,
+                                     const void* q_norm_w, const void* k_norm_w, int norm_w_f32, float eps, int* status,
+                                     cudaStream_t stream) {
   if (n_work == 0) return JV_OK;
   if (!jv_attn_decode_tcgen05_supports(head_dim, n_q_heads, n_kv_heads, page_size, 0, n_work) || n_blocks < 1)
     return JV_ERR_UNSUPPORTED;
@@ -690,7 +856,7 @@ JV_EXPORT int jv_attn_decode_tcgen05(const void* q, int q_stride, int n_tokens, 
     const cuuint64_t strides[3] = {(cuuint64_t)D * 2, (cuuint64_t)n_kv_heads * D * 2, (cuuint64_t)page_size * n_kv_heads * D * 2};
     const cuuint32_t box[4] = {64, 1, (cuuint32_t)page_size, 1};
     const cuuint32_t es[4] = {1, 1, 1, 1};
-    if (fn(which ? &v_map : &k_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(which ? v_cache : k_cache), dims,
+    if (fn(which ? &v_map : &k_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, (which ? v_cache : k_cache), dims,
            strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
       return JV_ERR_UNSUPPORTED;
@@ -700,7 +866,15 @@ JV_EXPORT int jv_attn_decode_tcgen05(const void* q, int q_stride, int n_tokens, 
   p.block_table = block_table; p.table_width = table_width; p.cu_seqlens = cu_seqlens; p.start_pos = start_pos; p.work = work;
   p.n_work = n_work; p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads; p.page_size = page_size; p.num_pages = num_pages;
   p.scale_log2 = scale * LOG2E; p.status = status;
-  if (G <= 4) return launch<4>(n_blocks, stream, q_map, k_map, v_map, p);
-  if (G <= 8) return launch<8>(n_blocks, stream, q_map, k_map, v_map, p);
-  return launch<16>(n_blocks, stream, q_map, k_map, v_map, p);
+  p.qkv = (const __nv_bfloat16*)q; p.qkv_stride = q_stride; p.inv_freq = inv_freq; p.q_norm_w = q_norm_w; p.k_norm_w = k_norm_w;
+  p.norm_w_f32 = norm_w_f32; p.eps = eps; p.k_cache = (__nv_bfloat16*)k_cache; p.v_cache = (__nv_bfloat16*)v_cache;
+  if (fused) {
+    if (q_stride < (n_q_heads + 2 * n_kv_heads) * D) return JV_ERR_UNSUPPORTED;
+    if (G <= 4) return launch<4, true>(n_blocks, stream, q_map, k_map, v_map, p);
+    if (G <= 8) return launch<8, true>(n_blocks, stream, q_map, k_map, v_map, p);
+    return launch<16, true>(n_blocks, stream, q_map, k_map, v_map, p);
+  }
+  if (G <= 4) return launch<4, false>(n_blocks, stream, q_map, k_map, v_map, p);
+  if (G <= 8) return launch<8, false>(n_blocks, stream, q_map, k_map, v_map, p);
+  return launch<16, false>(n_blocks, stream, q_map, k_map, v_map, p);
 }

@@ -407,16 +407,36 @@ def _multiprocessors(device) -> int:
 def attn_decode_tcgen05(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                         block_table: torch.Tensor, cu_seqlens: torch.Tensor, start_pos: torch.Tensor,
                         work: torch.Tensor, n_work: int, n_q_heads: int, n_kv_heads: int, head_dim: int,
-                        scale: float) -> None:
+                        scale: float, prepare: tuple | None = None) -> None:
     """Decode attention (single tokens) with the keys of a tile as tensor-core rows and scores and output in
     tensor memory; one persistent launch shares the key tiles of all requests evenly among the
-    multiprocessors (csrc/attn_decode_tcgen05.cu).  `work`, `cu_seqlens`, `start_pos` as for `attn_mma`."""
+    multiprocessors (csrc/attn_decode_tcgen05.cu).  `work`, `cu_seqlens`, `start_pos` as for `attn_mma`.
+
+    `prepare` = (inv_freq or None, q_norm_weight or None, k_norm_weight or None, eps): `q` is then the product
+    q|k|v as it comes, and the kernel does what `rope_kv` does for these tokens itself (per-head norm,
+    rotation at position start_pos, write of the new key and value into the caches)."""
     for t, nm in ((q, "q"), (out, "out"), (k_cache, "k_cache"), (v_cache, "v_cache")):
         _cuda(t, nm, torch.bfloat16, contiguous=(nm != "q"))
     for t, nm in ((block_table, "block_table"), (cu_seqlens, "cu_seqlens"), (start_pos, "start_pos"), (work, "work")):
         _cuda(t, nm, torch.int32)
     if n_work == 0:
         return
+    inv_freq = q_w = k_w = None
+    eps, w_f32 = 0.0, 0
+    if prepare is not None:
+        inv_freq, q_w, k_w, eps = prepare
+        if inv_freq is not None:
+            _cuda(inv_freq, "inv_freq", torch.float32)
+            if inv_freq.numel() != head_dim // 2:
+                raise KernelError("the kernel rotates whole heads only")
+        if (q_w is None) != (k_w is None):
+            raise KernelError("norm weights for queries and keys come together")
+        if q_w is not None:
+            _cuda(q_w, "q_norm_weight"); _cuda(k_w, "k_norm_weight")
+            if q_w.dtype != k_w.dtype or q_w.numel() != head_dim or k_w.numel() != head_dim:
+                raise KernelError("norm weights must have one dtype and head_dim elements")
+            w_f32 = 1 if q_w.dtype == torch.float32 else 0
+            _code(q_w, "q_norm_weight")
     n_blocks = _multiprocessors(q.device)
     slots = n_work * n_kv_heads + n_blocks
     g = n_q_heads // max(n_kv_heads, 1)
@@ -425,11 +445,13 @@ def attn_decode_tcgen05(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cac
     counters = _split_counters(q.device, n_work * n_kv_heads)
     f = _fn("attn_decode_tcgen05", "jv_attn_decode_tcgen05",
             [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
-             c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p])
+             c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p,
+             c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p])
     _check(f(q.data_ptr(), q_stride, q.shape[0], out.data_ptr(), out.stride(0), part_o.data_ptr(), part_ml.data_ptr(),
              counters.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_table.data_ptr(), block_table.shape[1],
              cu_seqlens.data_ptr(), start_pos.data_ptr(), work.data_ptr(), n_work, n_q_heads, n_kv_heads, head_dim,
-             k_cache.shape[1], k_cache.shape[0], float(scale), n_blocks, status_word(q.device).data_ptr(), _stream()),
+             k_cache.shape[1], k_cache.shape[0], float(scale), n_blocks, 0 if prepare is None else 1, _ptr(inv_freq),
+             _ptr(q_w), _ptr(k_w), w_f32, float(eps), status_word(q.device).data_ptr(), _stream()),
            "attn_decode_tcgen05")
 
 

@@ -101,13 +101,28 @@ class Attention(Part):
         qkv = ops.linear(x, self.w_qkv, dt)
         table = step.block_tables[cache.group]
         writes = self.writes_cache and cache.writes
+        out = torch.empty((step.n_tokens, self.hq * self.d), dtype=dt, device=x.device)
+        dwork, n_dec = step.decode_work
+        if writes and n_dec == step.n_tokens and self._decode_kernel_prepares(cache, n_dec):
+            # single tokens only: the decode kernel does the norm, the rotation and the cache write itself
+            freq = self.position.table() if self.position is not None else None
+            ops.attn_decode_tcgen05(qkv, qkv.stride(0), out, cache.k, cache.v, table, step.cu_seqlens, step.start_pos,
+                                    dwork, n_dec, self.hq, self.hkv, self.d, self.spec.scale,
+                                    prepare=(freq, self.q_norm, self.k_norm, self.spec.qk_norm_eps or 0.0))
+            return ops.linear(out, self.w_o, dt, parts_ok=True)
         ops.rope_kv(qkv, step.positions, step.token_entry, table,
                     self.position.table() if self.position is not None else None,
                     self.q_norm, self.k_norm, self.spec.qk_norm_eps or 0.0,
                     cache.k if writes else None, cache.v if writes else None, self.hq, self.hkv, self.d)
-        out = torch.empty((step.n_tokens, self.hq * self.d), dtype=dt, device=x.device)
         self.attend(qkv, out, step, cache, table)
         return ops.linear(out, self.w_o, dt, parts_ok=True)    # maybe the parts of a sum, for the next norm to add
+
+    def _decode_kernel_prepares(self, cache, n_dec) -> bool:
+        """Whether the tcgen05 decode kernel takes these tokens together with their preparation (it rotates whole
+        heads only)."""
+        return (ops.attn_decode_tcgen05_supports(self.ctx.dtype, self.d, self.hq, self.hkv, cache.k.shape[1], self.window,
+                                                 n_dec)
+                and (self.position is None or self.position.dim == self.d))
 
     def attend(self, qkv, out, step, cache, table):
         common = (cache.k, cache.v, table, step.cu_seqlens, step.start_pos)

@@ -523,6 +523,79 @@ def test_tcgen05_decode_attention_twice_in_a_row_and_many_requests(ops):
         torch.testing.assert_close(got, want, **BF16_TOL)
 
 
+@pytest.mark.parametrize("hq,hkv,page,with_norm,with_rope", [(32, 8, 16, True, True), (4, 1, 8, True, True), (6, 2, 64, False, True),
+                                                             (16, 1, 32, True, False), (5, 1, 128, False, False)])
+def test_tcgen05_decode_attention_that_prepares_its_tokens(ops, hq, hkv, page, with_norm, with_rope):
+    """The kernel is given q|k|v as the product leaves it: it must do what rope_kv does (per-head norm, rotation,
+    write of the new key and value) and attend over the cached keys and the new one."""
+    d, G = 128, hq // hkv
+    g = torch.Generator().manual_seed(hq * 7 + page)
+    starts = [0, 1, 31, 127, 128, 129, 300, 1023, 1500, 256]      # keys in the cache before the new token
+    R = len(starts)
+    pages_per = [-(-(t + 1) // page) for t in starts]
+    num_pages = sum(pages_per) + 3
+    perm = torch.randperm(num_pages, generator=g).tolist()
+    table = torch.full((R, max(pages_per)), -1, dtype=torch.int32)
+    kc = torch.full((num_pages, page, hkv, d), float("nan"))
+    vc = torch.full((num_pages, page, hkv, d), float("nan"))
+    ks, vs, slot_of_new = [], [], []
+    bf = lambda t: t.to(torch.bfloat16).float()
+    for e in range(R):
+        k, v = bf(torch.randn(starts[e], hkv, d, generator=g)), bf(torch.randn(starts[e], hkv, d, generator=g))
+        ks.append(k); vs.append(v)
+        for i in range(pages_per[e]):
+            pg = perm.pop()
+            table[e, i] = pg
+            m = max(0, min(page, starts[e] - i * page))
+            kc[pg, :m] = k[i * page:i * page + m]
+            vc[pg, :m] = v[i * page:i * page + m]
+        slot_of_new.append((int(table[e, starts[e] // page]), starts[e] % page))
+    qkv = bf(torch.randn(R, (hq + 2 * hkv) * d, generator=g))
+    qw = bf(1 + 0.1 * torch.randn(d, generator=g)) if with_norm else None
+    kw = bf(1 + 0.1 * torch.randn(d, generator=g)) if with_norm else None
+    theta, eps = 1e6, 1e-6
+    inv_freq = 1.0 / (theta ** (torch.arange(0, d, 2, dtype=torch.float32) / d)) if with_rope else None
+    # ---- what it should be: the plain formulas on the same values, rounded where the engine rounds
+    pos = torch.tensor(starts)
+    q = qkv[:, : hq * d].reshape(R, hq, d).transpose(0, 1)
+    k_new = qkv[:, hq * d:(hq + hkv) * d].reshape(R, hkv, d).transpose(0, 1)
+    v_new = qkv[:, (hq + hkv) * d:].reshape(R, hkv, d)
+    if with_norm:
+        q, k_new = plain.rms_norm(q, qw, eps), plain.rms_norm(k_new, kw, eps)
+    if with_rope:
+        cos, sin = plain.rope_cos_sin(pos, d, theta)
+        q, k_new = plain.apply_rope(q, cos, sin), plain.apply_rope(k_new, cos, sin)
+    q, k_new = bf(q).transpose(0, 1), bf(k_new).transpose(0, 1)          # [R, heads, d]
+    scale = 1.0 / math.sqrt(d)
+    want = torch.cat([dense_attention(q[e:e + 1], torch.cat([ks[e], k_new[e:e + 1]]), torch.cat([vs[e], v_new[e:e + 1]]),
+                                      torch.tensor([starts[e]]), scale, 0, G) for e in range(R)])
+    # ---- the kernel
+    dq = qkv.to(torch.bfloat16).to(DEV)
+    out = torch.zeros(R, hq * d, dtype=torch.bfloat16, device=DEV)
+    dk, dv = kc.to(torch.bfloat16).to(DEV), vc.to(torch.bfloat16).to(DEV)
+    work = torch.tensor([[e, 0] for e in range(R)], dtype=torch.int32, device=DEV)
+    cu = torch.arange(R + 1, dtype=torch.int32, device=DEV)
+    dev = lambda t: None if t is None else t.to(DEV)
+    for w_dtype in ((torch.bfloat16, torch.float32) if with_norm else (None,)):
+        cast = (lambda t: None if t is None else t.to(w_dtype).to(DEV))
+        k_in, v_in = dk.clone(), dv.clone()
+        ops.attn_decode_tcgen05(dq, dq.stride(0), out, k_in, v_in, table.to(DEV), cu,
+                                torch.tensor(starts, dtype=torch.int32, device=DEV), work, R, hq, hkv, d, scale,
+                                prepare=(dev(inv_freq), cast(qw), cast(kw), eps))
+        ops.check_status()
+        got = out.float().cpu().reshape(R, hq, d)
+        assert not torch.isnan(got).any()
+        torch.testing.assert_close(got, want, **BF16_TOL)
+        # the new key and value are in the cache, and nothing else was written
+        kk, vv = k_in.float().cpu(), v_in.float().cpu()
+        for e, (pg, sl) in enumerate(slot_of_new):
+            torch.testing.assert_close(kk[pg, sl], k_new[e], atol=2e-2, rtol=2e-2)
+            assert torch.equal(vv[pg, sl], v_new[e])
+            kk[pg, sl] = kc[pg, sl]; vv[pg, sl] = vc[pg, sl]
+        same = lambda a, b: torch.equal(torch.nan_to_num(a, nan=123.0), torch.nan_to_num(b, nan=123.0))
+        assert same(kk, bf(kc)) and same(vv, bf(vc))
+
+
 def test_tcgen05_decode_support_rules(ops):
     from jax_vllm_b200.csrc import build
     lib = build.load("attn_decode_tcgen05")
