@@ -1,5 +1,6 @@
 """Decode and prefill throughput of the engine on one B200, for the Qwen3-8B shape with
-random bfloat16 weights (the metric and configuration that BASELINE.json names).
+random bfloat16 weights: the reference's headline metric (decoded tokens per second) at its largest
+dense Qwen3 configuration.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L]
 
