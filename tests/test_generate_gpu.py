@@ -128,3 +128,40 @@ def test_long_decoding_and_first_tokens(setup):
         row = runner.run([StepEntry(rc, [toks[i]], (0,))]).cpu()[0]
         assert (row - want[i]).abs().max().item() <= lim, f"position {i}"
     runner.check_kernels()
+
+
+def test_layers_of_the_benchmarked_size_in_bfloat16_follow_the_32_bit_path(tmp_path):
+    """Two layers with the widths that the kernels are tuned for (4,096 wide, 32/8 heads of 128, feed-forward
+    12,288): a prompt long enough for the product with the gate in its epilogue and the 128-row attention
+    tiles, then single tokens through the replayed graph (persistent decode attention that prepares its own
+    queries and keys, products whose k is cut into parts).  The bfloat16 engine must stay within the bfloat16
+    bound of the same engine in true 32-bit on the same weights, position by position."""
+    from jax_vllm_b200 import load_from_path, registry, write_model_folder
+    from jax_vllm_b200.engine import StepEntry, make_driver
+    cfg = dict(architectures=["Qwen3ForCausalLM"], vocab_size=2048, hidden_size=4096, intermediate_size=12288,
+               num_hidden_layers=2, num_attention_heads=32, num_key_value_heads=8, head_dim=128, rms_norm_eps=1e-6,
+               rope_theta=1e6, max_position_embeddings=4096, tie_word_embeddings=False)
+    folder = write_model_folder(tmp_path / "wide", registry.config_from_dict(cfg), seed=7)
+    lens, n_new = (1100, 300, 37), 24
+    seqs = [random_tokens(n + n_new, 2048, seed=90 + i) for i, n in enumerate(lens)]
+    logits = {}
+    for dtype in ("fp32", "bf16"):
+        model = load_from_path(folder, dtype=dtype)
+        d = make_driver(model, max_num_seqs=3, max_model_len=1280, block_size=16, prefix_cache=False,
+                        max_tokens_per_step=2048)
+        rcs = [d.cache.admit(i) for i in range(len(lens))]
+        rows = [d.runner.run([StepEntry(rc, s[:n], (n - 1,))]).float().cpu() for rc, s, n in zip(rcs, seqs, lens)]
+        for i in range(n_new):       # the three requests side by side, one token each
+            rows.append(d.runner.run([StepEntry(rc, s[n + i:n + i + 1], (0,)) for rc, s, n in zip(rcs, seqs, lens)]).float().cpu())
+        d.runner.check_kernels()
+        logits[dtype] = torch.cat(rows)
+        if dtype == "bf16":
+            assert d.runner.graphs, "single tokens were not replayed from a graph"
+        for i in range(len(lens)):
+            d.cache.release(i)
+        del d, model
+        torch.cuda.empty_cache()
+    want, got = logits["fp32"], logits["bf16"]
+    assert want.abs().max() > 1.0
+    lim = 3e-2 * max(1.0, want.abs().max().item())
+    assert (got - want).abs().max().item() <= lim
