@@ -244,7 +244,7 @@ def time_e2e(model, batch, steps, warmup, ctx=CONTEXT):
 def micro(spec: str, reps: int, eager: bool = False) -> int:
     """One kernel alone on data larger than the L2, for profiling:
     gemm:<N>x<K>:<M>:<impl>  the prompt product, impl = tcgen05 | tcgen05_swiglu | library (cuBLAS)
-    linear:<N>x<K>:<M>[:parts]   the decode product of M rows with an [N, K] weight (several weights in turn)
+    linear:<N>x<K>:<M>[:parts][:packed]   the decode product of M rows with an [N, K] weight (several weights in turn)
     attn_decode:<B>:<CTX>[:<SPLIT>[:<PAGE>[:<KV HEADS>]]]   split decode attention of B requests with CTX cached tokens (8B head layout,
                          several caches in turn so that none stays in the L2), mma.sync kernel
     attn_decode_tcgen05:<B>:<CTX>[:<SPLIT>[:<PAGE>]]   the same with the tcgen05 kernel
@@ -283,8 +283,12 @@ def micro(spec: str, reps: int, eager: bool = False) -> int:
         copies = max(2, int(400e6 // (n * k * 2)) + 1)
         ws = [(torch.randn(n, k, device=dev) * 0.02).to(torch.bfloat16) for _ in range(copies)]
         x = torch.randn(m, k, device=dev).to(torch.bfloat16)
-        parts_ok = len(rest) > 2 and rest[2] == "parts"       # let the kernel cut k and leave the parts of a sum
-        run = lambda i: ops.linear(x, ws[i % copies], parts_ok=parts_ok)
+        parts_ok = "parts" in rest[2:]        # let the kernel cut k and leave the parts of a sum
+        if "packed" in rest[2:]:              # the weight in the kernel's own order
+            ws = [ops.PackedWeight(w) for w in ws]
+            run = lambda i: ops.linear_skinny(x, ws[i % copies], torch.bfloat16, parts_ok)
+        else:
+            run = lambda i: ops.linear(x, ws[i % copies], parts_ok=parts_ok)
         nbytes = n * k * 2
     else:
         hq, hkv, d, page = 32, 8, 128, PAGE
@@ -417,7 +421,7 @@ def main():
                    "hidden": 4096, "q_heads": 32, "kv_heads": 8, "head_dim": 128, "intermediate": 12288,
                    "vocab": 151936, "global_batch": args.batch, "seq_len": CONTEXT, "max_context": 4096,
                    "page_size": PAGE, "parallelism": "none (1 GPU)", "l2": "inputs larger than L2 (15 GB of weights)",
-                   "cuda_graphs": True},
+                   "cuda_graphs": True, "decode_weight_copy": True},
         "gpu_launches": launches * args.steps,
         "clocks": clocks.summary,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",

@@ -491,12 +491,39 @@ def linear_skinny_splits(device, n: int, k: int) -> int:
     return plan
 
 
-def linear_skinny(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype, parts_ok: bool = False):
+class PackedWeight:
+    """A bfloat16 weight [n, k] in the order in which the decode product (csrc/linear_skinny.cu) reads it:
+    for every strip of 16 rows and every 64-wide chunk of k, four 512-byte pieces (rows 0-7 / 8-15 of the
+    strip x first / second 32 of the chunk), each piece lane by lane (lane = row % 8 * 4 + (k % 32) / 8, then
+    8 consecutive k); rows and k are padded with zeros to multiples of 16 and 64.  A warp's copy instruction
+    then reads 512 consecutive bytes and its chunks follow one another: the product streams the weight
+    linearly."""
+
+    def __init__(self, weight: torch.Tensor):
+        _cuda(weight, "weight", torch.bfloat16, contiguous=False)
+        n, k = weight.shape
+        n16, k64 = -(-n // 16) * 16, -(-k // 64) * 64
+        padded = weight
+        if (n16, k64) != (n, k):
+            padded = torch.zeros((n16, k64), dtype=weight.dtype, device=weight.device)
+            padded[:n, :k] = weight
+        # [strip, row half, row % 8, chunk, k half, (k % 32) / 8, k % 8] -> [strip, chunk, row half, k half, row % 8, (k % 32) / 8, k % 8]
+        v = padded.reshape(n16 // 16, 2, 8, k64 // 64, 2, 4, 8)
+        self.data = v.permute(0, 3, 1, 4, 2, 5, 6).contiguous()
+        self.shape = (n, k)
+        self.device = weight.device
+
+
+def linear_skinny(x: torch.Tensor, weight, out_dtype: torch.dtype, parts_ok: bool = False):
     """x [M <= 16, K] times weight [N, K] transposed, bfloat16 operands, 32-bit accumulation
-    (csrc/linear_skinny.cu); the result is bfloat16 or float32, or with `parts_ok`, where the kernel
-    cuts k for an even load, a PartialSum for a reader that adds the parts."""
-    _cuda(x, "x", torch.bfloat16, contiguous=False); _cuda(weight, "weight", torch.bfloat16, contiguous=False)
-    if x.dim() != 2 or weight.dim() != 2 or x.shape[1] != weight.shape[1] or x.stride(1) != 1 or weight.stride(1) != 1:
+    (csrc/linear_skinny.cu); `weight` is a tensor or a PackedWeight; the result is bfloat16 or float32, or
+    with `parts_ok`, where the kernel cuts k for an even load, a PartialSum for a reader that adds the parts."""
+    packed = isinstance(weight, PackedWeight)
+    _cuda(x, "x", torch.bfloat16, contiguous=False)
+    if not packed:
+        _cuda(weight, "weight", torch.bfloat16, contiguous=False)
+    if x.dim() != 2 or len(weight.shape) != 2 or x.shape[1] != weight.shape[1] or x.stride(1) != 1 or \
+            (not packed and weight.stride(1) != 1):
         raise KernelError(f"linear shapes {tuple(x.shape)} x {tuple(weight.shape)}^T do not fit")
     m, k = x.shape
     n = weight.shape[0]
@@ -508,9 +535,10 @@ def linear_skinny(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype,
         parts = None
         y = torch.empty((m, n), dtype=out_dtype, device=x.device)
     f = _fn("linear_skinny", "jv_linear_skinny", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
-                                                  c_int, c_void_p, c_int, c_void_p])
-    _check(f(x.data_ptr(), x.stride(0), weight.data_ptr(), weight.stride(0), _ptr(y), DTYPE_CODE[out_dtype],
-             n if y is None else y.stride(0), m, n, k, _ptr(parts), splits, _stream()), "linear_skinny")
+                                                  c_int, c_void_p, c_int, c_int, c_void_p])
+    w_ptr, ldw = (weight.data.data_ptr(), 0) if packed else (weight.data_ptr(), weight.stride(0))
+    _check(f(x.data_ptr(), x.stride(0), w_ptr, ldw, _ptr(y), DTYPE_CODE[out_dtype],
+             n if y is None else y.stride(0), m, n, k, _ptr(parts), splits, 1 if packed else 0, _stream()), "linear_skinny")
     return y if parts is None else PartialSum(parts)
 
 
@@ -544,9 +572,11 @@ def _skinny_ok(x: torch.Tensor, weight: torch.Tensor) -> bool:
             and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0 and x.stride(1) == 1)
 
 
-def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None = None, parts_ok: bool = False):
+def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None = None, parts_ok: bool = False,
+           packed=None):
     """y = x @ weight.T.  With `parts_ok` the result may be a PartialSum (the caller hands it to `rmsnorm`,
-    `residual_add` or `swiglu`, which add its parts as they read them).
+    `residual_add` or `swiglu`, which add its parts as they read them).  `packed`: the same weight as a
+    PackedWeight, which the product for a few rows reads instead.
 
     float32 weights: the CUDA-core product of this package in true 32-bit (16-bit
     activations are read as they are and widened inside).  bfloat16 weights and
@@ -558,7 +588,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None 
         return gemm_simt(x, weight, out_dtype)
     _cuda(x, "x", torch.bfloat16, contiguous=False); _cuda(weight, "weight", torch.bfloat16)
     if _skinny_ok(x, weight):
-        return linear_skinny(x, weight, out_dtype, parts_ok)
+        return linear_skinny(x, weight if packed is None else packed, out_dtype, parts_ok)
     if out_dtype == torch.bfloat16:
         return torch.mm(x, weight.t())
     return torch.mm(x, weight.t(), out_dtype=out_dtype)

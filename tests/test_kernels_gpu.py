@@ -125,6 +125,26 @@ def test_linear_skinny(ops, m, n, k, out_dtype):
     torch.testing.assert_close(y2.double(), wide[:, 8:8 + k].double() @ w.double().T, atol=1e-4, rtol=1e-4)
 
 
+@pytest.mark.parametrize("m", [1, 8, 11, 16])
+@pytest.mark.parametrize("n,k", [(70, 96), (4096, 4096), (1000, 2056), (24, 8), (151, 4104), (4096, 12288)])
+def test_linear_skinny_reads_a_weight_in_its_own_order(ops, m, n, k):
+    """The weight packed in the order of the kernel's copy instructions gives bit for bit what the rows give,
+    whole and as the parts of a sum, and `linear` takes the packed copy for a few rows only."""
+    g = torch.Generator().manual_seed(m + n)
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(n, k, generator=g) / k ** 0.5).to(torch.bfloat16).to(DEV)
+    packed = ops.PackedWeight(w)
+    assert tuple(packed.shape) == (n, k) and packed.data.numel() == (-(-n // 16) * 16) * (-(-k // 64) * 64)
+    for out_dtype in (torch.bfloat16, torch.float32):
+        assert torch.equal(ops.linear_skinny(x, packed, out_dtype), ops.linear_skinny(x, w, out_dtype))
+    a, b = ops.linear_skinny(x, packed, torch.bfloat16, parts_ok=True), ops.linear_skinny(x, w, torch.bfloat16, parts_ok=True)
+    assert type(a) is type(b)
+    assert torch.equal(a.parts, b.parts) if isinstance(a, ops.PartialSum) else torch.equal(a, b)
+    assert torch.equal(ops.linear(x, w, torch.bfloat16, packed=packed), ops.linear(x, w, torch.bfloat16))
+    many = torch.randn(40, k, generator=g).to(torch.bfloat16).to(DEV)       # more rows: the library product, from the rows
+    assert torch.equal(ops.linear(many, w, torch.bfloat16, packed=packed), ops.linear(many, w, torch.bfloat16))
+
+
 def test_linear_skinny_cuts_k_when_strips_are_few(ops):
     # few strips of a long k are cut into parts that other blocks take; many strips, or a short k, are not
     assert ops.linear_skinny_splits(DEV, 4096, 12288) > 1
