@@ -33,7 +33,8 @@ def main(argv=None) -> int:
                    help="Path to HF model directory. Env: JLLM_MODEL_PATH.")
     p.add_argument("--max-num-seqs", type=int, default=4)
     p.add_argument("--max-model-len", type=int, default=2048)
-    p.add_argument("--max-prefill-len", type=int, default=512)
+    p.add_argument("--max-prefill-len", type=int, default=None,
+                   help="longest prompt accepted (default: 512 as in the reference, or --max-model-len if that is less)")
     p.add_argument("--dtype", choices=["bf16", "fp32"], default="bf16")
     p.add_argument("--no-prewarm", dest="prewarm", action="store_false",
                    help="Skip the warm-up step at startup (kernels are then compiled and first run on the first request).")
@@ -83,8 +84,9 @@ def main(argv=None) -> int:
     if not prompts:
         p.error("give at least one --prompt-ids or --prompt")
 
+    max_prefill_len = args.max_prefill_len if args.max_prefill_len is not None else min(512, args.max_model_len)
     driver = make_driver(model, max_num_seqs=args.max_num_seqs, max_model_len=args.max_model_len,
-                         max_prefill_len=args.max_prefill_len, block_size=args.block_size, num_blocks=args.num_blocks,
+                         max_prefill_len=max_prefill_len, block_size=args.block_size, num_blocks=args.num_blocks,
                          max_tokens_per_step=args.max_tokens_per_step, prefix_cache=args.prefix_cache)
     if args.prewarm:
         print(f"prewarm: done in {prewarm(driver):.1f}s", flush=True)

@@ -165,3 +165,22 @@ def test_layers_of_the_benchmarked_size_in_bfloat16_follow_the_32_bit_path(tmp_p
     assert want.abs().max() > 1.0
     lim = 3e-2 * max(1.0, want.abs().max().item())
     assert (got - want).abs().max().item() <= lim
+
+
+def test_command_line_generates_what_plain_generates(setup):
+    """cli.py as a user runs it: a model folder, prompts as token ids, 32-bit; the printed token ids are the
+    plain implementation's greedy continuation."""
+    import json, os, subprocess, sys
+    from pathlib import Path
+    tag, folder, plain = setup
+    vocab = TINY[tag]["vocab_size"]
+    prompts = [random_tokens(9, vocab, seed=130), random_tokens(21, vocab, seed=131)]
+    root = Path(__file__).resolve().parent.parent
+    cmd = [sys.executable, str(root / "cli.py"), "--model-path", str(folder), "--dtype", "fp32", "--max-tokens", "6",
+           "--max-model-len", "64", "--block-size", str(PAGE_SIZE[tag]), "--no-prewarm"]
+    for p in prompts:
+        cmd += ["--prompt-ids", ",".join(map(str, p))]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, cwd=str(root), env=dict(os.environ))
+    assert out.returncode == 0, out.stderr[-2000:]
+    got = [json.loads(line)["output_ids"] for line in out.stdout.splitlines() if line.startswith("{")]
+    assert got == [plain.greedy(p, 6) for p in prompts]
