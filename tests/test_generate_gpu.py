@@ -184,3 +184,24 @@ def test_command_line_generates_what_plain_generates(setup):
     assert out.returncode == 0, out.stderr[-2000:]
     got = [json.loads(line)["output_ids"] for line in out.stdout.splitlines() if line.startswith("{")]
     assert got == [plain.greedy(p, 6) for p in prompts]
+
+
+def test_llm_class_and_background_thread_on_the_device(setup):
+    """The convenience class, and the entry point's background thread with streams (start, stream, stop), give
+    the plain greedy continuation."""
+    from jax_vllm_b200 import LLM, SamplingParams, add_request, start, stop, stream
+    tag, folder, plain = setup
+    vocab = TINY[tag]["vocab_size"]
+    prompts = [random_tokens(7, vocab, seed=140), random_tokens(18, vocab, seed=141)]
+    want = [plain.greedy(p, 5) for p in prompts]
+    llm = LLM(folder, dtype="fp32", max_num_seqs=2, max_model_len=64, block_size=PAGE_SIZE[tag])
+    assert llm.generate(prompts, SamplingParams(max_new_tokens=5)) == want
+    assert not llm.has_work() and llm.stats.finished == 2
+    start(llm.driver)
+    try:
+        ids = [add_request(llm.driver, p, SamplingParams(max_new_tokens=5)) for p in prompts]
+        got = [[ev.token for ev in stream(llm.driver, i)] for i in ids]
+    finally:
+        stop(llm.driver)
+    assert got == want
+    llm.driver.cache.check()
