@@ -250,7 +250,7 @@ def micro(spec: str, reps: int, eager: bool = False) -> int:
     attn_decode_tcgen05:<B>:<CTX>[:<SPLIT>[:<PAGE>]]   the same with the tcgen05 kernel
     (the decode kernels are timed as replays of a CUDA graph of one launch per cache, as the engine runs them)
     attn_prefill:<T>     prompt attention of one request of T tokens (8B head layout), mma.sync kernel
-    attn_prefill_tcgen05:<T>   the same with the tcgen05 kernel"""
+    attn_prefill_tcgen05:<T>[:<PAGE>]   the same with the tcgen05 kernel"""
     import torch
     from jax_vllm_b200 import ops
     kind, *rest = spec.split(":")
@@ -301,6 +301,7 @@ def micro(spec: str, reps: int, eager: bool = False) -> int:
             q_lens = [1] * b
         else:
             b, ctx, q_lens = 1, 0, [int(rest[0])]
+            page = int(rest[1]) if len(rest) > 1 else PAGE
         total = [ctx + q for q in q_lens]
         pages_per = [-(-t // page) for t in total]
         num_pages = sum(pages_per)

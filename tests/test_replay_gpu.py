@@ -183,3 +183,24 @@ def test_trace_run_program(setup, tmp_path):
     assert proc.returncode == 0, proc.stderr[-2000:]
     assert proc.stdout.split() == [w for s in steps for w in ("done", str(s["step"]))]
     compare(steps, tmp_path, TINY[tag]["vocab_size"], dict(want, r4=want["r0"], r5=want["r1"]), "float32")
+
+
+@pytest.mark.parametrize("head_dim,heads,kv_heads", [(80, 3, 1), (144, 2, 2), (256, 2, 1), (112, 4, 2)])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_other_head_sizes_in_steps_of_16(head_dim, heads, kv_heads, dtype, tmp_path):
+    """Head sizes that no tensor-core kernel of the engine is built for run on the CUDA-core kernels, in both
+    modes: whole, and the last tokens one by one."""
+    from tests.util import write_folder, make_weights
+    cfg = dict(architectures=["Qwen3ForCausalLM"], vocab_size=200, hidden_size=88, intermediate_size=120,
+               num_hidden_layers=2, num_attention_heads=heads, num_key_value_heads=kv_heads, head_dim=head_dim,
+               rms_norm_eps=1e-6, rope_theta=1e4, max_position_embeddings=256, tie_word_embeddings=True)
+    folder = write_folder(tmp_path / "model", cfg, make_weights(cfg, seed=head_dim))
+    toks = random_tokens(50, 200, seed=head_dim + 1)
+    want = {"r": PlainModel(folder).logits(toks)}
+    from jax_vllm_b200.engine.replay import Replayer
+    for i, steps in enumerate((whole("r", toks), prefix_then_single("r", toks, tail=12))):
+        out = tmp_path / f"out{i}"
+        rep = Replayer(folder, dtype, out, max_tokens=64, page_size=8)
+        rep.run_stream(json.dumps(s) for s in steps)
+        rep.cache.check()
+        compare(steps, out, 200, want, dtype)
