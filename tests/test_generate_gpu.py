@@ -205,3 +205,30 @@ def test_llm_class_and_background_thread_on_the_device(setup):
         stop(llm.driver)
     assert got == want
     llm.driver.cache.check()
+
+
+def test_replayed_graphs_and_planning_ahead_change_no_token(tmp_path):
+    """Many requests of mixed lengths in bfloat16 on the configuration that takes the tcgen05 kernels, with few
+    pages (requests are preempted) and more requests than slots: the engine with replayed decode graphs, sampling
+    inside the graph and the next step planned ahead gives exactly the tokens of the same engine stepping
+    eagerly.  Same kernels, same schedule: any difference is a fault of the machinery around them."""
+    from jax_vllm_b200 import SamplingParams, generate, load_from_path, make_driver
+    folder = make_folder(tmp_path / "c", "c", seed=21)
+    vocab, P = TINY["c"]["vocab_size"], PAGE_SIZE["c"]
+    model = load_from_path(folder, dtype="bf16")
+    lens = [5, 140, 33, 270, 18, 64, 129, 7, 200, 90, 31, 256]
+    prompts = [random_tokens(n, vocab, seed=300 + i) for i, n in enumerate(lens)]
+    sps = [SamplingParams(max_new_tokens=24 + (i % 5) * 9, temperature=0.0 if i % 3 else 0.7, seed=11 + i)
+           for i in range(len(prompts))]
+    outs = []
+    for graphs in (False, True):
+        d = make_driver(model, max_num_seqs=4, max_model_len=352, block_size=P, num_blocks=30, cuda_graphs=graphs,
+                        max_tokens_per_step=192)
+        outs.append(generate(d, prompts, sps))
+        d.cache.check()
+        assert not d.cache.live and d.stats.finished == len(prompts)
+        if graphs:
+            assert d.runner.graphs_sampled, "no decode step was replayed with its sampling"
+            assert d.stats.preemptions >= 1
+    assert outs[0] == outs[1]
+    assert [len(o) for o in outs[1]] == [sp.max_new_tokens for sp in sps]
