@@ -245,10 +245,13 @@ def _driver_loop(driver: Driver) -> None:
 
 
 def prewarm(driver: Driver) -> float:
-    """Compiles what the model needs and runs one tiny batch, so that the first request does
-    not pay for it.  Returns the seconds it took."""
+    """Compiles what the model needs, runs one tiny batch and captures the decode graphs of every batch size up
+    to `max_num_seqs`, so that no request pays for it (the reference compiles its shape buckets here,
+    jllm/engine/engine.py:112-150).  Returns the seconds it took."""
     t0 = time.perf_counter()
-    driver.runner.warm_up()
+    with driver.step_lock:
+        driver.ahead = None
+        driver.runner.warm_up(decode_batches=driver.max_num_seqs)
     return time.perf_counter() - t0
 
 

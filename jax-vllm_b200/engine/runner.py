@@ -223,8 +223,10 @@ class Runner:
     def clear_status(self) -> None:
         ops.status_word(self.device).zero_()
 
-    def warm_up(self) -> None:
-        """One two-token portion and one single token through every kernel of the model."""
+    def warm_up(self, decode_batches: int = 0) -> None:
+        """One two-token portion and one single token through every kernel of the model; then, with CUDA
+        graphs, the decode steps of 1 .. `decode_batches` requests with their sampling are captured (a step
+        of each size runs twice: once eagerly, once into the graph), so that no request pays for that."""
         if not self.cache.can_admit():
             return
         rc = self.cache.admit("__warm_up__")
@@ -237,6 +239,29 @@ class Runner:
         finally:
             rc.num_tokens = 0
             self.cache.release("__warm_up__")
+        if not self.cuda_graphs:
+            return
+        live = []
+        try:
+            for n in range(1, min(decode_batches, self.max_graph_batch, self.cache.max_live) + 1):
+                if not self.cache.can_admit():
+                    break
+                rc = self.cache.admit(f"__warm_up_{n}__")
+                live.append(rc)
+                if not self.cache.can_grow(rc, 2):
+                    break
+                self.cache.grow(rc, 2)
+                rc.num_tokens = 1              # as if one token were cached: the step adds the second
+                entries = [StepEntry(r, [0], (0,)) for r in live]
+                zeros = [0.0] * n
+                if self.step_sampled(entries, zeros, [0] * n, [0] * n) is None:
+                    self.step(entries)                                       # the first time at this size: eagerly
+                    self.step_sampled(entries, zeros, [0] * n, [0] * n)      # then into the graph
+            self.check_kernels()
+        finally:
+            for r in live:
+                r.num_tokens = 0
+                self.cache.release(r.request_id)
 
 
 def build_runner(spec, tensors_fn, *, dtype, device, page_size, num_pages, max_live, prefix_cache=True,

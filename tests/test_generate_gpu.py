@@ -177,7 +177,7 @@ def test_command_line_generates_what_plain_generates(setup):
     prompts = [random_tokens(9, vocab, seed=130), random_tokens(21, vocab, seed=131)]
     root = Path(__file__).resolve().parent.parent
     cmd = [sys.executable, str(root / "cli.py"), "--model-path", str(folder), "--dtype", "fp32", "--max-tokens", "6",
-           "--max-model-len", "64", "--block-size", str(PAGE_SIZE[tag]), "--no-prewarm"]
+           "--max-model-len", "64", "--block-size", str(PAGE_SIZE[tag])]
     for p in prompts:
         cmd += ["--prompt-ids", ",".join(map(str, p))]
     out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, cwd=str(root), env=dict(os.environ))
@@ -232,3 +232,20 @@ def test_replayed_graphs_and_planning_ahead_change_no_token(tmp_path):
             assert d.stats.preemptions >= 1
     assert outs[0] == outs[1]
     assert [len(o) for o in outs[1]] == [sp.max_new_tokens for sp in sps]
+
+
+def test_prewarm_captures_the_decode_graphs_and_changes_nothing(tmp_path):
+    from jax_vllm_b200 import SamplingParams, generate, load_from_path, make_driver, prewarm
+    folder = make_folder(tmp_path / "c", "c", seed=33)
+    vocab, P = TINY["c"]["vocab_size"], PAGE_SIZE["c"]
+    model = load_from_path(folder, dtype="bf16")
+    prompts = [random_tokens(n, vocab, seed=400 + n) for n in (9, 40, 3)]
+    sp = SamplingParams(max_new_tokens=12)
+    cold = make_driver(model, max_num_seqs=3, max_model_len=96, block_size=P)
+    want = generate(cold, prompts, sp)
+    warm = make_driver(model, max_num_seqs=3, max_model_len=96, block_size=P)
+    assert prewarm(warm) > 0
+    assert sorted(warm.runner.graphs_sampled) == [1, 2, 3]
+    warm.cache.check()
+    assert not warm.cache.live and warm.cache.groups[0].pool.num_free == warm.cache.num_pages
+    assert generate(warm, prompts, sp) == want
