@@ -165,6 +165,13 @@ def test_layers_of_the_benchmarked_size_in_bfloat16_follow_the_32_bit_path(tmp_p
     assert want.abs().max() > 1.0
     lim = 3e-2 * max(1.0, want.abs().max().item())
     assert (got - want).abs().max().item() <= lim
+    # and the 32-bit path at these widths against the plain implementation (on the CPU): the shortest request,
+    # its prompt's last position and every decoded position
+    plain = PlainModel(folder)
+    n = lens[2]
+    oracle = plain.logits(seqs[2])[n - 1:]
+    mine = torch.cat([want[2:3]] + [want[3 + 3 * i + 2:3 + 3 * i + 3] for i in range(n_new)])
+    assert (mine - oracle).abs().max().item() <= 1e-4 * max(1.0, oracle.abs().max().item())
 
 
 def test_command_line_generates_what_plain_generates(setup):
