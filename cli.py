@@ -47,6 +47,7 @@ def main(argv=None) -> int:
     p.add_argument("--block-size", type=int, default=16, help="tokens per cache page")
     p.add_argument("--num-blocks", type=int, default=None, help="pages in the pool (default: worst case)")
     p.add_argument("--max-tokens-per-step", type=int, default=2048)
+    p.add_argument("--ignore-eos", action="store_true", help="generate --max-tokens tokens whatever is sampled")
     p.add_argument("--no-prefix-cache", dest="prefix_cache", action="store_false")
     p.add_argument("--no-decode-weight-copy", dest="pack_decode_weights", action="store_false",
                    help="do not keep a second copy of the matrices in the order the decode product streams them "
@@ -91,7 +92,8 @@ def main(argv=None) -> int:
     if args.prewarm:
         print(f"prewarm: done in {prewarm(driver):.1f}s", flush=True)
 
-    sp = [SamplingParams(max_new_tokens=args.max_tokens, eos_id=args.eos_id, temperature=args.temperature,
+    sp = [SamplingParams(max_new_tokens=args.max_tokens, eos_id=args.eos_id, ignore_eos=args.ignore_eos,
+                         temperature=args.temperature,
                          seed=None if args.seed is None else args.seed + i) for i in range(len(prompts))]
     t0 = time.perf_counter()
     ids = [add_request(driver, pr, s) for pr, s in zip(prompts, sp)]

@@ -161,8 +161,7 @@ def _step_locked(driver: Driver) -> list:
         if req.first_token_time is None:
             req.first_token_time = now
         driver.stats.emitted_tokens += 1
-        done = len(req.output_ids) >= req.sampling.max_new_tokens or \
-            (req.sampling.eos_id is not None and tok == req.sampling.eos_id)
+        done = len(req.output_ids) >= req.sampling.max_new_tokens or req.sampling.stops_at(int(tok))
         if done:
             sched.finish(req)
         events.append(StepEvent(req.request_id, int(tok), done))

@@ -13,12 +13,20 @@ class SamplingParams:
     eos_id: Optional[int] = None      # generation stops after this token (which is emitted)
     temperature: float = 0.0          # 0: greedy; > 0: a draw from softmax(logits / temperature)
     seed: Optional[int] = None        # None: the request id
+    stop_token_ids: tuple = ()        # more tokens that end the generation (emitted, like eos_id)
+    ignore_eos: bool = False          # run to max_new_tokens whatever is sampled (for measurements)
 
     def __post_init__(self):
         if self.max_new_tokens < 1:
             raise ValueError("max_new_tokens must be at least 1")
         if self.temperature < 0:
             raise ValueError("temperature must not be negative")
+        self.stop_token_ids = tuple(int(t) for t in self.stop_token_ids)
+
+    def stops_at(self, token: int) -> bool:
+        if self.ignore_eos:
+            return False
+        return (self.eos_id is not None and token == self.eos_id) or token in self.stop_token_ids
 
 
 @dataclass

@@ -118,6 +118,19 @@ def test_first_token_comes_from_the_last_portion_and_eos_is_emitted():
     assert events[0].request_id == rid
 
 
+def test_stop_tokens_and_ignore_eos():
+    d, _ = driver(max_num_seqs=2, max_model_len=64, block_size=4)
+    prompt = [3, 1, 4, 1, 5]
+    free = expected(prompt, 10)
+    stop = free[4]
+    first = free.index(stop)
+    outs = generate(d, [prompt, prompt, prompt],
+                    [SamplingParams(max_new_tokens=10, stop_token_ids=(stop, 999)),
+                     SamplingParams(max_new_tokens=10, eos_id=stop, ignore_eos=True),
+                     SamplingParams(max_new_tokens=10, eos_id=free[7], stop_token_ids=[stop])])
+    assert outs == [free[:first + 1], free, free[:first + 1]]
+
+
 def test_slots_limit_live_requests_first_come_first_served():
     d, r = driver(max_num_seqs=2, max_model_len=32, block_size=4)
     ids = [add_request(d, [i + 1] * 3, SamplingParams(max_new_tokens=3)) for i in range(5)]
