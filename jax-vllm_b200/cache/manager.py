@@ -19,6 +19,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Optional
 
+import numpy as np
 import torch
 
 from ..parts.base import FixedStateNeed, PagedKVNeed, PagedLayerCache, StateLayerCache
@@ -38,12 +39,60 @@ class CacheGroup:
         return 2 * len(self.layers) * page_size * self.need.num_kv_heads * self.need.head_dim * itemsize
 
 
+class PageTable:
+    """Page ids of one request in one group by logical page index (-1: given back): a list of ints
+    kept as a growing int32 array, so that a batch copies a row of a block table without
+    converting it number by number (a request of 32k tokens has 2k pages, in every step)."""
+
+    __slots__ = ("_a", "_n")
+
+    def __init__(self):
+        self._a = np.empty(16, dtype=np.int32)
+        self._n = 0
+
+    def append(self, page: int) -> None:
+        if self._n == self._a.size:
+            grown = np.empty(2 * self._a.size, dtype=np.int32)
+            grown[:self._n] = self._a[:self._n]
+            self._a = grown
+        self._a[self._n] = page
+        self._n += 1
+
+    def array(self, n=None) -> np.ndarray:
+        """The first `n` entries (all by default) as a view of the array; not to be kept over an append."""
+        return self._a[:self._n if n is None else n]
+
+    def __len__(self):
+        return self._n
+
+    def __getitem__(self, i):
+        if isinstance(i, slice):
+            return self._a[:self._n][i].tolist()
+        if not -self._n <= i < self._n:
+            raise IndexError(i)
+        return int(self._a[i % self._n])
+
+    def __setitem__(self, i, page):
+        if not 0 <= i < self._n:
+            raise IndexError(i)
+        self._a[i] = page
+
+    def __iter__(self):
+        return iter(self._a[:self._n].tolist())
+
+    def __eq__(self, other):
+        return list(self) == list(other)
+
+    def __repr__(self):
+        return f"PageTable({list(self)})"
+
+
 @dataclass
 class RequestCache:
     """What one live request holds."""
     request_id: object
     slot: int
-    tables: list                          # per group: page id by logical page index (-1: given back)
+    tables: list                          # per group: a PageTable
     num_tokens: int = 0                   # tokens whose keys and values are in the cache
     hashes: list = field(default_factory=list)   # hash chain of the full pages so far
     freed_upto: list = field(default_factory=list)  # per group: logical pages below this were given back
@@ -105,7 +154,7 @@ class CacheManager:
         known prefix of `prompt`; `num_tokens` tells how many tokens those pages cover."""
         if request_id in self.live:
             raise KeyError(f"request {request_id!r} is already live")
-        rc = RequestCache(request_id, self.slots.take(), [[] for _ in self.groups],
+        rc = RequestCache(request_id, self.slots.take(), [PageTable() for _ in self.groups],
                           freed_upto=[0 for _ in self.groups])
         self.live[request_id] = rc
         if self.prefix_cache and prompt is not None and self.groups:

@@ -112,7 +112,7 @@ class BatchBuilder:
                                        f"{s + q} tokens need {need}")
                 if need > w:
                     raise RuntimeError(f"block table of width {w} is too narrow for {need} pages")
-                row[:need] = t[:need]
+                row[:need] = t.array(need)
                 row[need:] = -1
         for cls, lst in tiles.items():
             if lst:

@@ -188,3 +188,20 @@ def test_random_orders_lose_no_page(seed, needs, prefix):
         m.release(rid)
     m.check()
     assert all(g.pool.num_free == 24 for g in m.groups) and m.slots.num_free == 4
+
+
+def test_page_table_behaves_like_a_list():
+    from jax_vllm_b200.cache.manager import PageTable
+    t, ref = PageTable(), []
+    for i in range(100):                     # grows past its first allocation
+        t.append(3 * i + 1)
+        ref.append(3 * i + 1)
+    assert len(t) == 100 and list(t) == ref and t == ref and t[:7] == ref[:7] and t[-1] == ref[-1]
+    t[5] = -1
+    ref[5] = -1
+    assert t[5] == -1 and isinstance(t[5], int) and t.array(8).tolist() == ref[:8]
+    assert t.array().dtype.name == "int32" and sum(p >= 0 for p in t) == 99
+    with pytest.raises(IndexError):
+        t[100]
+    with pytest.raises(IndexError):
+        t[100] = 0
