@@ -3,6 +3,7 @@ random bfloat16 weights: the reference's headline metric (decoded tokens per sec
 dense Qwen3 configuration.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L]
+    python bench.py --workload mixed14b|long32b      # a serving workload of a larger shape (its own JSON line)
 
 Prints ONE JSON line.  `value` is decoded tokens per second at the given batch, each request
 holding 2,048 tokens of context, timed on the device with CUDA events over K decode steps
@@ -365,6 +366,77 @@ def micro(spec: str, reps: int, eager: bool = False) -> int:
     return 0
 
 
+WORKLOADS = {
+    # the larger dense Qwen3 shapes as serving workloads: all requests arrive at once, the scheduler cuts their
+    # prompts into portions beside the decode tokens of the others
+    "mixed14b": dict(config=dict(hidden_size=5120, intermediate_size=17408, num_hidden_layers=40, num_attention_heads=40),
+                     seed=6, requests=32, prompt=(128, 4096), prompt_seed=7, shared_prefix=1024, new_tokens=256,
+                     tokens_per_step=512),
+    "long32b": dict(config=dict(hidden_size=5120, intermediate_size=25600, num_hidden_layers=64, num_attention_heads=64),
+                    seed=8, requests=16, prompt=(8192, 8192), prompt_seed=9, shared_prefix=0, new_tokens=512,
+                    tokens_per_step=2048),
+}
+
+
+def workload(name: str, layers, weight_copy: bool) -> int:
+    """Runs one of WORKLOADS through the entry point and prints one JSON line: wall-clock seconds, prompt and
+    generated tokens per second, time to the first token, and the steps by kind (with a portion of a prompt
+    in them, or decoding alone) with their time and the tokens they ran."""
+    import random
+    import torch
+    from jax_vllm_b200 import SamplingParams, add_request, has_work, make_driver, prewarm, random_model, registry, step
+    w = WORKLOADS[name]
+    cfg_dict = dict(QWEN3_8B, **w["config"])
+    if layers:
+        cfg_dict["num_hidden_layers"] = layers
+    model = random_model(registry.config_from_dict(cfg_dict), seed=w["seed"], dtype="bf16", device="cuda:0",
+                         pack_decode_weights=weight_copy)
+    rng = random.Random(w["prompt_seed"])
+    vocab = cfg_dict["vocab_size"]
+    shared = [rng.randrange(vocab) for _ in range(w["shared_prefix"])]
+    prompts = []
+    for i in range(w["requests"]):
+        n = rng.randint(*w["prompt"])
+        own = [rng.randrange(vocab) for _ in range(n)]
+        prompts.append((shared + own[len(shared):]) if shared and i % 2 == 0 and n > len(shared) else own)
+    longest = max(len(p) for p in prompts)
+    max_len = -(-(longest + w["new_tokens"]) // PAGE) * PAGE
+    driver = make_driver(model, max_num_seqs=w["requests"], max_model_len=max_len, max_prefill_len=longest,
+                         block_size=PAGE, max_tokens_per_step=w["tokens_per_step"])
+    warm = prewarm(driver)
+    torch.cuda.synchronize()
+    st = driver.stats
+    kinds = {"with_prompt": [0, 0.0, 0], "decode_only": [0, 0.0, 0]}          # steps, seconds, tokens run
+    with ClockSampler() as clocks:
+        t0 = time.perf_counter()
+        ids = [add_request(driver, p, SamplingParams(max_new_tokens=w["new_tokens"])) for p in prompts]
+        reqs = [driver.requests[i] for i in ids]
+        while has_work(driver):
+            t1 = time.perf_counter()
+            before = (st.prefill_tokens, st.decode_tokens)
+            step(driver)
+            rec = kinds["with_prompt" if st.prefill_tokens > before[0] else "decode_only"]
+            rec[0] += 1
+            rec[1] += time.perf_counter() - t1
+            rec[2] += st.prefill_tokens + st.decode_tokens - sum(before)
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+    n_prompt, n_new = sum(len(p) for p in prompts), sum(len(r.output_ids) for r in reqs)
+    ttft = sorted(r.first_token_time - r.arrival for r in reqs)
+    out = {"workload": name, "layers": cfg_dict["num_hidden_layers"], "requests": len(prompts), "prompt_tokens": n_prompt,
+           "new_tokens": n_new, "seconds": round(dt, 3), "tokens_per_s": round((n_prompt + n_new) / dt, 1),
+           "new_tokens_per_s": round(n_new / dt, 1),
+           "ttft_s": {"median": round(ttft[len(ttft) // 2], 3), "max": round(ttft[-1], 3)}, "steps": st.steps}
+    for kind, (n, sec, toks) in kinds.items():
+        out["steps_" + kind] = {"steps": n, "ms_per_step": round(1e3 * sec / max(1, n), 2),
+                                "tokens_per_s": round(toks / max(1e-9, sec), 1)}
+    out.update({"preemptions": st.preemptions, "prefix_hit_tokens": st.cache_hit_tokens, "prewarm_s": round(warm, 1),
+                "gb_allocated": round(torch.cuda.max_memory_allocated() / 1e9, 1), "decode_weight_copy": weight_copy,
+                "clocks": clocks.summary})
+    print(json.dumps(out))
+    return 0
+
+
 def reference_arm():
     why = ("the reference (jllm) needs jax, jaxlib and equinox and the hatchling build backend; none is installed "
            "and none is in the offline wheelhouse, so it can neither be installed nor run here")
@@ -378,12 +450,15 @@ def main():
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--layers", type=int, default=QWEN3_8B["num_hidden_layers"],
+    ap.add_argument("--layers", type=int, default=None,
                     help="fewer layers than the configuration has (same layer sizes), for a quick run")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64, and the prefill")
     ap.add_argument("--only-prefill", action="store_true", help="time the 2,048-token prefill alone (for profiling)")
     ap.add_argument("--micro", default=None, help="run one kernel alone, e.g. linear:24576x4096:8 (see micro())")
+    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS),
+                    help="a serving workload of a larger shape through the entry point (see WORKLOADS); --layers cuts it")
+    ap.add_argument("--no-decode-weight-copy", action="store_true", help="with --workload: no second copy of the matrices")
     ap.add_argument("--micro-eager", action="store_true",
                     help="with --micro: plain launches instead of replays of a CUDA graph (for a profiler)")
     args = ap.parse_args()
@@ -394,6 +469,9 @@ def main():
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
+    if args.workload:
+        return workload(args.workload, args.layers, not args.no_decode_weight_copy)
+    args.layers = args.layers or QWEN3_8B["num_hidden_layers"]
     warmup = max(3, args.warmup)
 
     import torch

@@ -4,16 +4,20 @@
 //
 // A block handles 128 rows = (token, query head) pairs of ONE kv head (row r -> token r / HPT, head
 // r % HPT, HPT = query heads per kv head, a power of two up to 16), against 128-key tiles:
-//   warp 0   producer: reads the block table, issues the TMA loads of the query tile (once) and of the key
-//            and value tiles (one 4-D box per page and half of the head: [page slots, 64] elements);
+//   warp 0   key producer: reads the block table, issues the TMA loads of the query tile (once) and of the key
+//            tiles (one 4-D box per page and half of the head: [page slots, 64] elements);
+//   warp 10  value producer: the same for the value tiles (a stage of values is free much later than a stage
+//            of keys, and one warp that waits for both holds the keys back);
 //   warp 1   one thread issues S = Q K^T (8 x tcgen05.mma 128x128x16 over the head) into one of two score
-//            buffers in TMEM, and O += P V (8 x mma over the keys; V is the MN-major operand), after the
-//            softmax warps have written P (bfloat16) to shared memory;
-//   warps 2..5  softmax, one row per thread: read the scores from TMEM, mask, running (max, sum) in 32-bit,
+//            buffers in TMEM, and O += P V (8 x mma over the keys; P is read from TMEM, V is the MN-major
+//            operand from shared memory), after the softmax warps have written P (bfloat16) to TMEM;
+//   warps 2..9  softmax, two threads per row: read the scores from TMEM, mask, running (max, sum) in 32-bit,
 //            exp2, write P; when a row's maximum has moved, rescale O in TMEM first.  At the end O / sum is
 //            written out.
-// The score buffer of tile j+1 is filled while the softmax of tile j runs.  Every mbarrier wait is bounded
-// by a clock deadline and reports to the status word instead of spinning.
+// The score buffer of tile j+1 is filled while the softmax of tile j runs.  Shared memory moves 128 bytes a
+// clock, which a 128x128x16 product with both operands there needs all by itself: P therefore never goes
+// through shared memory.  Every mbarrier wait is bounded by a clock deadline and reports to the status word
+// instead of spinning.
 //
 // Restrictions (the caller falls back to the mma.sync kernel otherwise): bfloat16, head size 128, no
 // window, HPT in {1, 2, 4, 8, 16}, page size a power of two from 8 to 128.
@@ -28,10 +32,11 @@ namespace {
 constexpr int D = 128, ROWS = 128, BN = 128;
 constexpr int TILE_BYTES = 128 * 128 * 2;       // a 128 x 128 bfloat16 tile: two halves of [128 rows][128 bytes]
 constexpr int HALF_BYTES = 128 * 128;            // one half: 128 rows of 128 bytes
-constexpr int KV_STAGES = 2;
-constexpr int THREADS = 320;                     // producer warp, mma warp, 8 softmax warps
+constexpr int KV_STAGES = 3;
+constexpr int THREADS = 352;                     // key producer warp, mma warp, 8 softmax warps, value producer warp
 constexpr int SOFTMAX_THREADS = 256;
-constexpr int TMEM_COLS = 512;                   // S0: [0,128)  S1: [128,256)  O: [256,384)
+constexpr int TMEM_COLS = 512;                   // S0: [0,128)  S1: [128,256)  O: [256,384)  P0: [384,448)  P1: [448,512)
+constexpr int TMEM_O = 256, TMEM_P = 384;        // a column of P holds two bfloat16: keys 2c and 2c+1
 constexpr long long WAIT_CYCLES = 2000000000LL;
 constexpr float LOG2E = 1.4426950408889634f;
 
@@ -96,6 +101,12 @@ __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t a_desc, uint64_t 
                "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
                ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
+// The same with the A operand in tensor memory (rows = lanes, two 16-bit elements of k per column).
+__device__ __forceinline__ void umma_a_tmem(uint32_t tmem_d, uint32_t tmem_a, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+               "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
+               ::"r"(tmem_d), "r"(tmem_a), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar)) : "memory");
 }
@@ -146,6 +157,41 @@ __device__ __forceinline__ float fast_exp2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
   return y;
 }
+__device__ __forceinline__ void tmem_st32_bits(uint32_t taddr, const uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n"
+      ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]),
+        "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]),
+        "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]),
+        "r"(v[30]), "r"(v[31])
+      : "memory");
+  asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;\n" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+// Two 32-bit floats in one 64-bit register pair, for the packed fma and add of sm_100.
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+  uint64_t d;
+  asm("mov.b64 %0, {%1, %2};\n" : "=l"(d) : "f"(lo), "f"(hi));
+  return d;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;\n" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;\n" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;\n" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
 #define TC_FENCE_BEFORE() asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory")
 #define TC_FENCE_AFTER() asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory")
 #define PROXY_FENCE() asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory")
@@ -174,8 +220,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tcgen05_kernel(const __grid_c
   unsigned char* q_s = base;                                   // [2 halves of d][128 rows][128 B]
   unsigned char* k_s = q_s + TILE_BYTES;                       // [stages][2 halves of d][128 keys][128 B]
   unsigned char* v_s = k_s + KV_STAGES * TILE_BYTES;           // [stages][2 halves of d][128 keys][128 B]
-  unsigned char* p_s = v_s + KV_STAGES * TILE_BYTES;           // [2 buffers][2 halves of keys][128 rows][128 B]
-  Shared* sh = reinterpret_cast<Shared*>(p_s + 2 * TILE_BYTES);
+  Shared* sh = reinterpret_cast<Shared*>(v_s + KV_STAGES * TILE_BYTES);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   // longest blocks first: the work list is in ascending order of the tile's first token
@@ -213,12 +258,13 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tcgen05_kernel(const __grid_c
   __syncthreads();
   TC_FENCE_AFTER();
   const uint32_t tmem = sh->tmem_base;
-  const uint32_t tmem_o = tmem + 256;
+  const uint32_t tmem_o = tmem + TMEM_O;
 
   if (tokens_here > 0) {
-    if (warp == 0) {
-      // ---------------------------------------------------------------- producer
-      if (lane == 0) {
+    if (warp == 0 || warp == 10) {
+      // --------------------------------------------------------------- producers
+      const int which = warp == 0 ? 0 : 1;                        // keys or values
+      if (which == 0 && lane == 0) {
         mbar_expect_tx(&sh->q_full, TILE_BYTES);
         tma_load_3d(q_s, &q_map, 0, kv_head * G, q_begin + q_off, &sh->q_full);
         tma_load_3d(q_s + HALF_BYTES, &q_map, 64, kv_head * G, q_begin + q_off, &sh->q_full);
@@ -234,40 +280,29 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tcgen05_kernel(const __grid_c
         }
         return page;
       };
-      // one tile (keys or values) into its stage, once the stage is free
-      auto load_tile = [&](int j, int which, int page) -> bool {
+      uint64_t* full_bars = which ? sh->v_full : sh->k_full;
+      uint64_t* empty_bars = which ? sh->v_empty : sh->k_empty;
+      unsigned char* tiles = which ? v_s : k_s;
+      const CUtensorMap* map = which ? &v_map : &k_map;
+      // the block-table entries of a tile are read while the tile before it is loaded
+      int pages = tile_pages(0);
+      bool ok = true;
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int pages_next = tile_pages(j + 1);
         const int s = j % KV_STAGES, ph = (j / KV_STAGES) & 1;
-        uint64_t* full = which ? &sh->v_full[s] : &sh->k_full[s];
-        uint64_t* empty = which ? &sh->v_empty[s] : &sh->k_empty[s];
-        unsigned char* dst = (which ? v_s : k_s) + s * TILE_BYTES;
-        const CUtensorMap* map = which ? &v_map : &k_map;
-        const int n_pages = __popc(__ballot_sync(0xffffffffu, page >= 0));
-        bool ok = true;
+        unsigned char* dst = tiles + s * TILE_BYTES;
+        const int n_pages = __popc(__ballot_sync(0xffffffffu, pages >= 0));
         if (lane == 0) {
-          ok = mbar_wait(empty, ph ^ 1);
-          if (ok) mbar_expect_tx(full, n_pages * P * 128 * 2);
+          ok = mbar_wait(&empty_bars[s], ph ^ 1);
+          if (ok) mbar_expect_tx(&full_bars[s], n_pages * P * 128 * 2);
         }
         ok = __shfl_sync(0xffffffffu, ok, 0);      // also orders the announcement before the copies
-        // lane i issues the two boxes of page i: the copies of a tile are started by one pair of instructions of
-        // the warp, not one after another by a single thread (which takes longer than the tile's mathematics)
-        if (ok && page >= 0) {
-          tma_load_4d(dst + lane * P * 128, map, 0, kv_head, 0, page, full);
-          tma_load_4d(dst + HALF_BYTES + lane * P * 128, map, 64, kv_head, 0, page, full);
+        // lane i issues the two boxes of page i
+        if (ok && pages >= 0) {
+          tma_load_4d(dst + lane * P * 128, map, 0, kv_head, 0, pages, &full_bars[s]);
+          tma_load_4d(dst + HALF_BYTES + lane * P * 128, map, 64, kv_head, 0, pages, &full_bars[s]);
         }
-        return ok;
-      };
-      // keys run one tile ahead of values (the scores of tile j+1 are wanted while tile j is in its softmax),
-      // and the block-table entries of a tile are read while the tile before it is loaded
-      int pages_k = tile_pages(0);
-      bool ok = load_tile(0, 0, pages_k);
-      int pages_v = pages_k;
-      pages_k = tile_pages(1);
-      for (int j = 0; j < n_tiles && ok; ++j) {
-        const int pages_next = tile_pages(j + 2);
-        if (j + 1 < n_tiles) ok = load_tile(j + 1, 0, pages_k);
-        if (ok) ok = load_tile(j, 1, pages_v);
-        pages_v = pages_k;
-        pages_k = pages_next;
+        pages = pages_next;
       }
       if (!ok && lane == 0) atomicOr(p.status, JV_STATUS_WAIT_EXPIRED);
     } else if (warp == 1) {
@@ -275,17 +310,12 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tcgen05_kernel(const __grid_c
       if (lane == 0) {
         bool ok = mbar_wait(&sh->q_full, 0);
         const uint64_t q_desc0 = desc_k_major(smem_u32(q_s)), q_desc1 = desc_k_major(smem_u32(q_s + HALF_BYTES));
-        uint64_t k_desc[KV_STAGES][2], v_desc[KV_STAGES], p_desc[2][2];
+        uint64_t k_desc[KV_STAGES][2], v_desc[KV_STAGES];
 #pragma unroll
         for (int st = 0; st < KV_STAGES; ++st) {
           k_desc[st][0] = desc_k_major(smem_u32(k_s + st * TILE_BYTES));
           k_desc[st][1] = desc_k_major(smem_u32(k_s + st * TILE_BYTES + HALF_BYTES));
           v_desc[st] = desc_mn_major(smem_u32(v_s + st * TILE_BYTES));
-        }
-#pragma unroll
-        for (int b = 0; b < 2; ++b) {
-          p_desc[b][0] = desc_k_major(smem_u32(p_s + b * TILE_BYTES));
-          p_desc[b][1] = desc_k_major(smem_u32(p_s + b * TILE_BYTES + HALF_BYTES));
         }
         auto issue_qk = [&](int j) -> bool {                   // S[j % 2] = Q K_j^T
           const int s = j % KV_STAGES;
@@ -308,10 +338,11 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tcgen05_kernel(const __grid_c
           const int s = j % KV_STAGES;
           if (!mbar_wait(&sh->p_full[j & 1], (j >> 1) & 1) || !mbar_wait(&sh->v_full[s], (j / KV_STAGES) & 1)) { ok = false; break; }
           TC_FENCE_AFTER();
-          // O += P V_j : 8 steps of 16 keys; P K-major (keys along the 128-byte rows), V MN-major
+          // O += P V_j : 8 steps of 16 keys; P from tensor memory (8 columns a step), V MN-major
+          const uint32_t tmem_p = tmem + TMEM_P + (j & 1) * 64;
 #pragma unroll
-          for (int kk = 0; kk < 8; ++kk)   // 16 keys further: 32 bytes along P's rows, 16 rows (2048 bytes) down V
-            umma(tmem_o, p_desc[j & 1][kk >> 2] + 2 * (kk & 3), v_desc[s] + kk * (16 * 128 / 16), IDESC_PV, (j | kk) != 0);
+          for (int kk = 0; kk < 8; ++kk)   // 16 keys further: 8 columns of P, 16 rows (2048 bytes) down V
+            umma_a_tmem(tmem_o, tmem_p + kk * 8, v_desc[s] + kk * (16 * 128 / 16), IDESC_PV, (j | kk) != 0);
           umma_commit(&sh->v_empty[s]);
           umma_commit(&sh->o_done[j & 1]);
         }
@@ -349,17 +380,22 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tcgen05_kernel(const __grid_c
           tmem_ld32_issue(s_addr, sr[0]);
           tmem_ld32_issue(s_addr + 32, sr[1]);
           tmem_ld_wait();
+          // masking is a loop of its own behind a branch that the whole block takes or not: only the last
+          // tile of a block has keys to hide
+          if (need_mask) {
+            const int last = min(pos, j_hi - 1) - key0;          // the last of this thread's 64 keys that counts
+#pragma unroll
+            for (int c = 0; c < 2; ++c)
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (c * 32 + i > last) sr[c][i] = __float_as_uint(-INFINITY);
+          }
           float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
           for (int c = 0; c < 2; ++c)
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              if (need_mask) {
-                const int key = key0 + c * 32 + i;
-                if (!(key <= pos && key < j_hi)) sr[c][i] = __float_as_uint(-INFINITY);
-              }
-              mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(sr[c][i]));
-            }
+            for (int i = 0; i < 32; i += 2)
+              mx[(i >> 1) & 3] = max3(mx[(i >> 1) & 3], __uint_as_float(sr[c][i]), __uint_as_float(sr[c][i + 1]));
           my_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
         }
         // ---- the reference moves only if some score of the tile has outgrown it (always in a row's first tile
@@ -393,29 +429,32 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tcgen05_kernel(const __grid_c
             }
           }
         }
-        // ---- this tile's P buffer was read by the product of tile j-2
+        // ---- this tile's P buffer (in tensor memory) was read by the product of tile j-2
         if (ok && j >= 2) ok = __all_sync(0xffffffffu, mbar_wait(&sh->o_done[j & 1], ((j - 2) >> 1) & 1));
         if (!ok) continue;
-        // ---- probabilities, as bfloat16 into the swizzled K-major tile: this thread's 64 keys are one 128-byte row
-        float sum[4] = {0.f, 0.f, 0.f, 0.f};
-        unsigned char* row_base = p_s + (j & 1) * TILE_BYTES + half * HALF_BYTES + r * 128;
+        // ---- probabilities: pairs of scores in packed 32-bit arithmetic, as bfloat16 pairs into this thread's 32
+        // columns of the P buffer (column c of a row holds its keys 2c and 2c+1)
+        float sum[4];
+        {
+          const uint64_t scale2 = pack2(p.scale_log2, p.scale_log2), neg_m2 = pack2(-m_scaled, -m_scaled);
+          uint64_t sum2[2] = {pack2(0.f, 0.f), pack2(0.f, 0.f)};
+          uint32_t pw[32];
 #pragma unroll
-        for (int c = 0; c < 2; ++c)
+          for (int c = 0; c < 2; ++c)
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            uint4 pk;
-            __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&pk);
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const int i = q * 8 + e * 2;
-              const float p0 = fast_exp2(fmaf(__uint_as_float(sr[c][i]), p.scale_log2, -m_scaled));
-              const float p1 = fast_exp2(fmaf(__uint_as_float(sr[c][i + 1]), p.scale_log2, -m_scaled));
-              sum[e] += p0 + p1;
-              h2[e] = __floats2bfloat162_rn(p0, p1);
+            for (int i = 0; i < 32; i += 2) {
+              const uint64_t x2 = fma2(pack2(__uint_as_float(sr[c][i]), __uint_as_float(sr[c][i + 1])), scale2, neg_m2);
+              float x0, x1;
+              unpack2(x2, x0, x1);
+              const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+              sum2[(i >> 1) & 1] = add2(sum2[(i >> 1) & 1], pack2(p0, p1));
+              const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+              pw[c * 16 + (i >> 1)] = *reinterpret_cast<const uint32_t*>(&h);
             }
-            const int chunk = c * 4 + q;                         // 16-byte chunk within the 128-byte row
-            *reinterpret_cast<uint4*>(row_base + ((chunk ^ (r & 7)) << 4)) = pk;
-          }
+          unpack2(sum2[0], sum[0], sum[1]);
+          unpack2(sum2[1], sum[2], sum[3]);
+          tmem_st32_bits(tmem + lane_addr + TMEM_P + (j & 1) * 64 + half * 32, pw);
+        }
         l_run = l_run * alpha + ((sum[0] + sum[1]) + (sum[2] + sum[3]));
         // ---- in the last tile the value rows past the end become zero (they may hold anything)
         if (j == n_tiles - 1 && j_hi < j * BN + BN) {
@@ -430,8 +469,8 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tcgen05_kernel(const __grid_c
           }
         }
         if (!ok) continue;
-        PROXY_FENCE();                                           // P (and the zeroed rows) visible to the tensor core
-        TC_FENCE_BEFORE();
+        if (j == n_tiles - 1) PROXY_FENCE();                     // the zeroed rows visible to the tensor core
+        TC_FENCE_BEFORE();                                       // P is in tensor memory before the arrival
         mbar_arrive(&sh->p_full[j & 1]);
       }
       // ---- output: O / sum, each thread its 64 columns; the row's sum is the two threads' together
@@ -538,7 +577,7 @@ JV_EXPORT int jv_attn_tcgen05(const void* q, int q_stride, int n_tokens, void* o
   p.cu_seqlens = cu_seqlens; p.start_pos = start_pos; p.work = work; p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads;
   p.page_size = page_size; p.num_pages = num_pages; p.hpt = G; p.tokens_per_tile = ROWS / G;
   p.scale_log2 = scale * LOG2E; p.status = status;
-  constexpr size_t smem = TILE_BYTES * (3 + 2 * KV_STAGES) + sizeof(Shared) + 1024;
+  constexpr size_t smem = TILE_BYTES * (1 + 2 * KV_STAGES) + sizeof(Shared) + 1024;
   static bool ready = false;
   if (!ready) {
     if (cudaFuncSetAttribute(attn_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
