@@ -81,6 +81,11 @@ __device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, i
                ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(z), "r"(w), "r"(smem_u32(bar)) : "memory");
 }
 
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, const void* src, int x, int y, int z) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%1, %2, %3}], [%4];\n"
+               ::"l"(map), "r"(x), "r"(y), "r"(z), "r"(smem_u32(src)) : "memory");
+}
+
 // Descriptor of a K-major operand tile (rows of 128 bytes along k, 8-row groups 1024 bytes apart, 128-byte swizzle).
 __device__ __forceinline__ uint64_t desc_k_major(uint32_t addr) {
   return (uint64_t)((addr & 0x3FFFF) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
@@ -196,13 +201,15 @@ __device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
 #define TC_FENCE_AFTER() asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory")
 #define PROXY_FENCE() asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory")
 
-// Barrier of the 256 softmax threads that also tells every one of them whether any had `flag` set.
-__device__ __forceinline__ bool softmax_barrier_or(bool flag) {
+// Barrier of the two softmax warps that share 32 rows (64 threads; barriers 1..4, one for each pair) that also
+// tells every one of them whether any had `flag` set.
+__device__ __forceinline__ bool pair_barrier_or(int quad, bool flag) {
   uint32_t any;
-  asm volatile("{\n.reg .pred p, q;\nsetp.ne.b32 q, %1, 0;\nbar.red.or.pred p, 1, 256, q;\nselp.u32 %0, 1, 0, p;\n}\n"
-               : "=r"(any) : "r"((uint32_t)flag) : "memory");
+  asm volatile("{\n.reg .pred p, q;\nsetp.ne.b32 q, %2, 0;\nbar.red.or.pred p, %1, 64, q;\nselp.u32 %0, 1, 0, p;\n}\n"
+               : "=r"(any) : "r"(quad + 1), "r"((uint32_t)flag) : "memory");
   return any != 0;
 }
+__device__ __forceinline__ void pair_barrier(int quad) { asm volatile("bar.sync %0, 64;\n" ::"r"(quad + 1) : "memory"); }
 
 struct Shared {
   uint64_t q_full, k_full[KV_STAGES], k_empty[KV_STAGES], v_full[KV_STAGES], v_empty[KV_STAGES];
@@ -214,6 +221,7 @@ struct Shared {
 __global__ void __launch_bounds__(THREADS, 1) attn_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map,
                                                                   const __grid_constant__ CUtensorMap k_map,
                                                                   const __grid_constant__ CUtensorMap v_map,
+                                                                  const __grid_constant__ CUtensorMap out_map,
                                                                   const Params p) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -223,10 +231,12 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tcgen05_kernel(const __grid_c
   Shared* sh = reinterpret_cast<Shared*>(v_s + KV_STAGES * TILE_BYTES);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  // longest blocks first: the work list is in ascending order of the tile's first token
-  const int item = gridDim.x - 1 - blockIdx.x;
+  // longest blocks first, over all heads: the work list is in ascending order of the tile's first token, and
+  // blocks start in the order of their linear index
+  const int linear = blockIdx.x + gridDim.x * blockIdx.y;
+  const int item = gridDim.x - 1 - linear / p.n_kv_heads;
+  const int kv_head = linear % p.n_kv_heads;
   const int entry = p.work[2 * item], q_off = p.work[2 * item + 1];
-  const int kv_head = blockIdx.y;
   const int G = p.n_q_heads / p.n_kv_heads, HPT = p.hpt;
   const int q_begin = p.cu_seqlens[entry];
   const int q_len = p.cu_seqlens[entry + 1] - q_begin;
@@ -247,17 +257,20 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tcgen05_kernel(const __grid_c
     mbar_init(&sh->o_done[0], 1); mbar_init(&sh->o_done[1], 1);
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
-  // value tiles start as zeros: a probability of exactly zero must never meet a NaN left in shared memory
-  for (int i = threadIdx.x; i < KV_STAGES * TILE_BYTES / 16; i += THREADS) reinterpret_cast<uint4*>(v_s)[i] = make_uint4(0, 0, 0, 0);
-  PROXY_FENCE();
-  if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&sh->tmem_base)), "r"(TMEM_COLS) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
-  }
-  TC_FENCE_BEFORE();
   __syncthreads();
-  TC_FENCE_AFTER();
-  const uint32_t tmem = sh->tmem_base;
+  // The producers start at once; the others wait until the second warp has its tensor memory.  Shared memory is
+  // not cleared: key rows that were never loaded give scores that are masked before they are looked at, and the
+  // value rows past the end of the last tile are set to zero there.
+  if (warp >= 1 && warp <= 9) {
+    if (warp == 1) {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&sh->tmem_base)), "r"(TMEM_COLS) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    TC_FENCE_BEFORE();
+    asm volatile("bar.sync 6, 288;\n" ::: "memory");
+    TC_FENCE_AFTER();
+  }
+  const uint32_t tmem = (warp >= 1 && warp <= 9) ? sh->tmem_base : 0u;
   const uint32_t tmem_o = tmem + TMEM_O;
 
   if (tokens_here > 0) {
@@ -403,11 +416,11 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tcgen05_kernel(const __grid_c
         // then do the two threads of a row exchange their maxima
         const bool outgrown = ok && my_max != -INFINITY && (m_ref == -INFINITY || (my_max - m_ref) * p.scale_log2 > LAZY);
         float alpha = 1.f;
-        if (softmax_barrier_or(outgrown)) {
+        if (pair_barrier_or(quad, outgrown)) {
           sh->xch[half][r] = my_max;
-          asm volatile("bar.sync 1, 256;\n" ::: "memory");
+          pair_barrier(quad);
           const float m_tile = fmaxf(sh->xch[0][r], sh->xch[1][r]);
-          asm volatile("bar.sync 1, 256;\n" ::: "memory");          // both have read before a later tile writes
+          pair_barrier(quad);                                        // both have read before a later tile writes
           if (ok && m_tile != -INFINITY && (m_ref == -INFINITY || (m_tile - m_ref) * p.scale_log2 > LAZY)) {
             alpha = (m_ref == -INFINITY) ? 0.f : fast_exp2((m_ref - m_tile) * p.scale_log2);
             m_ref = m_tile;
@@ -429,8 +442,8 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tcgen05_kernel(const __grid_c
             }
           }
         }
-        // ---- this tile's P buffer (in tensor memory) was read by the product of tile j-2
-        if (ok && j >= 2) ok = __all_sync(0xffffffffu, mbar_wait(&sh->o_done[j & 1], ((j - 2) >> 1) & 1));
+        // this tile's P buffer (in tensor memory) was read by the product of tile j-2, which was issued before
+        // the scores of tile j: their arrival has told that it is complete
         if (!ok) continue;
         // ---- probabilities: pairs of scores in packed 32-bit arithmetic, as bfloat16 pairs into this thread's 32
         // columns of the P buffer (column c of a row holds its keys 2c and 2c+1)
@@ -475,11 +488,42 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tcgen05_kernel(const __grid_c
       }
       // ---- output: O / sum, each thread its 64 columns; the row's sum is the two threads' together
       sh->xch[half][r] = l_run;
-      asm volatile("bar.sync 1, 256;\n" ::: "memory");
+      pair_barrier(quad);
       const float l_row = sh->xch[0][r] + sh->xch[1][r];
-      if (ok && mbar_wait(&sh->o_done[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1)) {
+      const bool got = ok && mbar_wait(&sh->o_done[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1);
+      const float inv = row_ok ? 1.f / l_row : 0.f;
+      if (tokens_here == p.tokens_per_tile) {
+        // A whole tile leaves through shared memory (where the queries were: every product has completed) and one
+        // TMA store per half of the head; threads that write their 128 bytes to rows 8 KB apart in memory take
+        // five times as long.
+        if (got) {
+          TC_FENCE_AFTER();
+          unsigned char* row_base = q_s + half * HALF_BYTES + r * 128;
+#pragma unroll 1
+          for (int c = 0; c < 2; ++c) {
+            float v[32];
+            tmem_ld32(tmem_o + lane_addr + half * 64 + c * 32, v);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint4 pk;
+              __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+              for (int e = 0; e < 4; ++e) h2[e] = __floats2bfloat162_rn(v[q * 8 + 2 * e] * inv, v[q * 8 + 2 * e + 1] * inv);
+              const int chunk = c * 4 + q;                       // 16-byte chunk within the 128-byte row
+              *reinterpret_cast<uint4*>(row_base + ((chunk ^ (r & 7)) << 4)) = pk;
+            }
+          }
+        }
+        PROXY_FENCE();
+        asm volatile("bar.sync 5, 256;\n" ::: "memory");
+        if (threadIdx.x == 64) {
+          tma_store_3d(&out_map, q_s, 0, kv_head * G, q_begin + q_off);
+          tma_store_3d(&out_map, q_s + HALF_BYTES, 64, kv_head * G, q_begin + q_off);
+          asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
+          asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory");
+        }
+      } else if (got) {
         TC_FENCE_AFTER();
-        const float inv = row_ok ? 1.f / l_row : 0.f;
         __nv_bfloat16* dst = p.out + (size_t)(q_begin + q_off + t) * p.out_stride + (size_t)(kv_head * G + hh) * D + half * 64;
 #pragma unroll 1
         for (int c = 0; c < 2; ++c) {
@@ -496,9 +540,8 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tcgen05_kernel(const __grid_c
             }
           }
         }
-      } else if (lane == 0) {
-        atomicOr(p.status, JV_STATUS_WAIT_EXPIRED);
       }
+      if (!got && lane == 0) atomicOr(p.status, JV_STATUS_WAIT_EXPIRED);
     }
   }
 
@@ -549,14 +592,14 @@ JV_EXPORT int jv_attn_tcgen05(const void* q, int q_stride, int n_tokens, void* o
   auto fn = encode_fn();
   if (fn == nullptr) return JV_ERR_UNSUPPORTED;
   const int G = n_q_heads / n_kv_heads;
-  CUtensorMap q_map, k_map, v_map;
-  {
-    // queries: (d, head, token); a box is 64 d x G heads x (128 / G) tokens = 128 rows, head fastest
+  CUtensorMap q_map, k_map, v_map, out_map;
+  for (int which = 0; which < 2; ++which) {
+    // queries and output: (d, head, token); a box is 64 d x G heads x (128 / G) tokens = 128 rows, head fastest
     const cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)n_q_heads, (cuuint64_t)n_tokens};
-    const cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)q_stride * 2};
+    const cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)(which ? out_stride : q_stride) * 2};
     const cuuint32_t box[3] = {64, (cuuint32_t)G, (cuuint32_t)(ROWS / G)};
     const cuuint32_t es[3] = {1, 1, 1};
-    if (fn(&q_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(q), dims, strides, box, es,
+    if (fn(which ? &out_map : &q_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, which ? out : const_cast<void*>(q), dims, strides, box, es,
            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
       return JV_ERR_UNSUPPORTED;
@@ -584,6 +627,6 @@ JV_EXPORT int jv_attn_tcgen05(const void* q, int q_stride, int n_tokens, void* o
       return JV_ERR_UNSUPPORTED;
     ready = true;
   }
-  attn_tcgen05_kernel<<<dim3(n_work, n_kv_heads), THREADS, smem, stream>>>(q_map, k_map, v_map, p);
+  attn_tcgen05_kernel<<<dim3(n_work, n_kv_heads), THREADS, smem, stream>>>(q_map, k_map, v_map, out_map, p);
   return jv_check_launch();
 }
