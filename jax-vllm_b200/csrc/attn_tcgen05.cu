@@ -2,8 +2,9 @@
 // scores and output accumulate in tensor memory (TMEM), queries, keys and values come in by TMA in the
 // 128-byte-swizzle layout that tcgen05.mma reads.
 //
-// A block handles 128 rows = (token, query head) pairs of ONE kv head (row r -> token r / HPT, head
-// r % HPT, HPT = query heads per kv head, a power of two up to 16), against 128-key tiles:
+// A block handles up to 128 rows = (token, query head) pairs of ONE kv head (row r -> token r / HPT, head
+// r % HPT, HPT = query heads per kv head, any number up to 16: 128 / HPT tokens, the rows that are left over
+// when HPT does not divide 128 are computed and thrown away), against 128-key tiles:
 //   warp 0   key producer: reads the block table, issues the TMA loads of the query tile (once) and of the key
 //            tiles (one 4-D box per page and half of the head: [page slots, 64] elements);
 //   warp 10  value producer: the same for the value tiles (a stage of values is free much later than a stage
@@ -20,7 +21,7 @@
 // instead of spinning.
 //
 // Restrictions (the caller falls back to the mma.sync kernel otherwise): bfloat16, head size 128, no
-// window, HPT in {1, 2, 4, 8, 16}, page size a power of two from 8 to 128.
+// window, HPT up to 16, page size a power of two from 8 to 128.
 #include "common.cuh"
 
 #include <cuda.h>
@@ -278,7 +279,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tcgen05_kernel(const __grid_c
       // --------------------------------------------------------------- producers
       const int which = warp == 0 ? 0 : 1;                        // keys or values
       if (which == 0 && lane == 0) {
-        mbar_expect_tx(&sh->q_full, TILE_BYTES);
+        mbar_expect_tx(&sh->q_full, 2 * 128 * G * p.tokens_per_tile);      // two boxes of 64 d x G heads x tokens
         tma_load_3d(q_s, &q_map, 0, kv_head * G, q_begin + q_off, &sh->q_full);
         tma_load_3d(q_s + HALF_BYTES, &q_map, 64, kv_head * G, q_begin + q_off, &sh->q_full);
       }
@@ -570,7 +571,7 @@ PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
 JV_EXPORT int jv_attn_tcgen05_supports(int head_dim, int n_q_heads, int n_kv_heads, int page_size, int window) {
   if (head_dim != 128 || window > 0 || n_kv_heads < 1 || n_q_heads % n_kv_heads) return 0;
   const int G = n_q_heads / n_kv_heads;
-  if (!(G == 1 || G == 2 || G == 4 || G == 8 || G == 16)) return 0;
+  if (G > 16) return 0;
   return page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64 || page_size == 128;
 }
 

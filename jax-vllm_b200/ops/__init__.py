@@ -65,7 +65,13 @@ def _fn(lib: str, name: str, argtypes):
     return f
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream() -> int:
+    """The current stream's handle: asked for before every launch, so by the short way where torch has one."""
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
 
 
@@ -356,7 +362,7 @@ def attn_tcgen05_supports(dtype: torch.dtype, head_dim: int, n_q_heads: int, n_k
     """Whether the tcgen05 prompt-attention kernel takes the case (csrc/attn_tcgen05.cu)."""
     g = n_q_heads // max(n_kv_heads, 1)
     return (dtype == torch.bfloat16 and head_dim == 128 and not window and n_q_heads % n_kv_heads == 0
-            and g in (1, 2, 4, 8, 16) and page_size in (8, 16, 32, 64, 128))
+            and 1 <= g <= 16 and page_size in (8, 16, 32, 64, 128))
 
 
 def attn_tcgen05_tokens_per_tile(n_q_heads: int, n_kv_heads: int) -> int:

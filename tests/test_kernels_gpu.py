@@ -484,7 +484,8 @@ def test_mma_attention_finds_one_far_key_among_hundreds(ops, split, far):
 
 
 # ---- the tcgen05 kernel (bfloat16, head size 128)
-@pytest.mark.parametrize("hq,hkv,page", [(4, 1, 16), (32, 8, 16), (8, 8, 8), (2, 1, 128), (16, 1, 32), (16, 2, 64)])
+@pytest.mark.parametrize("hq,hkv,page", [(4, 1, 16), (32, 8, 16), (8, 8, 8), (2, 1, 128), (16, 1, 32), (16, 2, 64),
+                                         (40, 8, 16), (3, 1, 32), (12, 2, 16), (7, 1, 64), (13, 1, 16)])
 def test_tcgen05_attention_portions_with_context(ops, hq, hkv, page):
     got, want = run_attention(ops, torch.bfloat16, hq, hkv, 128, page, q_lens=[7, 300, 133, 2, 70], starts=[0, 50, 21, 64, 190],
                               tc5=True)
@@ -630,10 +631,12 @@ def test_tcgen05_support_rules(ops):
     from jax_vllm_b200.csrc import build
     lib = build.load("attn_tcgen05")
     for d, hq, hkv, page, window in [(128, 32, 8, 16, 0), (64, 32, 8, 16, 0), (128, 6, 1, 16, 0), (128, 32, 8, 4, 0),
-                                     (128, 32, 8, 16, 5), (128, 16, 1, 128, 0), (128, 20, 1, 16, 0)]:
+                                     (128, 32, 8, 16, 5), (128, 16, 1, 128, 0), (128, 20, 1, 16, 0), (128, 40, 8, 16, 0),
+                                     (128, 17, 1, 16, 0)]:
         assert bool(lib.jv_attn_tcgen05_supports(d, hq, hkv, page, window)) == \
             ops.attn_tcgen05_supports(torch.bfloat16, d, hq, hkv, page, window)
     assert lib.jv_attn_tcgen05_tokens_per_tile(32, 8) == ops.attn_tcgen05_tokens_per_tile(32, 8) == 32
+    assert lib.jv_attn_tcgen05_tokens_per_tile(40, 8) == ops.attn_tcgen05_tokens_per_tile(40, 8) == 25
 
 
 def test_mma_support_table_matches_the_library(ops):
