@@ -204,3 +204,24 @@ def test_other_head_sizes_in_steps_of_16(head_dim, heads, kv_heads, dtype, tmp_p
         rep.run_stream(json.dumps(s) for s in steps)
         rep.cache.check()
         compare(steps, out, 200, want, dtype)
+
+
+@pytest.mark.parametrize("heads,kv_heads", [(5, 1), (6, 2), (7, 1)])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_group_sizes_that_do_not_divide_the_tile(heads, kv_heads, dtype, tmp_path):
+    """Head size 128 with 5, 3 and 7 query heads per kv head: the 128-row tiles of the tcgen05 kernels hold 25, 42
+    and 18 tokens and leave rows over.  Whole, in portions, and the last tokens one by one."""
+    from tests.util import write_folder, make_weights
+    cfg = dict(architectures=["Qwen3ForCausalLM"], vocab_size=200, hidden_size=96, intermediate_size=128,
+               num_hidden_layers=2, num_attention_heads=heads, num_key_value_heads=kv_heads, head_dim=128,
+               rms_norm_eps=1e-6, rope_theta=1e4, max_position_embeddings=512, tie_word_embeddings=True)
+    folder = write_folder(tmp_path / "model", cfg, make_weights(cfg, seed=heads))
+    toks = random_tokens(230, 200, seed=heads + 1)
+    want = {"r": PlainModel(folder).logits(toks)}
+    from jax_vllm_b200.engine.replay import Replayer
+    for i, steps in enumerate((whole("r", toks), portions("r", toks, [97, 2, 51, 30, 26, 24]), prefix_then_single("r", toks, tail=12))):
+        out = tmp_path / f"out{i}"
+        rep = Replayer(folder, dtype, out, max_tokens=256, page_size=16)
+        rep.run_stream(json.dumps(s) for s in steps)
+        rep.cache.check()
+        compare(steps, out, 200, want, dtype)
