@@ -288,6 +288,10 @@ def micro(spec: str, reps: int, eager: bool = False) -> int:
         if "packed" in rest[2:]:              # the weight in the kernel's own order
             ws = [ops.PackedWeight(w) for w in ws]
             run = lambda i: ops.linear_skinny(x, ws[i % copies], torch.bfloat16, parts_ok)
+        elif "stream" in rest[2:]:            # the tcgen05 product for larger batches, whatever the rows
+            run = lambda i: ops.linear_stream(x, ws[i % copies], torch.bfloat16, parts_ok)
+        elif "library" in rest[2:]:
+            run = lambda i: torch.mm(x, ws[i % copies].t())
         else:
             run = lambda i: ops.linear(x, ws[i % copies], parts_ok=parts_ok)
         nbytes = n * k * 2

@@ -548,6 +548,58 @@ def linear_skinny(x: torch.Tensor, weight, out_dtype: torch.dtype, parts_ok: boo
     return y if parts is None else PartialSum(parts)
 
 
+STREAM_MAX_ROWS = 128
+# which product the dispatcher takes: up to 8 rows the mma.sync kernel (its second 8 rows cost it a fifth), up to
+# 64 rows the tcgen05 one, beyond that the library's (which shares x between two multiprocessors)
+SKINNY_BEST_ROWS = 8
+STREAM_BEST_ROWS = 64
+_stream_plans: dict = {}
+
+
+def linear_stream_splits(device, n: int, k: int) -> int:
+    """Into how many parts of k the product for 17 to 128 rows (csrc/linear_stream.cu) would best cut the
+    128-row strips of an [n, k] weight on this device (1: not at all)."""
+    key = (torch.device(device).index or 0, n, k)
+    plan = _stream_plans.get(key)
+    if plan is None:
+        f = _build.load("linear_stream").jv_linear_stream_plan
+        f.argtypes = [c_int, c_int]
+        f.restype = c_int
+        with torch.cuda.device(key[0]):
+            plan = _stream_plans[key] = int(f(n, k))
+    return plan
+
+
+def linear_stream(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype, parts_ok: bool = False):
+    """x [M <= 128, K] times weight [N, K] transposed on tcgen05 with the weight as the 128-row operand and the
+    batch as the narrow one (csrc/linear_stream.cu): bfloat16 operands, 32-bit accumulation; the result is
+    bfloat16 or float32, or with `parts_ok`, where the kernel cuts k for an even load, a PartialSum."""
+    _cuda(x, "x", torch.bfloat16, contiguous=False); _cuda(weight, "weight", torch.bfloat16, contiguous=False)
+    if x.dim() != 2 or weight.dim() != 2 or x.shape[1] != weight.shape[1] or x.stride(1) != 1 or weight.stride(1) != 1:
+        raise KernelError(f"linear shapes {tuple(x.shape)} x {tuple(weight.shape)}^T do not fit")
+    m, k = x.shape
+    n = weight.shape[0]
+    splits = linear_stream_splits(x.device, n, k) if parts_ok else 1
+    if splits > 1:
+        parts = torch.empty((splits, m, n), dtype=torch.float32, device=x.device)
+        y = None
+    else:
+        parts = None
+        y = torch.empty((m, n), dtype=out_dtype, device=x.device)
+    f = _fn("linear_stream", "jv_linear_stream", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
+                                                  c_int, c_void_p, c_int, c_void_p, c_void_p])
+    _check(f(x.data_ptr(), x.stride(0), weight.data_ptr(), weight.stride(0), _ptr(y), DTYPE_CODE[out_dtype],
+             n if y is None else y.stride(0), m, n, k, _ptr(parts), splits, status_word(x.device).data_ptr(), _stream()),
+           "linear_stream")
+    return y if parts is None else PartialSum(parts)
+
+
+def _stream_ok(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    return (x.dim() == 2 and 0 < x.shape[0] <= STREAM_MAX_ROWS and x.stride(1) == 1 and x.shape[1] % 8 == 0
+            and x.stride(0) % 8 == 0 and weight.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0
+            and x.dtype == torch.bfloat16)
+
+
 GEMM_EPILOGUES = {"bf16": 0, "f32": 1, "swiglu": 2}
 
 
@@ -573,6 +625,20 @@ def gemm_tcgen05(x: torch.Tensor, weight: torch.Tensor, epilogue: str = "bf16") 
     return y
 
 
+_sm_counts: dict = {}
+
+
+def _strips_fill_the_device(device, n: int) -> bool:
+    """Whether the 128-row strips of a weight of n rows, uncut, keep the multiprocessors busy (0.85 of them over
+    the rounds it takes): the tcgen05 product for larger batches takes a weight whole only then."""
+    idx = torch.device(device).index or 0
+    sms = _sm_counts.get(idx)
+    if sms is None:
+        sms = _sm_counts[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
+    strips = -(-n // 128)
+    return strips >= 0.85 * sms * -(-strips // sms)
+
+
 def _skinny_ok(x: torch.Tensor, weight: torch.Tensor) -> bool:
     return (x.shape[0] <= SKINNY_MAX_ROWS and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0 and weight.stride(0) % 8 == 0
             and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0 and x.stride(1) == 1)
@@ -586,15 +652,20 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None 
 
     float32 weights: the CUDA-core product of this package in true 32-bit (16-bit
     activations are read as they are and widened inside).  bfloat16 weights and
-    activations: up to SKINNY_MAX_ROWS rows (decoding) the weight-streaming kernel of this
-    package; more rows (prompts) cuBLAS through torch.mm; both accumulate in 32-bit and give
-    the result in `out_dtype` (bfloat16 by default, float32 for logits)."""
+    activations: up to SKINNY_BEST_ROWS rows (decoding) the weight-streaming kernel of this
+    package on mma.sync, up to STREAM_BEST_ROWS rows (larger batches of decoded tokens) the one on tcgen05;
+    more rows (prompts) cuBLAS through torch.mm; all accumulate in 32-bit and give the result in
+    `out_dtype` (bfloat16 by default, float32 for logits)."""
     out_dtype = out_dtype or x.dtype
     if weight.dtype == torch.float32 or x.dtype == torch.float32:
         return gemm_simt(x, weight, out_dtype)
     _cuda(x, "x", torch.bfloat16, contiguous=False); _cuda(weight, "weight", torch.bfloat16)
-    if _skinny_ok(x, weight):
+    stream = _stream_ok(x, weight) and out_dtype in (torch.bfloat16, torch.float32) and \
+        (parts_ok or _strips_fill_the_device(x.device, weight.shape[0]))
+    if _skinny_ok(x, weight) and (x.shape[0] <= SKINNY_BEST_ROWS or not stream):
         return linear_skinny(x, weight if packed is None else packed, out_dtype, parts_ok)
+    if stream and x.shape[0] <= STREAM_BEST_ROWS:
+        return linear_stream(x, weight, out_dtype, parts_ok)
     if out_dtype == torch.bfloat16:
         return torch.mm(x, weight.t())
     return torch.mm(x, weight.t(), out_dtype=out_dtype)

@@ -61,7 +61,7 @@ class Model(Part):
     def kernels(self):
         names = {"embed", "norm", "gemm_simt"}
         if self.ctx.dtype == torch.bfloat16:
-            names.add("linear_skinny")
+            names.update(("linear_skinny", "linear_stream"))
         for layer in self.layers:
             for part in layer.parts():
                 names.update(part.kernels)

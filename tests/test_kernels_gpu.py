@@ -125,6 +125,53 @@ def test_linear_skinny(ops, m, n, k, out_dtype):
     torch.testing.assert_close(y2.double(), wide[:, 8:8 + k].double() @ w.double().T, atol=1e-4, rtol=1e-4)
 
 
+@pytest.mark.parametrize("m", [1, 17, 33, 64, 100, 128])
+@pytest.mark.parametrize("n,k", [(70, 96), (4096, 4096), (1000, 1536), (24, 8), (151, 4104), (24576, 512), (4096, 12288), (50, 2056)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_linear_stream(ops, m, n, k, out_dtype):
+    """The tcgen05 product for larger batches of decoded tokens: the weight is the 128-row operand."""
+    g = torch.Generator().manual_seed(m * 1000 + n)
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(n, k, generator=g) / k ** 0.5).to(torch.bfloat16).to(DEV)
+    y = ops.linear_stream(x, w, out_dtype)
+    want = (x.double() @ w.double().T)
+    if out_dtype == torch.float32:
+        torch.testing.assert_close(y.double(), want, atol=1e-4, rtol=1e-4)
+    else:
+        torch.testing.assert_close(y.double(), want, atol=2e-2, rtol=2e-2)
+    # a row's result does not depend on the rest of the batch
+    for rows in ([m // 2], list(range(min(m, 21)))):
+        ys = ops.linear_stream(x[rows].contiguous(), w, out_dtype)
+        assert torch.equal(ys, y[rows])
+    # rows of a wider tensor
+    wide = torch.randn(m, k + 16, generator=g).to(torch.bfloat16).to(DEV)
+    y2 = ops.linear_stream(wide[:, 8:8 + k], w, torch.float32)
+    torch.testing.assert_close(y2.double(), wide[:, 8:8 + k].double() @ w.double().T, atol=1e-4, rtol=1e-4)
+    ops.check_status()
+
+
+@pytest.mark.parametrize("m,n,k", [(17, 4096, 4096), (64, 6144, 4096), (40, 4096, 12288), (128, 24576, 4096), (33, 1000, 1536)])
+def test_linear_stream_parts_of_a_sum(ops, m, n, k):
+    g = torch.Generator().manual_seed(m * 1000 + n)
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(n, k, generator=g) / k ** 0.5).to(torch.bfloat16).to(DEV)
+    splits = ops.linear_stream_splits(DEV, n, k)
+    y = ops.linear_stream(x, w, torch.bfloat16, parts_ok=True)
+    want = x.double() @ w.double().T
+    if splits > 1:
+        assert isinstance(y, ops.PartialSum) and y.parts.shape == (splits, m, n) and tuple(y.shape) == (m, n)
+        torch.testing.assert_close(y.parts.double().sum(0), want, atol=1e-4, rtol=1e-4)
+        ys = ops.linear_stream(x[m // 2:m // 2 + 1].contiguous(), w, torch.bfloat16, parts_ok=True)
+        assert torch.equal(ys.parts[:, 0], y.parts[:, m // 2])
+    else:
+        torch.testing.assert_close(y.double(), want, atol=2e-2, rtol=2e-2)
+    assert ops.linear_stream_splits(DEV, 4096, 4096) > 1            # 32 strips for 148 multiprocessors: k is cut
+    # the dispatcher takes this kernel between the rows of the mma.sync one and the library's
+    got = ops.linear(x, w, torch.float32)
+    torch.testing.assert_close(got.double(), want, atol=1e-4, rtol=1e-4)
+    ops.check_status()
+
+
 @pytest.mark.parametrize("m", [1, 8, 11, 16])
 @pytest.mark.parametrize("n,k", [(70, 96), (4096, 4096), (1000, 2056), (24, 8), (151, 4104), (4096, 12288)])
 def test_linear_skinny_reads_a_weight_in_its_own_order(ops, m, n, k):
