@@ -224,6 +224,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tcgen05_kernel(const __grid_c
                                                                   const __grid_constant__ CUtensorMap v_map,
                                                                   const __grid_constant__ CUtensorMap out_map,
                                                                   const Params p) {
+  pdl_trigger();      // a kernel launched behind this one (decode attention of the same step) may take the multiprocessors that the last blocks leave free
   extern __shared__ unsigned char smem_raw[];
   unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   unsigned char* q_s = base;                                   // [2 halves of d][128 rows][128 B]
@@ -278,6 +279,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tcgen05_kernel(const __grid_c
     if (warp == 0 || warp == 10) {
       // --------------------------------------------------------------- producers
       const int which = warp == 0 ? 0 : 1;                        // keys or values
+      pdl_wait();                         // queries, keys and values are the work of the kernels before this one
       if (which == 0 && lane == 0) {
         mbar_expect_tx(&sh->q_full, 2 * 128 * G * p.tokens_per_tile);      // two boxes of 64 d x G heads x tokens
         tma_load_3d(q_s, &q_map, 0, kv_head * G, q_begin + q_off, &sh->q_full);
@@ -628,6 +630,5 @@ JV_EXPORT int jv_attn_tcgen05(const void* q, int q_stride, int n_tokens, void* o
       return JV_ERR_UNSUPPORTED;
     ready = true;
   }
-  attn_tcgen05_kernel<<<dim3(n_work, n_kv_heads), THREADS, smem, stream>>>(q_map, k_map, v_map, out_map, p);
-  return jv_check_launch();
+  return jv_launch(attn_tcgen05_kernel, dim3(n_work, n_kv_heads), dim3(THREADS), smem, stream, q_map, k_map, v_map, out_map, p);
 }
