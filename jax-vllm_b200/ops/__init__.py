@@ -3,9 +3,11 @@
 Every function here checks device, dtype, shape and contiguity of what it is given,
 then passes raw pointers and the current CUDA stream to an `extern "C"` launcher loaded
 by `csrc.build`.  There is no CPU path and no library fallback: a tensor on the CPU, a
-missing compiler or a failed launch raises.  Matrix products of 16-bit operands go to
-cuBLAS through `torch.mm` (a library product, as in the reference, whose every product
-is XLA's); every other operation on the forward path is a kernel of this package.
+missing compiler or a failed launch raises.  Matrix products of 16-bit operands with more
+than 64 rows (prompt portions), except the one with the gate in its epilogue, go to cuBLAS
+through `torch.mm` (a library product, as in the reference, whose every product is XLA's);
+every other operation on the forward path, the products of decode steps among them, is a
+kernel of this package.
 """
 
 from __future__ import annotations
