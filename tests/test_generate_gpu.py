@@ -256,3 +256,37 @@ def test_prewarm_captures_the_decode_graphs_and_changes_nothing(tmp_path):
     warm.cache.check()
     assert not warm.cache.live and warm.cache.groups[0].pool.num_free == warm.cache.num_pages
     assert generate(warm, prompts, sp) == want
+
+
+@pytest.mark.parametrize("dtype", ["fp32", "bf16"])
+def test_many_requests_at_once(setup, dtype):
+    """Twenty-four requests decode together, with CUDA graphs: batches of 9 and more rows take other kernels than
+    small ones (the tcgen05 product for larger batches, the decode attention over many requests).  32-bit tokens
+    equal the plain implementation's; bfloat16 tokens equal it wherever the plain choice is clear."""
+    from jax_vllm_b200 import SamplingParams, generate, make_driver, prewarm
+    tag, folder, plain = setup
+    vocab, P = TINY[tag]["vocab_size"], PAGE_SIZE[tag]
+    new = 6
+    prompts = [random_tokens(3 + (7 * i) % 23, vocab, seed=300 + i) for i in range(24)]
+    model = load(folder, dtype)
+    d = make_driver(model, max_num_seqs=24, max_model_len=-(-(26 + new) // P) * P, block_size=P, prefix_cache=False)
+    prewarm(d)
+    got = generate(d, prompts, SamplingParams(max_new_tokens=new))
+    assert d.stats.steps < 24 * new                      # they did run together
+    d.cache.check()
+    assert not d.cache.live
+    checked = 0
+    for p, out in zip(prompts, got):
+        assert len(out) == new
+        if dtype == "fp32":
+            assert out == plain.greedy(p, new)
+            continue
+        seq = list(p)
+        for tok in out:
+            logits = plain.logits(seq)[-1]
+            top = logits.topk(2).values
+            if (top[0] - top[1]).item() > 0.06 * logits.abs().max().item():
+                assert tok == int(logits.argmax())
+                checked += 1
+            seq.append(tok)
+    assert dtype == "fp32" or checked >= 40
