@@ -245,7 +245,8 @@ def time_e2e(model, batch, steps, warmup, ctx=CONTEXT):
 def micro(spec: str, reps: int, eager: bool = False) -> int:
     """One kernel alone on data larger than the L2, for profiling:
     gemm:<N>x<K>:<M>:<impl>  the prompt product, impl = tcgen05 | tcgen05_swiglu | library (cuBLAS)
-    linear:<N>x<K>:<M>[:parts][:packed]   the decode product of M rows with an [N, K] weight (several weights in turn)
+    linear:<N>x<K>:<M>[:parts][:stream|:skinny|:library]   the decode product of M rows with an [N, K] weight (several weights in turn):
+                         as the engine picks it, or the tcgen05 kernel, the mma.sync kernel, cuBLAS
     attn_decode:<B>:<CTX>[:<SPLIT>[:<PAGE>[:<KV HEADS>]]]   split decode attention of B requests with CTX cached tokens (8B head layout,
                          several caches in turn so that none stays in the L2), mma.sync kernel
     attn_decode_tcgen05:<B>:<CTX>[:<SPLIT>[:<PAGE>]]   the same with the tcgen05 kernel
@@ -285,8 +286,7 @@ def micro(spec: str, reps: int, eager: bool = False) -> int:
         ws = [(torch.randn(n, k, device=dev) * 0.02).to(torch.bfloat16) for _ in range(copies)]
         x = torch.randn(m, k, device=dev).to(torch.bfloat16)
         parts_ok = "parts" in rest[2:]        # let the kernel cut k and leave the parts of a sum
-        if "packed" in rest[2:]:              # the weight in the kernel's own order
-            ws = [ops.PackedWeight(w) for w in ws]
+        if "skinny" in rest[2:]:              # the mma.sync kernel, whatever the dispatcher would take
             run = lambda i: ops.linear_skinny(x, ws[i % copies], torch.bfloat16, parts_ok)
         elif "stream" in rest[2:]:            # the tcgen05 product for larger batches, whatever the rows
             run = lambda i: ops.linear_stream(x, ws[i % copies], torch.bfloat16, parts_ok)
@@ -382,7 +382,7 @@ WORKLOADS = {
 }
 
 
-def workload(name: str, layers, weight_copy: bool) -> int:
+def workload(name: str, layers) -> int:
     """Runs one of WORKLOADS through the entry point and prints one JSON line: wall-clock seconds, prompt and
     generated tokens per second, time to the first token, and the steps by kind (with a portion of a prompt
     in them, or decoding alone) with their time and the tokens they ran."""
@@ -393,8 +393,7 @@ def workload(name: str, layers, weight_copy: bool) -> int:
     cfg_dict = dict(QWEN3_8B, **w["config"])
     if layers:
         cfg_dict["num_hidden_layers"] = layers
-    model = random_model(registry.config_from_dict(cfg_dict), seed=w["seed"], dtype="bf16", device="cuda:0",
-                         pack_decode_weights=weight_copy)
+    model = random_model(registry.config_from_dict(cfg_dict), seed=w["seed"], dtype="bf16", device="cuda:0")
     rng = random.Random(w["prompt_seed"])
     vocab = cfg_dict["vocab_size"]
     shared = [rng.randrange(vocab) for _ in range(w["shared_prefix"])]
@@ -435,7 +434,7 @@ def workload(name: str, layers, weight_copy: bool) -> int:
         out["steps_" + kind] = {"steps": n, "ms_per_step": round(1e3 * sec / max(1, n), 2),
                                 "tokens_per_s": round(toks / max(1e-9, sec), 1)}
     out.update({"preemptions": st.preemptions, "prefix_hit_tokens": st.cache_hit_tokens, "prewarm_s": round(warm, 1),
-                "gb_allocated": round(torch.cuda.max_memory_allocated() / 1e9, 1), "decode_weight_copy": weight_copy,
+                "gb_allocated": round(torch.cuda.max_memory_allocated() / 1e9, 1),
                 "clocks": clocks.summary})
     print(json.dumps(out))
     return 0
@@ -462,7 +461,6 @@ def main():
     ap.add_argument("--micro", default=None, help="run one kernel alone, e.g. linear:24576x4096:8 (see micro())")
     ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS),
                     help="a serving workload of a larger shape through the entry point (see WORKLOADS); --layers cuts it")
-    ap.add_argument("--no-decode-weight-copy", action="store_true", help="with --workload: no second copy of the matrices")
     ap.add_argument("--micro-eager", action="store_true",
                     help="with --micro: plain launches instead of replays of a CUDA graph (for a profiler)")
     args = ap.parse_args()
@@ -474,7 +472,7 @@ def main():
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
     if args.workload:
-        return workload(args.workload, args.layers, not args.no_decode_weight_copy)
+        return workload(args.workload, args.layers)
     args.layers = args.layers or QWEN3_8B["num_hidden_layers"]
     warmup = max(3, args.warmup)
 
@@ -504,7 +502,7 @@ def main():
                    "hidden": 4096, "q_heads": 32, "kv_heads": 8, "head_dim": 128, "intermediate": 12288,
                    "vocab": 151936, "global_batch": args.batch, "seq_len": CONTEXT, "max_context": 4096,
                    "page_size": PAGE, "parallelism": "none (1 GPU)", "l2": "inputs larger than L2 (15 GB of weights)",
-                   "cuda_graphs": True, "decode_weight_copy": True},
+                   "cuda_graphs": True},
         "gpu_launches": launches * args.steps,
         "clocks": clocks.summary,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",

@@ -49,9 +49,6 @@ def main(argv=None) -> int:
     p.add_argument("--max-tokens-per-step", type=int, default=2048)
     p.add_argument("--ignore-eos", action="store_true", help="generate --max-tokens tokens whatever is sampled")
     p.add_argument("--no-prefix-cache", dest="prefix_cache", action="store_false")
-    p.add_argument("--no-decode-weight-copy", dest="pack_decode_weights", action="store_false",
-                   help="do not keep a second copy of the matrices in the order the decode product streams them "
-                        "(saves their bytes, decoding is a few per cent slower)")
     p.add_argument("--random-weights", type=int, default=None, metavar="SEED",
                    help="do not read weights: draw them from this seed (needs --config or --model-path for config.json)")
     p.add_argument("--config", default=None, help="a config.json for --random-weights")
@@ -64,14 +61,13 @@ def main(argv=None) -> int:
         src = args.config or args.model_path
         if not src:
             p.error("--random-weights needs --config or --model-path")
-        model = random_model(registry.config_from_path(src), args.random_weights, dtype=args.dtype,
-                             pack_decode_weights=args.pack_decode_weights)
+        model = random_model(registry.config_from_path(src), args.random_weights, dtype=args.dtype)
         print(f"random weights (seed {args.random_weights}) for {src} ({args.dtype})", flush=True)
     else:
         if not args.model_path:
             p.error("--model-path is required")
         print(f"loading {args.model_path} ({args.dtype})...", flush=True)
-        model = load_from_path(args.model_path, dtype=args.dtype, pack_decode_weights=args.pack_decode_weights)
+        model = load_from_path(args.model_path, dtype=args.dtype)
 
     prompts = [parse_ids(t) for t in args.prompt_ids]
     tokenizer = None

@@ -53,12 +53,7 @@ __device__ __forceinline__ void cp_async16(void* dst, const void* src, bool vali
 // strip goes to parts[s] ([splits, M, N], 32-bit) and the kernel that reads the result adds the parts in the
 // order of s as it loads them: nobody waits and no block sums up after another.  The partition depends on
 // N, K and the number of multiprocessors only, never on the batch.
-// PACKED: W is not [N, K] rows but the same values in the order in which this kernel asks for them: for every
-// strip of 16 rows and every 64-wide chunk of k, the four 512-byte pieces (rows 0-7 / 8-15 x first / second half of
-// the chunk) that a warp's four copy instructions fetch, lane by lane (rows and k padded with zeros to multiples
-// of 16 and 64).  Every instruction of a warp then reads 512 consecutive bytes, every chunk 2 KB, and a warp's
-// chunks of a unit follow one another in memory: a linear stream instead of 8 rows x 64 bytes per instruction.
-template <int NB, typename TOut, bool PACKED>
+template <int NB, typename TOut>
 __global__ void __launch_bounds__(WARPS * 32, CTAS_PER_SM) skinny_kernel(const __nv_bfloat16* __restrict__ X, int ldx,
                                                                          const __nv_bfloat16* __restrict__ W, int ldw,
                                                                          TOut* __restrict__ Y, int ldy, int M, int N,
@@ -94,26 +89,16 @@ __global__ void __launch_bounds__(WARPS * 32, CTAS_PER_SM) skinny_kernel(const _
       const int n0 = p_n0;
       const int k0 = p_k;
       uint4* slot = &ring[warp][p_count % STAGES][0][lane];
-      if constexpr (PACKED) {
-        // chunk (strip, k0 / 64) is 2 KB; `ldw` is the number of chunks of a strip (k padded), beyond which lie zeros
-        const bool ok = k0 < K;
-        const uint4* src = reinterpret_cast<const uint4*>(W) + ((size_t)(n0 >> 4) * ldw + (ok ? (k0 >> 6) : 0)) * 128 + lane;
-        cp_async16(slot, src, ok);
-        cp_async16(slot + 32, src + 32, ok);
-        cp_async16(slot + 64, src + 64, ok);
-        cp_async16(slot + 96, src + 96, ok);
-      } else {
-        const int ka = k0 + c * 8, kb = k0 + 32 + c * 8;
-        const bool oka = ka + 8 <= K, okb = kb + 8 <= K;
-        const int r0 = n0 + r, r1 = n0 + r + 8;
-        const bool ok0 = r0 < N, ok1 = r1 < N;
-        const __nv_bfloat16* w0 = W + (size_t)(ok0 ? r0 : 0) * ldw;
-        const __nv_bfloat16* w1 = W + (size_t)(ok1 ? r1 : 0) * ldw;
-        cp_async16(slot, w0 + (oka ? ka : 0), ok0 && oka);
-        cp_async16(slot + 32, w0 + (okb ? kb : 0), ok0 && okb);
-        cp_async16(slot + 64, w1 + (oka ? ka : 0), ok1 && oka);
-        cp_async16(slot + 96, w1 + (okb ? kb : 0), ok1 && okb);
-      }
+      const int ka = k0 + c * 8, kb = k0 + 32 + c * 8;
+      const bool oka = ka + 8 <= K, okb = kb + 8 <= K;
+      const int r0 = n0 + r, r1 = n0 + r + 8;
+      const bool ok0 = r0 < N, ok1 = r1 < N;
+      const __nv_bfloat16* w0 = W + (size_t)(ok0 ? r0 : 0) * ldw;
+      const __nv_bfloat16* w1 = W + (size_t)(ok1 ? r1 : 0) * ldw;
+      cp_async16(slot, w0 + (oka ? ka : 0), ok0 && oka);
+      cp_async16(slot + 32, w0 + (okb ? kb : 0), ok0 && okb);
+      cp_async16(slot + 64, w1 + (oka ? ka : 0), ok1 && oka);
+      cp_async16(slot + 96, w1 + (okb ? kb : 0), ok1 && okb);
       ++p_count;
       p_k += KC;
       if (++p_chunk == per_warp) { p_chunk = 0; p_unit += gridDim.x; p_n0 = (p_unit / splits) * 16; p_k = k_of(p_unit); }
@@ -241,7 +226,7 @@ int choose_splits(int n_strips, int K, int sms) {
   return best;
 }
 
-template <typename TOut, bool PACKED>
+template <typename TOut>
 int launch(const void* X, int ldx, const void* W, int ldw, void* Y, int ldy, int M, int N, int K, int splits, float* parts,
            cudaStream_t stream) {
   const int sms = multiprocessors();
@@ -255,16 +240,16 @@ int launch(const void* X, int ldx, const void* W, int ldw, void* Y, int ldy, int
   TOut* y = (TOut*)Y;
   static bool ready = false;   // set once: the attribute calls are kept out of stream captures
   if (!ready) {
-    if (cudaFuncSetAttribute(skinny_kernel<1, TOut, PACKED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes<1>()) != cudaSuccess ||
-        cudaFuncSetAttribute(skinny_kernel<2, TOut, PACKED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes<2>()) != cudaSuccess)
+    if (cudaFuncSetAttribute(skinny_kernel<1, TOut>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes<1>()) != cudaSuccess ||
+        cudaFuncSetAttribute(skinny_kernel<2, TOut>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes<2>()) != cudaSuccess)
       return JV_ERR_UNSUPPORTED;
     ready = true;
   }
   if (M <= 8)
-    return jv_launch(skinny_kernel<1, TOut, PACKED>, dim3(blocks), dim3(WARPS * 32), smem_bytes<1>(), stream, x, ldx, w, ldw, y,
+    return jv_launch(skinny_kernel<1, TOut>, dim3(blocks), dim3(WARPS * 32), smem_bytes<1>(), stream, x, ldx, w, ldw, y,
                      ldy, M, N, K, n_strips, splits, per_warp, parts);
   if (M <= 16)
-    return jv_launch(skinny_kernel<2, TOut, PACKED>, dim3(blocks), dim3(WARPS * 32), smem_bytes<2>(), stream, x, ldx, w, ldw, y,
+    return jv_launch(skinny_kernel<2, TOut>, dim3(blocks), dim3(WARPS * 32), smem_bytes<2>(), stream, x, ldx, w, ldw, y,
                      ldy, M, N, K, n_strips, splits, per_warp, parts);
   return JV_ERR_UNSUPPORTED;
 }
@@ -280,21 +265,14 @@ JV_EXPORT int jv_linear_skinny_plan(int N, int K) { return choose_splits((N + 15
 // bfloat16 (out_dtype 1) or float (0).  splits > 1 (at most 8, each part at least 8 chunks of 64): Y is not
 // written; parts [splits, M, N] float gets the sums over the parts of k, to be added by the reader.
 // K, ldx and ldw must be multiples of 8 and X, W 16-byte aligned.
-// packed != 0: W is the weight in this kernel's own order (see jv_linear_skinny_pack_size; ldw is ignored).
 JV_EXPORT int jv_linear_skinny(const void* X, int ldx, const void* W, int ldw, void* Y, int out_dtype, int ldy, int M,
-                               int N, int K, float* parts, int splits, int packed, cudaStream_t stream) {
+                               int N, int K, float* parts, int splits, cudaStream_t stream) {
   if (M == 0 || N == 0) return JV_OK;
-  if (M > 16 || K < 8 || (K % 8) || (ldx % 8) || (!packed && (ldw % 8)) || ((uintptr_t)X % 16) || ((uintptr_t)W % 16))
+  if (M > 16 || K < 8 || (K % 8) || (ldx % 8) || (ldw % 8) || ((uintptr_t)X % 16) || ((uintptr_t)W % 16))
     return JV_ERR_UNSUPPORTED;
   if (splits < 1 || splits > 8 || (splits > 1 && (parts == nullptr || (K + KC - 1) / KC < splits * WARPS)))
     return JV_ERR_UNSUPPORTED;
-  if (packed) {
-    const int chunks = (K + KC - 1) / KC;            // chunks of a strip in the packed weight
-    if (out_dtype == 0) return launch<float, true>(X, ldx, W, chunks, Y, ldy, M, N, K, splits, parts, stream);
-    if (out_dtype == 1) return launch<__nv_bfloat16, true>(X, ldx, W, chunks, Y, ldy, M, N, K, splits, parts, stream);
-    return JV_ERR_UNSUPPORTED;
-  }
-  if (out_dtype == 0) return launch<float, false>(X, ldx, W, ldw, Y, ldy, M, N, K, splits, parts, stream);
-  if (out_dtype == 1) return launch<__nv_bfloat16, false>(X, ldx, W, ldw, Y, ldy, M, N, K, splits, parts, stream);
+  if (out_dtype == 0) return launch<float>(X, ldx, W, ldw, Y, ldy, M, N, K, splits, parts, stream);
+  if (out_dtype == 1) return launch<__nv_bfloat16>(X, ldx, W, ldw, Y, ldy, M, N, K, splits, parts, stream);
   return JV_ERR_UNSUPPORTED;
 }

@@ -499,39 +499,12 @@ def linear_skinny_splits(device, n: int, k: int) -> int:
     return plan
 
 
-class PackedWeight:
-    """A bfloat16 weight [n, k] in the order in which the decode product (csrc/linear_skinny.cu) reads it:
-    for every strip of 16 rows and every 64-wide chunk of k, four 512-byte pieces (rows 0-7 / 8-15 of the
-    strip x first / second 32 of the chunk), each piece lane by lane (lane = row % 8 * 4 + (k % 32) / 8, then
-    8 consecutive k); rows and k are padded with zeros to multiples of 16 and 64.  A warp's copy instruction
-    then reads 512 consecutive bytes and its chunks follow one another: the product streams the weight
-    linearly."""
-
-    def __init__(self, weight: torch.Tensor):
-        _cuda(weight, "weight", torch.bfloat16, contiguous=False)
-        n, k = weight.shape
-        n16, k64 = -(-n // 16) * 16, -(-k // 64) * 64
-        padded = weight
-        if (n16, k64) != (n, k):
-            padded = torch.zeros((n16, k64), dtype=weight.dtype, device=weight.device)
-            padded[:n, :k] = weight
-        # [strip, row half, row % 8, chunk, k half, (k % 32) / 8, k % 8] -> [strip, chunk, row half, k half, row % 8, (k % 32) / 8, k % 8]
-        v = padded.reshape(n16 // 16, 2, 8, k64 // 64, 2, 4, 8)
-        self.data = v.permute(0, 3, 1, 4, 2, 5, 6).contiguous()
-        self.shape = (n, k)
-        self.device = weight.device
-
-
-def linear_skinny(x: torch.Tensor, weight, out_dtype: torch.dtype, parts_ok: bool = False):
+def linear_skinny(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype, parts_ok: bool = False):
     """x [M <= 16, K] times weight [N, K] transposed, bfloat16 operands, 32-bit accumulation
-    (csrc/linear_skinny.cu); `weight` is a tensor or a PackedWeight; the result is bfloat16 or float32, or
-    with `parts_ok`, where the kernel cuts k for an even load, a PartialSum for a reader that adds the parts."""
-    packed = isinstance(weight, PackedWeight)
-    _cuda(x, "x", torch.bfloat16, contiguous=False)
-    if not packed:
-        _cuda(weight, "weight", torch.bfloat16, contiguous=False)
-    if x.dim() != 2 or len(weight.shape) != 2 or x.shape[1] != weight.shape[1] or x.stride(1) != 1 or \
-            (not packed and weight.stride(1) != 1):
+    (csrc/linear_skinny.cu); the result is bfloat16 or float32, or with `parts_ok`, where the kernel cuts k
+    for an even load, a PartialSum for a reader that adds the parts."""
+    _cuda(x, "x", torch.bfloat16, contiguous=False); _cuda(weight, "weight", torch.bfloat16, contiguous=False)
+    if x.dim() != 2 or weight.dim() != 2 or x.shape[1] != weight.shape[1] or x.stride(1) != 1 or weight.stride(1) != 1:
         raise KernelError(f"linear shapes {tuple(x.shape)} x {tuple(weight.shape)}^T do not fit")
     m, k = x.shape
     n = weight.shape[0]
@@ -543,17 +516,15 @@ def linear_skinny(x: torch.Tensor, weight, out_dtype: torch.dtype, parts_ok: boo
         parts = None
         y = torch.empty((m, n), dtype=out_dtype, device=x.device)
     f = _fn("linear_skinny", "jv_linear_skinny", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
-                                                  c_int, c_void_p, c_int, c_int, c_void_p])
-    w_ptr, ldw = (weight.data.data_ptr(), 0) if packed else (weight.data_ptr(), weight.stride(0))
-    _check(f(x.data_ptr(), x.stride(0), w_ptr, ldw, _ptr(y), DTYPE_CODE[out_dtype],
-             n if y is None else y.stride(0), m, n, k, _ptr(parts), splits, 1 if packed else 0, _stream()), "linear_skinny")
+                                                  c_int, c_void_p, c_int, c_void_p])
+    _check(f(x.data_ptr(), x.stride(0), weight.data_ptr(), weight.stride(0), _ptr(y), DTYPE_CODE[out_dtype],
+             n if y is None else y.stride(0), m, n, k, _ptr(parts), splits, _stream()), "linear_skinny")
     return y if parts is None else PartialSum(parts)
 
 
 STREAM_MAX_ROWS = 128
-# which product the dispatcher takes: up to 8 rows the mma.sync kernel (its second 8 rows cost it a fifth), up to
-# 64 rows the tcgen05 one, beyond that the library's (which shares x between two multiprocessors)
-SKINNY_BEST_ROWS = 8
+# up to this many rows the dispatcher takes the tcgen05 product of this package, beyond that the library's (which
+# shares x between two multiprocessors)
 STREAM_BEST_ROWS = 64
 _stream_plans: dict = {}
 
@@ -646,28 +617,25 @@ def _skinny_ok(x: torch.Tensor, weight: torch.Tensor) -> bool:
             and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0 and x.stride(1) == 1)
 
 
-def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None = None, parts_ok: bool = False,
-           packed=None):
+def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None = None, parts_ok: bool = False):
     """y = x @ weight.T.  With `parts_ok` the result may be a PartialSum (the caller hands it to `rmsnorm`,
-    `residual_add` or `swiglu`, which add its parts as they read them).  `packed`: the same weight as a
-    PackedWeight, which the product for a few rows reads instead.
+    `residual_add` or `swiglu`, which add its parts as they read them).
 
-    float32 weights: the CUDA-core product of this package in true 32-bit (16-bit
-    activations are read as they are and widened inside).  bfloat16 weights and
-    activations: up to SKINNY_BEST_ROWS rows (decoding) the weight-streaming kernel of this
-    package on mma.sync, up to STREAM_BEST_ROWS rows (larger batches of decoded tokens) the one on tcgen05;
-    more rows (prompts) cuBLAS through torch.mm; all accumulate in 32-bit and give the result in
-    `out_dtype` (bfloat16 by default, float32 for logits)."""
+    float32 weights: the CUDA-core product of this package in true 32-bit (16-bit activations are read as they
+    are and widened inside).  bfloat16 weights and activations: up to STREAM_BEST_ROWS rows (decoding) the
+    weight-streaming product on tcgen05 (csrc/linear_stream.cu), which cuts the k of a weight with few strips into
+    parts; where the reader wants one tensor and the strips are few, the mma.sync product (csrc/linear_skinny.cu, up
+    to SKINNY_MAX_ROWS rows), whose strips are 16 rows; more rows (prompts) cuBLAS through torch.mm.  All
+    accumulate in 32-bit and give the result in `out_dtype` (bfloat16 by default, float32 for logits)."""
     out_dtype = out_dtype or x.dtype
     if weight.dtype == torch.float32 or x.dtype == torch.float32:
         return gemm_simt(x, weight, out_dtype)
     _cuda(x, "x", torch.bfloat16, contiguous=False); _cuda(weight, "weight", torch.bfloat16)
-    stream = _stream_ok(x, weight) and out_dtype in (torch.bfloat16, torch.float32) and \
-        (parts_ok or _strips_fill_the_device(x.device, weight.shape[0]))
-    if _skinny_ok(x, weight) and (x.shape[0] <= SKINNY_BEST_ROWS or not stream):
-        return linear_skinny(x, weight if packed is None else packed, out_dtype, parts_ok)
-    if stream and x.shape[0] <= STREAM_BEST_ROWS:
+    if _stream_ok(x, weight) and x.shape[0] <= STREAM_BEST_ROWS and out_dtype in (torch.bfloat16, torch.float32) and \
+            (parts_ok or _strips_fill_the_device(x.device, weight.shape[0])):
         return linear_stream(x, weight, out_dtype, parts_ok)
+    if _skinny_ok(x, weight):
+        return linear_skinny(x, weight, out_dtype, parts_ok)
     if out_dtype == torch.bfloat16:
         return torch.mm(x, weight.t())
     return torch.mm(x, weight.t(), out_dtype=out_dtype)

@@ -44,7 +44,7 @@ class Attention(Part):
             self.kernels = ("rope_kv", "attn_mma", "gemm_simt", "linear_skinny")
             if self.d == 128 and not self.window:
                 self.kernels += ("attn_tcgen05", "attn_decode_tcgen05")
-        self.w_qkv = self.w_o = self.q_norm = self.k_norm = self.w_qkv_decode = self.w_o_decode = None
+        self.w_qkv = self.w_o = self.q_norm = self.k_norm = None
 
     # -------------------------------------------------------------------- weights
     def _names(self):
@@ -74,7 +74,6 @@ class Attention(Part):
             mats = [m.to(torch.float32) for m in mats]
         self.w_qkv = torch.cat(mats, dim=0).contiguous()
         self.w_o = self.compute_weight(tensors[n["o_proj"]], self.ctx).contiguous()
-        self.w_qkv_decode, self.w_o_decode = self.decode_copy(self.w_qkv, self.ctx), self.decode_copy(self.w_o, self.ctx)
         if self.spec.qk_norm_eps is not None:
             self.q_norm = tensors[n["q_norm"]].contiguous()
             self.k_norm = tensors[n["k_norm"]].contiguous() if self.writes_cache else None
@@ -99,7 +98,7 @@ class Attention(Part):
     # ----------------------------------------------------------------------- step
     def forward(self, x, step, cache):
         dt = self.ctx.dtype
-        qkv = ops.linear(x, self.w_qkv, dt, packed=self.w_qkv_decode)
+        qkv = ops.linear(x, self.w_qkv, dt)
         table = step.block_tables[cache.group]
         writes = self.writes_cache and cache.writes
         out = torch.empty((step.n_tokens, self.hq * self.d), dtype=dt, device=x.device)
@@ -110,13 +109,13 @@ class Attention(Part):
             ops.attn_decode_tcgen05(qkv, qkv.stride(0), out, cache.k, cache.v, table, step.cu_seqlens, step.start_pos,
                                     dwork, n_dec, self.hq, self.hkv, self.d, self.spec.scale,
                                     prepare=(freq, self.q_norm, self.k_norm, self.spec.qk_norm_eps or 0.0))
-            return ops.linear(out, self.w_o, dt, parts_ok=True, packed=self.w_o_decode)
+            return ops.linear(out, self.w_o, dt, parts_ok=True)
         ops.rope_kv(qkv, step.positions, step.token_entry, table,
                     self.position.table() if self.position is not None else None,
                     self.q_norm, self.k_norm, self.spec.qk_norm_eps or 0.0,
                     cache.k if writes else None, cache.v if writes else None, self.hq, self.hkv, self.d)
         self.attend(qkv, out, step, cache, table)
-        return ops.linear(out, self.w_o, dt, parts_ok=True, packed=self.w_o_decode)    # maybe the parts of a sum, for the next norm to add
+        return ops.linear(out, self.w_o, dt, parts_ok=True)    # maybe the parts of a sum, for the next norm to add
 
     def _decode_kernel_prepares(self, cache, n_dec) -> bool:
         """Whether the tcgen05 decode kernel takes these tokens together with their preparation (it rotates whole

@@ -52,7 +52,6 @@ class BuildContext:
     dtype: torch.dtype            # compute dtype: activations, 16-bit weights, cache
     device: torch.device
     decode_split_size: int = 256
-    pack_decode_weights: bool = True   # keep a second copy of every 16-bit matrix in the order the decode product reads it
 
 
 class Part:
@@ -63,15 +62,6 @@ class Part:
 
     def bind(self, tensors: dict) -> None:
         pass
-
-    def decode_copy(self, w: torch.Tensor, ctx: BuildContext):
-        """The matrix once more in the order in which the product for a few rows (decoding) streams it
-        (`ops.PackedWeight`): 3 to 8 % faster there, for as many bytes again; None where that product is not
-        taken (32-bit path, 32-bit-stored weights) or the copy is switched off."""
-        from .. import ops
-        if ctx.pack_decode_weights and ctx.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.is_cuda:
-            return ops.PackedWeight(w)
-        return None
 
     def compute_weight(self, t: torch.Tensor, ctx: BuildContext) -> torch.Tensor:
         """Matrix weights as the products read them: the compute dtype in 32-bit mode;

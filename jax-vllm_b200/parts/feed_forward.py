@@ -47,8 +47,6 @@ class GatedMLP(Part):
         else:
             self.w_gate_up = torch.cat([g, u], dim=0).contiguous()
         self.w_down = self.compute_weight(tensors[f"{p}.down_proj.weight"], self.ctx).contiguous()
-        self.w_gate_up_decode = self.decode_copy(self.w_gate_up, self.ctx)
-        self.w_down_decode = self.decode_copy(self.w_down, self.ctx)
 
     # From this many rows on the gate is applied in the epilogue of the tcgen05 product; below, the product's
     # 128 x 256 tiles leave multiprocessors idle and the library product followed by the gate kernel is faster
@@ -60,9 +58,9 @@ class GatedMLP(Part):
         if self.block is not None and x.shape[0] >= self.FUSED_GATE_ROWS:
             act = ops.gemm_tcgen05(x, self.w_gate_up, "swiglu")
         else:
-            act = ops.swiglu(ops.linear(x, self.w_gate_up, dt, parts_ok=True, packed=self.w_gate_up_decode), self.block, out_dtype=dt)
+            act = ops.swiglu(ops.linear(x, self.w_gate_up, dt, parts_ok=True), self.block, out_dtype=dt)
         # a few rows: the product may come as the parts of a sum, which the next norm adds as it reads them
-        return ops.linear(act, self.w_down, dt, parts_ok=True, packed=self.w_down_decode)
+        return ops.linear(act, self.w_down, dt, parts_ok=True)
 
 
 register_feed_forward("gated_mlp", GatedMLP)

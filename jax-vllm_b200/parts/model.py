@@ -56,7 +56,6 @@ class Model(Part):
         self.final_norm.bind(tensors)
         head = self.embedding if s.lm_head_name is None else tensors[s.lm_head_name]
         self.lm_head = self.compute_weight(head, self.ctx).contiguous()
-        self.lm_head_decode = self.decode_copy(self.lm_head, self.ctx)
 
     def kernels(self):
         names = {"embed", "norm", "gemm_simt"}
@@ -93,4 +92,4 @@ class Model(Part):
         if step.n_logit_rows == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=h.device)
         x = self.final_norm.gather(h, delta, step.logit_rows)
-        return ops.linear(x, self.lm_head, torch.float32, packed=self.lm_head_decode)
+        return ops.linear(x, self.lm_head, torch.float32)

@@ -165,9 +165,8 @@ def test_feed_forward_bf16_with_the_gate_in_the_product(rows):
 
 @pytest.mark.parametrize("rows", [1, 7, 16, 40])
 def test_feed_forward_bf16_whose_down_product_comes_as_the_parts_of_a_sum(rows):
-    """A feed-forward wide enough that the decode kernels (mma.sync up to 8 rows, tcgen05 up to 64) cut the k of the
-    down product (few strips, long k): the part hands back the parts of a sum, which the next norm adds to the
-    stream as it reads them."""
+    """A feed-forward wide enough that the decode product cuts the k of the down product (few strips, long k): the
+    part hands back the parts of a sum, which the next norm adds to the stream as it reads them."""
     j, cache, config, engine, parts, weights = pkg()
     from jax_vllm_b200 import ops
     ctx = parts.BuildContext(torch.bfloat16, DEV)
@@ -177,7 +176,7 @@ def test_feed_forward_bf16_whose_down_product_comes_as_the_parts_of_a_sum(rows):
     ff.bind({k: v.to(DEV) for k, v in w.items()})
     x = torch.randn(rows, 1024, generator=g).to(torch.bfloat16)
     got = ff.forward(x.to(DEV), None)
-    plan = ops.linear_skinny_splits if rows <= ops.SKINNY_BEST_ROWS else ops.linear_stream_splits
+    plan = ops.linear_stream_splits
     assert isinstance(got, ops.PartialSum) and got.parts.shape[0] == plan(DEV, 1024, 2048) > 1
     rnd = lambda t: t.to(torch.bfloat16).double()
     wd = {k: v.double() for k, v in w.items()}
