@@ -479,7 +479,7 @@ def gemm_simt(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype) -> 
     return y
 
 
-SKINNY_MAX_ROWS = 16      # batches up to this many rows take the kernel that is bound by reading the weight
+SKINNY_MAX_ROWS = 16      # rows the mma.sync kernel takes (in a replayed decode step it beats the library up to there)
 
 
 _skinny_plans: dict = {}      # (device, N, K) -> parts of k per strip
@@ -625,7 +625,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None 
     are and widened inside).  bfloat16 weights and activations: up to STREAM_BEST_ROWS rows (decoding) the
     weight-streaming product on tcgen05 (csrc/linear_stream.cu), which cuts the k of a weight with few strips into
     parts; where the reader wants one tensor and the strips are few, the mma.sync product (csrc/linear_skinny.cu, up
-    to SKINNY_MAX_ROWS rows), whose strips are 16 rows; more rows (prompts) cuBLAS through torch.mm.  All
+    to SKINNY_MAX_ROWS rows), whose strips are 16 rows; else (prompts) cuBLAS through torch.mm.  All
     accumulate in 32-bit and give the result in `out_dtype` (bfloat16 by default, float32 for logits)."""
     out_dtype = out_dtype or x.dtype
     if weight.dtype == torch.float32 or x.dtype == torch.float32:
