@@ -66,7 +66,21 @@ __global__ void swiglu_parts_kernel(const float* __restrict__ gu, T* __restrict_
     const size_t col = (size_t)(i / block) * 2 * block + (i % block);
     const float* src = gu + n * 2 * inter + col;
     float4 g = *reinterpret_cast<const float4*>(src), u = *reinterpret_cast<const float4*>(src + block);
-    for (int s = 1; s < parts; ++s) {
+    // up to eight parts ask for their loads together; they are added in the order of the parts
+    float4 gp[7], up[7];
+#pragma unroll
+    for (int s = 1; s < 8; ++s)
+      if (s < parts) {
+        gp[s - 1] = *reinterpret_cast<const float4*>(src + s * part_stride);
+        up[s - 1] = *reinterpret_cast<const float4*>(src + s * part_stride + block);
+      }
+#pragma unroll
+    for (int s = 1; s < 8; ++s)
+      if (s < parts) {
+        g.x += gp[s - 1].x; g.y += gp[s - 1].y; g.z += gp[s - 1].z; g.w += gp[s - 1].w;
+        u.x += up[s - 1].x; u.y += up[s - 1].y; u.z += up[s - 1].z; u.w += up[s - 1].w;
+      }
+    for (int s = 8; s < parts; ++s) {
       const float4 g2 = *reinterpret_cast<const float4*>(src + s * part_stride);
       const float4 u2 = *reinterpret_cast<const float4*>(src + s * part_stride + block);
       g.x += g2.x; g.y += g2.y; g.z += g2.z; g.w += g2.w;

@@ -83,8 +83,12 @@ template <> __device__ __forceinline__ void store8<__nv_bfloat16>(__nv_bfloat16*
   *reinterpret_cast<uint4*>(p) = a;
 }
 
-template <typename TD, typename TW, typename TY>
-__global__ void rmsnorm_vec_kernel(float* __restrict__ h, const TD* __restrict__ delta,
+// ITERS: passes per thread (1 for rows of up to 640 vectors of 8, else RM_ITERS).  TOGETHER: how many parts of a
+// sum ask for their loads at once: 8 for a few rows (a decode step waits for this kernel, and one trip to the L2
+// per part is most of its time), 1 for many rows, where registers are better spent on more blocks per
+// multiprocessor.
+template <typename TD, typename TW, typename TY, int ITERS, int TOGETHER>
+__global__ void __launch_bounds__(ITERS == 1 ? 640 : 1024) rmsnorm_vec_kernel(float* __restrict__ h, const TD* __restrict__ delta,
                                    const int* __restrict__ rows, const TW* __restrict__ weight,
                                    TY* __restrict__ y, int hidden, float eps, int n_rows_total,
                                    int* __restrict__ status, int parts, size_t part_stride) {
@@ -104,21 +108,32 @@ __global__ void rmsnorm_vec_kernel(float* __restrict__ h, const TD* __restrict__
   float* hr = h + (size_t)r * hidden;
   const TD* dr = delta ? delta + (size_t)r * hidden : nullptr;
   const bool write_back = (dr != nullptr) && (rows == nullptr);
-  float v[RM_ITERS][8];
+  float v[ITERS][8];
   float ss = 0.f;
 #pragma unroll
-  for (int it = 0; it < RM_ITERS; ++it) {
+  for (int it = 0; it < ITERS; ++it) {
     const int c = (it * blockDim.x + threadIdx.x) * 8;
     if (c < hidden) {
       load8<float>(hr + c, v[it]);
       if (dr) {
+        // the parts of a sum (eight at most ask for their loads together, then add in the order of the parts)
         float d[8];
         load8<TD>(dr + c, d);
-        for (int s = 1; s < parts; ++s) {
-          float e[8];
-          load8<TD>(dr + s * part_stride + c, e);
+        float e[TOGETHER][8];
 #pragma unroll
-          for (int k = 0; k < 8; ++k) d[k] += e[k];
+        for (int s = 1; s < TOGETHER; ++s)
+          if (s < parts) load8<TD>(dr + s * part_stride + c, e[s]);
+#pragma unroll
+        for (int s = 1; s < TOGETHER; ++s)
+          if (s < parts) {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) d[k] += e[s][k];
+          }
+        for (int s = TOGETHER; s < parts; ++s) {
+          float f[8];
+          load8<TD>(dr + s * part_stride + c, f);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) d[k] += f[k];
         }
 #pragma unroll
         for (int k = 0; k < 8; ++k) v[it][k] += d[k];
@@ -132,7 +147,7 @@ __global__ void rmsnorm_vec_kernel(float* __restrict__ h, const TD* __restrict__
   const float inv = rsqrtf(ss / (float)hidden + eps);
   TY* yr = y + (size_t)i * hidden;
 #pragma unroll
-  for (int it = 0; it < RM_ITERS; ++it) {
+  for (int it = 0; it < ITERS; ++it) {
     const int c = (it * blockDim.x + threadIdx.x) * 8;
     if (c < hidden) {
       float w[8];
@@ -160,12 +175,20 @@ JV_EXPORT int jv_rmsnorm(float* h, const void* delta, int delta_dtype, const int
                        ((uintptr_t)y % 16) == 0;
   if (hidden % 8 == 0 && hidden <= 1024 * 8 * RM_ITERS && aligned) {
     const int vecs = hidden / 8;
-    int iters = (vecs + 511) / 512;                 // up to 512 threads, then more passes per thread
+    int iters = vecs <= 640 ? 1 : (vecs + 511) / 512;     // up to 640 threads, then more passes per thread
     if (iters > RM_ITERS) iters = RM_ITERS;
     int vthreads = ((vecs + iters - 1) / iters + 31) / 32 * 32;
     if (vthreads > 1024) vthreads = 1024;
+    if (iters == 1 && parts > 1 && n_out <= 256)
+      JV_DISPATCH_DTYPE(out_dtype, TY, JV_DISPATCH_DTYPE(weight_dtype, TW, JV_DISPATCH_DTYPE(delta_dtype, TD,
+          return jv_launch(rmsnorm_vec_kernel<TD, TW, TY, 1, 8>, dim3(n_out), dim3(vthreads), 0, stream,
+                           h, (const TD*)delta, rows, (const TW*)weight, (TY*)y, hidden, eps, n_total, status, parts, part_stride))));
+    if (iters == 1)
+      JV_DISPATCH_DTYPE(out_dtype, TY, JV_DISPATCH_DTYPE(weight_dtype, TW, JV_DISPATCH_DTYPE(delta_dtype, TD,
+          return jv_launch(rmsnorm_vec_kernel<TD, TW, TY, 1, 1>, dim3(n_out), dim3(vthreads), 0, stream,
+                           h, (const TD*)delta, rows, (const TW*)weight, (TY*)y, hidden, eps, n_total, status, parts, part_stride))));
     JV_DISPATCH_DTYPE(out_dtype, TY, JV_DISPATCH_DTYPE(weight_dtype, TW, JV_DISPATCH_DTYPE(delta_dtype, TD,
-        return jv_launch(rmsnorm_vec_kernel<TD, TW, TY>, dim3(n_out), dim3(vthreads), 0, stream,
+        return jv_launch(rmsnorm_vec_kernel<TD, TW, TY, RM_ITERS, 1>, dim3(n_out), dim3(vthreads), 0, stream,
                          h, (const TD*)delta, rows, (const TW*)weight, (TY*)y, hidden, eps, n_total, status, parts, part_stride))));
     return JV_ERR_UNSUPPORTED;
   }
