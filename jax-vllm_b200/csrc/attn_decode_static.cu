@@ -17,8 +17,8 @@ constexpr size_t SCRATCH_FLOATS = SCRATCH_WORDS - COUNTER_WORDS;     // rest: pa
 // name is only a handle for cudaGetSymbolAddress, never a device address.
 static __device__ __align__(256) float g_static_scratch[SCRATCH_WORDS];
 
-constexpr int MAX_DEVICES = 64;
-float* g_scratch_ptr[MAX_DEVICES] = {};   // per device, filled by its first call
+constexpr int MAX_DEVICES = JV_MAX_DEVICES;
+float* g_scratch_ptr[MAX_DEVICES] = {};   // per device, filled by its first call (two threads racing there store the same value)
 
 // The device address of the scratch array on the current device; null if it cannot be had.
 float* scratch_on_current_device() {
@@ -50,6 +50,10 @@ extern "C" __attribute__((visibility("default"))) int jv_attn_decode_static(
   if (n_work == 0) return JV_OK;
   if (n_work < 0 || n_splits < 1 || split_size < 1 || n_q_heads < 1) return JV_ERR_UNSUPPORTED;
   if (n_kv_heads < 1 || n_q_heads % n_kv_heads != 0) return JV_ERR_UNSUPPORTED;
+  // what jv_attn_mma would refuse is refused here, before anything is enqueued on the stream
+  if (!jv_attn_mma_supports(head_dim) || (q_stride % 8) || (out_stride % 2) || ((uintptr_t)q % 16) ||
+      ((uintptr_t)k_cache % 16) || ((uintptr_t)v_cache % 16))
+    return JV_ERR_UNSUPPORTED;
   const long long need = jv_attn_decode_static_scratch_floats(n_work, n_q_heads, n_splits, head_dim);
   const int G = n_q_heads / n_kv_heads;
   const long long n_counters = (long long)n_work * n_kv_heads * ((G + 15) / 16);

@@ -30,6 +30,8 @@
 // Restrictions (the caller falls back to the mma.sync kernel): bfloat16, head size 128, no window, at most
 // 16 query heads per kv head, page size a power of two from 8 to 128, at most 512 requests.
 #include "common.cuh"
+#include "mbarrier.cuh"
+#include "qk_prepare.cuh"
 
 #include <cuda.h>
 #include <cudaTypedefs.h>
@@ -46,7 +48,6 @@ constexpr int STAGES = 3;
 constexpr int THREADS = 256;                      // warps: keys producer, mma issuer, 4 x softmax, values producer, query producer
 constexpr int TMEM_COLS = 64;                    // S^T buffers at columns 0 and 16, O^T buffers at 32 and 48
 constexpr int MAX_WORK = 512;                    // requests in one launch
-constexpr long long WAIT_CYCLES = 2000000000LL;
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float LAZY = 8.f;
 
@@ -67,29 +68,6 @@ struct Params {
   __nv_bfloat16* k_cache; __nv_bfloat16* v_cache;
 };
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, int bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint64_t* bar, int parity) {
-  uint32_t done;
-  asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
-               : "=r"(done) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-  return done != 0;
-}
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, int parity) {
-  if (mbar_try(bar, parity)) return true;
-  const long long deadline = clock64() + WAIT_CYCLES;
-  while (!mbar_try(bar, parity))
-    if (clock64() > deadline) return false;
-  return true;
-}
 __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int x, int y, int z, uint64_t* bar) {
   asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];\n"
                ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar)) : "memory");
@@ -117,9 +95,6 @@ __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t a_desc, uint64_t 
   asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
                "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
                ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar)) : "memory");
 }
 // One row (TMEM lane) per thread, N consecutive 32-bit columns.
 template <int N>
@@ -179,8 +154,12 @@ __device__ __forceinline__ bool softmax_barrier_or(bool flag) {
 struct Shared {
   uint64_t q_full[2], q_empty[2], k_full[STAGES], k_empty[STAGES], v_full[STAGES], v_empty[STAGES];
   uint64_t s_full[2], p_full[2], o_done[2], o_free[2];
+  uint64_t drain;                // used only after a wait ran out (see the tear-down)
   uint32_t tmem_base;
   int is_last;
+  int failed;                    // a role gave up on a wait
+  int armed[2][STAGES];          // parity of the phase that the key (0) / value (1) producer armed last on a stage; -1: never
+  int armed_q[2];                // the same for the two query buffers
   float m_ref[NH];               // reference maxima of the running segment (raw score units)
   float alpha[NH];
   float red[4][NH];              // per-warp partial maxima / sums
@@ -232,7 +211,11 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_tcgen05_kernel(const _
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&sh->k_full[s], 1); mbar_init(&sh->k_empty[s], 1);
       mbar_init(&sh->v_full[s], 1); mbar_init(&sh->v_empty[s], 1);
+      sh->armed[0][s] = sh->armed[1][s] = -1;
     }
+    mbar_init(&sh->drain, 1);
+    sh->failed = 0;
+    sh->armed_q[0] = sh->armed_q[1] = -1;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   // zeros where no copy will write: the unused rows of Q (heads G..15) and of P^T, in both buffers of each
@@ -337,7 +320,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_tcgen05_kernel(const _
       bool ok = true;
       if (lane == 0) {
         ok = mbar_wait(empty, ph ^ 1);
-        if (ok) mbar_expect_tx(full, n_pages * P * 128 * 2);
+        if (ok) { sh->armed[which][s] = ph; mbar_expect_tx(full, n_pages * P * 128 * 2); }
       }
       ok = __shfl_sync(0xffffffffu, ok, 0);    // also orders the announcement before the copies
       if (ok && page >= 0) {                   // lane l starts the two boxes of page l
@@ -358,7 +341,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_tcgen05_kernel(const _
       pages = pages_next;
       c = n;
     }
-    if (!ok && lane == 0) atomicOr(p.status, JV_STATUS_WAIT_EXPIRED);
+    if (!ok && lane == 0) { atomicOr(p.status, JV_STATUS_WAIT_EXPIRED); sh->failed = 1; }
   } else if (warp == 7) {
     // ------------------------------------------------------------------ query producer: once per segment
     if constexpr (!FUSED) {
@@ -371,6 +354,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_tcgen05_kernel(const _
             const int sp = c.seg & 1;
             if (c.seg >= 2) ok = mbar_wait(&sh->q_empty[sp], ((c.seg >> 1) - 1) & 1);
             if (ok) {
+              sh->armed_q[sp] = (c.seg >> 1) & 1;
               mbar_expect_tx(&sh->q_full[sp], G * 128 * 2);
               tma_load_3d(q_s + sp * SMALL_BYTES, &q_map, 0, c.head * G, sh->token[c.i], &sh->q_full[sp]);
               tma_load_3d(q_s + sp * SMALL_BYTES + SMALL_HALF, &q_map, 64, c.head * G, sh->token[c.i], &sh->q_full[sp]);
@@ -378,7 +362,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_tcgen05_kernel(const _
           }
           advance(c);
         }
-        if (!ok) atomicOr(p.status, JV_STATUS_WAIT_EXPIRED);
+        if (!ok) { atomicOr(p.status, JV_STATUS_WAIT_EXPIRED); sh->failed = 1; }
       }
     } else {
       // The whole warp prepares the segment's queries from q|k|v as the product left it: per-head norm and
@@ -396,18 +380,11 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_tcgen05_kernel(const _
                          float (&out)[4]) {
         const float2 lo = __bfloat1622float2(lo2), hi = __bfloat1622float2(hi2);
         float a[2] = {lo.x, lo.y}, b[2] = {hi.x, hi.y};
-        if (w != nullptr) {
-          float ss = (a[0] * a[0] + b[0] * b[0]) + (a[1] * a[1] + b[1] * b[1]);
-#pragma unroll
-          for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-          const float inv = rsqrtf(ss / (float)D + p.eps);
-#pragma unroll
-          for (int i = 0; i < 2; ++i) { a[i] = a[i] * inv * weight(w, 2 * lane + i); b[i] = b[i] * inv * weight(w, 64 + 2 * lane + i); }
-        }
+        qk_prepare_head<2>(a, b, 2 * lane, D / 2, w != nullptr, p.eps, [&](int i) { return weight(w, i); }, cs, sn);
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
-          out[i] = __bfloat162float(__float2bfloat16_rn(a[i] * cs[i] - b[i] * sn[i]));
-          out[2 + i] = __bfloat162float(__float2bfloat16_rn(b[i] * cs[i] + a[i] * sn[i]));
+          out[i] = __bfloat162float(__float2bfloat16_rn(a[i]));
+          out[2 + i] = __bfloat162float(__float2bfloat16_rn(b[i]));
         }
       };
       Cursor c = c0;
@@ -441,7 +418,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_tcgen05_kernel(const _
           float cs[2] = {1.f, 1.f}, sn[2] = {0.f, 0.f};
           if (p.inv_freq != nullptr) {
 #pragma unroll
-            for (int i = 0; i < 2; ++i) sincosf((float)pos * p.inv_freq[2 * lane + i], &sn[i], &cs[i]);
+            for (int i = 0; i < 2; ++i) qk_rotation(pos, p.inv_freq[2 * lane + i], &sn[i], &cs[i]);
           }
           if (lane == 0 && c.seg >= 2)                               // buffers of the segment before the last one:
             ok = mbar_wait(&sh->q_empty[sp], ((c.seg >> 1) - 1) & 1) &&      // its products have read the queries,
@@ -489,7 +466,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_tcgen05_kernel(const _
         }
         advance(c);
       }
-      if (!ok && lane == 0) atomicOr(p.status, JV_STATUS_WAIT_EXPIRED);
+      if (!ok && lane == 0) { atomicOr(p.status, JV_STATUS_WAIT_EXPIRED); sh->failed = 1; }
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------------- mma issuer
@@ -535,7 +512,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_tcgen05_kernel(const _
         umma_commit(&sh->o_done[t & 1]);
         advance(cp);
       }
-      if (!ok) atomicOr(p.status, JV_STATUS_WAIT_EXPIRED);
+      if (!ok) { atomicOr(p.status, JV_STATUS_WAIT_EXPIRED); sh->failed = 1; }
     }
   } else {
     // ------------------------------------------------------------------ softmax: one key row per thread
@@ -704,6 +681,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_tcgen05_kernel(const _
           }
         } else if (lane == 0) {
           atomicOr(p.status, JV_STATUS_WAIT_EXPIRED);
+          sh->failed = 1;
         }
         if (b_first != b_last) {                // the same in all 128 threads
           // ---- the block that finishes the pair last merges its segments in ascending order of the blocks
@@ -765,6 +743,20 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_tcgen05_kernel(const _
   // ---- tear-down
   TC_FENCE_BEFORE();
   __syncthreads();
+  if (sh->failed) {
+    // a wait ran out: products already issued may still write tensor memory and copies already asked for still land
+    // in this block's shared memory; both get a bounded time to finish before tensor memory is freed and the block ends
+    if (warp == 1 && lane == 0) drain_products_after_failure(&sh->drain);
+    if ((warp == 0 || warp == 6) && lane == 0) {
+      const int which = warp == 6;
+      for (int s = 0; s < STAGES; ++s)
+        if (sh->armed[which][s] >= 0) drain_copies_after_failure(which ? &sh->v_full[s] : &sh->k_full[s], sh->armed[which][s]);
+    }
+    if (warp == 7 && lane == 0)
+      for (int b = 0; b < 2; ++b)
+        if (sh->armed_q[b] >= 0) drain_copies_after_failure(&sh->q_full[b], sh->armed_q[b]);
+    __syncthreads();
+  }
   if (warp == 1) {
     TC_FENCE_AFTER();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
@@ -788,13 +780,12 @@ constexpr size_t SMEM_BYTES = 2 * STAGES * TILE_BYTES + 4 * SMALL_BYTES + sizeof
 template <int GP, bool FUSED>
 int launch(int n_blocks, cudaStream_t stream, const CUtensorMap& q_map, const CUtensorMap& k_map, const CUtensorMap& v_map,
            const Params& p) {
-  static bool ready = false;
-  if (!ready) {
-    if (cudaFuncSetAttribute(attn_decode_tcgen05_kernel<GP, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)SMEM_BYTES) != cudaSuccess)
-      return JV_ERR_UNSUPPORTED;
-    ready = true;
-  }
+  static bool ready[JV_MAX_DEVICES];
+  if (!jv_once_per_device(ready, [&] {
+        return cudaFuncSetAttribute(attn_decode_tcgen05_kernel<GP, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    (int)SMEM_BYTES) == cudaSuccess;
+      }))
+    return JV_ERR_UNSUPPORTED;
   return jv_launch(attn_decode_tcgen05_kernel<GP, FUSED>, dim3(n_blocks), dim3(THREADS), SMEM_BYTES, stream, q_map, k_map, v_map,
                    p);
 }

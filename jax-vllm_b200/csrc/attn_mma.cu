@@ -18,6 +18,7 @@
 // probabilities are rounded to bfloat16 for the second product.  Head sizes 16..128 in the
 // instantiated steps; other sizes are refused (the caller falls back to the CUDA-core kernel).
 #include "common.cuh"
+#include "mbarrier.cuh"
 #include <math.h>
 
 namespace {
@@ -44,9 +45,6 @@ struct Params {
   int* counters;               // decode: one per (work item, kv head, head group), zero between launches
 };
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-  return (uint32_t)__cvta_generic_to_shared(p);
-}
 __device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
   const int n = valid ? 16 : 0;  // 0 bytes read: the 16 bytes are filled with zeros
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_u32(dst)), "l"(src), "r"(n));
@@ -98,28 +96,9 @@ __device__ __forceinline__ void tile_rows(long long* rows, const Params& p, int 
 // ---- mbarrier + bulk-copy (TMA) helpers.  A cache row of one kv head is D contiguous elements, so a
 // 64-key tile is 64 + 64 bulk copies, one per thread, instead of 16-byte copies by the thousand; their
 // completion is counted in bytes on the stage's mbarrier.
-__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect(uint64_t* bar, int bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
 __device__ __forceinline__ void bulk_copy(void* dst, const void* src, int bytes, uint64_t* bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
                ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
-}
-// Waits for phase `parity` of the barrier, at most ~a second; false if it gave up.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, int parity) {
-  for (int spin = 0; spin < (1 << 20); ++spin) {
-    uint32_t done;
-    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
-                 : "=r"(done) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-    if (done) return true;
-  }
-  return false;
 }
 
 // Copies the rows listed by tile_rows into a K tile and a V tile: thread n < 64 the key row n, thread
@@ -135,7 +114,7 @@ __device__ __forceinline__ void issue_tile(__nv_bfloat16* ks, __nv_bfloat16* vs,
   const long long off = rows[n];
   __nv_bfloat16* dst = (is_v ? vs : ks) + n * S;
   if (off >= 0) {
-    mbar_arrive_expect(bar, D * 2);
+    mbar_expect_tx(bar, D * 2);
     bulk_copy(dst, (is_v ? p.v_cache : p.k_cache) + off, D * 2, bar);
   } else {
 #pragma unroll
@@ -299,6 +278,7 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_mma_kernel(const Params 
   cp_async_commit();                      // the queries
   __syncthreads();
   issue_tile<D>(ks, vs, rows[0], p, &bars[0], tid);
+  __syncthreads();                        // rows[0] has been read by all before iteration 0 refills it
 
   // ---- this thread's two rows
   int pos[2];
@@ -423,6 +403,7 @@ __global__ void __launch_bounds__(THREADS) attn_decode_mma_kernel(const Params p
 #pragma unroll
   for (int st = 0; st < DECODE_STAGES - 1; ++st)
     if (st < n_tiles) issue_tile<D>(ks + st * BN * S, vs + st * BN * S, rows[st], p, &bars[st], tid);
+  __syncthreads();                        // rows[0] has been read by all before iteration 0 refills it
 
   // every row is the same token: position pos_q for rows that hold a head, -1 otherwise
   int pos[2];
@@ -562,23 +543,21 @@ template <int D> size_t decode_smem() {
 template <int D>
 int launch(const Params& p, int n_work, bool split, cudaStream_t stream) {
   if (!split) {
-    static bool ready = false;   // set once: the attribute call is kept out of stream captures
+    static bool ready[JV_MAX_DEVICES];
     const size_t smem = prefill_smem<D>();
-    if (!ready) {
-      if (cudaFuncSetAttribute(attn_prefill_mma_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-        return JV_ERR_UNSUPPORTED;
-      ready = true;
-    }
+    if (!jv_once_per_device(ready, [&] {
+          return cudaFuncSetAttribute(attn_prefill_mma_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess;
+        }))
+      return JV_ERR_UNSUPPORTED;
     dim3 grid(n_work, p.n_kv_heads * p.n_head_groups);
     return jv_launch(attn_prefill_mma_kernel<D>, grid, dim3(THREADS), smem, stream, p);
   }
-  static bool ready = false;
+  static bool ready[JV_MAX_DEVICES];
   const size_t smem = decode_smem<D>();
-  if (!ready) {
-    if (cudaFuncSetAttribute(attn_decode_mma_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-      return JV_ERR_UNSUPPORTED;
-    ready = true;
-  }
+  if (!jv_once_per_device(ready, [&] {
+        return cudaFuncSetAttribute(attn_decode_mma_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess;
+      }))
+    return JV_ERR_UNSUPPORTED;
   dim3 grid(n_work, p.n_kv_heads * p.n_head_groups, p.n_splits);
   return jv_launch(attn_decode_mma_kernel<D>, grid, dim3(THREADS), smem, stream, p);
 }

@@ -23,6 +23,7 @@
 // Restrictions (the caller falls back to the mma.sync kernel otherwise): bfloat16, head size 128, no
 // window, HPT up to 16, page size a power of two from 8 to 128.
 #include "common.cuh"
+#include "mbarrier.cuh"
 
 #include <cuda.h>
 #include <cudaTypedefs.h>
@@ -38,7 +39,6 @@ constexpr int THREADS = 352;                     // key producer warp, mma warp,
 constexpr int SOFTMAX_THREADS = 256;
 constexpr int TMEM_COLS = 512;                   // S0: [0,128)  S1: [128,256)  O: [256,384)  P0: [384,448)  P1: [448,512)
 constexpr int TMEM_O = 256, TMEM_P = 384;        // a column of P holds two bfloat16: keys 2c and 2c+1
-constexpr long long WAIT_CYCLES = 2000000000LL;
 constexpr float LOG2E = 1.4426950408889634f;
 
 struct Params {
@@ -50,29 +50,6 @@ struct Params {
   int* status;
 };
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, int bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint64_t* bar, int parity) {
-  uint32_t done;
-  asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
-               : "=r"(done) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-  return done != 0;
-}
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, int parity) {
-  if (mbar_try(bar, parity)) return true;          // the usual case costs no reading of the clock
-  const long long deadline = clock64() + WAIT_CYCLES;
-  while (!mbar_try(bar, parity))
-    if (clock64() > deadline) return false;
-  return true;
-}
 __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int x, int y, int z, uint64_t* bar) {
   asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];\n"
                ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar)) : "memory");
@@ -112,9 +89,6 @@ __device__ __forceinline__ void umma_a_tmem(uint32_t tmem_d, uint32_t tmem_a, ui
   asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
                "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
                ::"r"(tmem_d), "r"(tmem_a), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
   uint32_t r[32];
@@ -215,7 +189,10 @@ __device__ __forceinline__ void pair_barrier(int quad) { asm volatile("bar.sync 
 struct Shared {
   uint64_t q_full, k_full[KV_STAGES], k_empty[KV_STAGES], v_full[KV_STAGES], v_empty[KV_STAGES];
   uint64_t s_full[2], p_full[2], o_done[2];
+  uint64_t drain;               // used only after a wait ran out (see the tear-down)
   uint32_t tmem_base;
+  int failed;                   // a role gave up on a wait
+  int armed[2][KV_STAGES];      // parity of the phase that the key (0) / value (1) producer armed last on a stage; -1: never
   float xch[2][128];            // a row's two softmax threads exchange their maxima (and at the end their sums)
 };
 
@@ -257,6 +234,9 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tcgen05_kernel(const __grid_c
     mbar_init(&sh->s_full[0], 1); mbar_init(&sh->s_full[1], 1);
     mbar_init(&sh->p_full[0], SOFTMAX_THREADS); mbar_init(&sh->p_full[1], SOFTMAX_THREADS);
     mbar_init(&sh->o_done[0], 1); mbar_init(&sh->o_done[1], 1);
+    mbar_init(&sh->drain, 1);
+    sh->failed = 0;
+    for (int s = 0; s < KV_STAGES; ++s) sh->armed[0][s] = sh->armed[1][s] = -1;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   __syncthreads();
@@ -310,7 +290,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tcgen05_kernel(const __grid_c
         const int n_pages = __popc(__ballot_sync(0xffffffffu, pages >= 0));
         if (lane == 0) {
           ok = mbar_wait(&empty_bars[s], ph ^ 1);
-          if (ok) mbar_expect_tx(&full_bars[s], n_pages * P * 128 * 2);
+          if (ok) { sh->armed[which][s] = ph; mbar_expect_tx(&full_bars[s], n_pages * P * 128 * 2); }
         }
         ok = __shfl_sync(0xffffffffu, ok, 0);      // also orders the announcement before the copies
         // lane i issues the two boxes of page i
@@ -320,7 +300,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tcgen05_kernel(const __grid_c
         }
         pages = pages_next;
       }
-      if (!ok && lane == 0) atomicOr(p.status, JV_STATUS_WAIT_EXPIRED);
+      if (!ok && lane == 0) { atomicOr(p.status, JV_STATUS_WAIT_EXPIRED); sh->failed = 1; }
     } else if (warp == 1) {
       // -------------------------------------------------------------- mma issuer
       if (lane == 0) {
@@ -362,7 +342,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tcgen05_kernel(const __grid_c
           umma_commit(&sh->v_empty[s]);
           umma_commit(&sh->o_done[j & 1]);
         }
-        if (!ok) atomicOr(p.status, JV_STATUS_WAIT_EXPIRED);
+        if (!ok) { atomicOr(p.status, JV_STATUS_WAIT_EXPIRED); sh->failed = 1; }
       }
     } else {
       // ----------------------------------------------------------------- softmax
@@ -544,12 +524,24 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tcgen05_kernel(const __grid_c
           }
         }
       }
-      if (!got && lane == 0) atomicOr(p.status, JV_STATUS_WAIT_EXPIRED);
+      if (!got && lane == 0) { atomicOr(p.status, JV_STATUS_WAIT_EXPIRED); sh->failed = 1; }
     }
   }
 
   TC_FENCE_BEFORE();
   __syncthreads();
+  if (sh->failed) {
+    // a wait ran out: products already issued may still write tensor memory and copies already asked for still land
+    // in this block's shared memory; both get a bounded time to finish before tensor memory is freed and the block ends
+    if (warp == 1 && lane == 0) drain_products_after_failure(&sh->drain);
+    if ((warp == 0 || warp == 10) && lane == 0) {
+      const int which = warp == 0 ? 0 : 1;
+      if (which == 0) drain_copies_after_failure(&sh->q_full, 0);
+      for (int s = 0; s < KV_STAGES; ++s)
+        if (sh->armed[which][s] >= 0) drain_copies_after_failure(which ? &sh->v_full[s] : &sh->k_full[s], sh->armed[which][s]);
+    }
+    __syncthreads();
+  }
   if (warp == 1) {
     TC_FENCE_AFTER();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
@@ -624,11 +616,10 @@ JV_EXPORT int jv_attn_tcgen05(const void* q, int q_stride, int n_tokens, void* o
   p.page_size = page_size; p.num_pages = num_pages; p.hpt = G; p.tokens_per_tile = ROWS / G;
   p.scale_log2 = scale * LOG2E; p.status = status;
   constexpr size_t smem = TILE_BYTES * (1 + 2 * KV_STAGES) + sizeof(Shared) + 1024;
-  static bool ready = false;
-  if (!ready) {
-    if (cudaFuncSetAttribute(attn_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-      return JV_ERR_UNSUPPORTED;
-    ready = true;
-  }
+  static bool ready[JV_MAX_DEVICES];
+  if (!jv_once_per_device(ready, [&] {
+        return cudaFuncSetAttribute(attn_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess;
+      }))
+    return JV_ERR_UNSUPPORTED;
   return jv_launch(attn_tcgen05_kernel, dim3(n_work, n_kv_heads), dim3(THREADS), smem, stream, q_map, k_map, v_map, out_map, p);
 }

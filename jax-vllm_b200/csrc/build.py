@@ -28,7 +28,7 @@ from pathlib import Path
 SRC_DIR = Path(__file__).resolve().parent
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--shared", "-Xcompiler", "-fPIC"]
-HEADERS = ["common.cuh"]
+HEADERS = sorted(p.name for p in SRC_DIR.glob("*.cuh"))     # every shared header counts for every hash
 # further files that a source includes (they count for its hash)
 DEPENDS = {"attn_decode_static": ["attn_mma.cu", "attn_decode_static.h"]}
 

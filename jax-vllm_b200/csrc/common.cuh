@@ -104,6 +104,21 @@ static inline int jv_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, siz
   return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...) == cudaSuccess ? JV_OK : JV_ERR_LAUNCH;
 }
 
+// One-time set-up per device (function attributes are per device): runs `setup` the first time it is reached
+// with a given device current; false if the device cannot be told or `setup` returns false.  Launchers call it
+// before their first launch, which keeps the attribute calls out of stream captures.
+#define JV_MAX_DEVICES 64
+template <typename F>
+static inline bool jv_once_per_device(bool (&done)[JV_MAX_DEVICES], F&& setup) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= JV_MAX_DEVICES) return false;
+  if (!done[dev]) {
+    if (!setup()) return false;
+    done[dev] = true;
+  }
+  return true;
+}
+
 static inline int jv_check_launch() {
   return cudaGetLastError() == cudaSuccess ? JV_OK : JV_ERR_LAUNCH;
 }

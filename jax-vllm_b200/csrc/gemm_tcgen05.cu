@@ -17,6 +17,7 @@
 // Every wait on an mbarrier is bounded by a clock deadline; a wait that runs out sets a bit in the
 // status word and the block goes to its tear-down (TMEM is freed) instead of spinning.
 #include "common.cuh"
+#include "mbarrier.cuh"
 
 #include <cuda.h>
 #include <cudaTypedefs.h>
@@ -27,31 +28,10 @@ constexpr int BM = 128, BN = 256, BK = 64, UMMA_K = 16, STAGES = 4;
 constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int TMEM_COLS = 512;
 constexpr int THREADS = 192;
-constexpr long long WAIT_CYCLES = 2000000000LL;   // about a second
 
 enum : int { EPI_BF16 = 0, EPI_F32 = 1, EPI_SWIGLU = 2 };
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
-__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, int bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, int parity) {
-  const long long deadline = clock64() + WAIT_CYCLES;
-  while (true) {
-    uint32_t done;
-    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
-                 : "=r"(done) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-    if (done) return true;
-    if (clock64() > deadline) return false;
-  }
-}
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
   asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
                ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
@@ -76,9 +56,6 @@ __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t a_desc, uint64_t 
                "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
                ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(IDESC), "r"(accumulate) : "memory");
 }
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar)) : "memory");
-}
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
   uint32_t r[32];
   asm volatile(
@@ -96,8 +73,10 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
 
 struct Shared {
   uint64_t full[STAGES], empty[STAGES], acc_full[2], acc_empty[2];
+  uint64_t drain;                 // used only after a wait ran out (see the tear-down)
   uint32_t tmem_base;
   int failed;
+  int armed[STAGES];              // parity of the phase that the producer armed last on full[s]; -1: never
 };
 
 template <int EPI>
@@ -115,7 +94,9 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tcgen05_kernel(const __grid_c
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&sh->full[s], 1); mbar_init(&sh->empty[s], 1); }
     for (int a = 0; a < 2; ++a) { mbar_init(&sh->acc_full[a], 1); mbar_init(&sh->acc_empty[a], 128); }
+    mbar_init(&sh->drain, 1);
     sh->failed = 0;
+    for (int s = 0; s < STAGES; ++s) sh->armed[s] = -1;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   if (warp == 1) {   // TMEM: all 512 columns (one block per SM)
@@ -136,6 +117,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tcgen05_kernel(const __grid_c
         const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
         for (int kb = 0; kb < k_blocks; ++kb) {
           if (!mbar_wait(&sh->empty[s], phase ^ 1)) { ok = false; break; }
+          sh->armed[s] = phase;
           mbar_expect_tx(&sh->full[s], STAGE_BYTES);
           tma_load_2d(tiles + s * STAGE_BYTES, &a_map, kb * BK, m0, &sh->full[s]);
           tma_load_2d(tiles + s * STAGE_BYTES + A_BYTES, &b_map, kb * BK, n0, &sh->full[s]);
@@ -250,6 +232,15 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tcgen05_kernel(const __grid_c
   // ---- tear-down: everybody is done with TMEM (or gave up); the allocating warp frees it
   asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
   __syncthreads();
+  if (sh->failed) {
+    // a wait ran out: products already issued may still write tensor memory and copies already asked for still land
+    // in this block's shared memory; both get a bounded time to finish before tensor memory is freed and the block ends
+    if (warp == 1 && lane == 0) drain_products_after_failure(&sh->drain);
+    if (warp == 0 && lane == 0)
+      for (int s = 0; s < STAGES; ++s)
+        if (sh->armed[s] >= 0) drain_copies_after_failure(&sh->full[s], sh->armed[s]);
+    __syncthreads();
+  }
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
@@ -285,16 +276,20 @@ template <int EPI>
 int launch(const CUtensorMap& a, const CUtensorMap& b, void* C, int ldc, int M, int N, int K, int* status,
            cudaStream_t stream) {
   constexpr size_t smem = STAGES * STAGE_BYTES + sizeof(Shared) + 1024;
-  static bool ready = false;
-  static int sms = 148;
-  if (!ready) {
-    if (cudaFuncSetAttribute(gemm_tcgen05_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-      return JV_ERR_UNSUPPORTED;
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
-      sms = 148;
-    ready = true;
-  }
+  static bool ready[JV_MAX_DEVICES];
+  static int sm_count[JV_MAX_DEVICES];
+  int dev = 0;
+  if (!jv_once_per_device(ready, [&] {
+        int d = 0, n = 0;
+        if (cudaFuncSetAttribute(gemm_tcgen05_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
+            cudaGetDevice(&d) != cudaSuccess)
+          return false;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, d) != cudaSuccess || n <= 0) n = 148;
+        sm_count[d] = n;
+        return true;
+      }) || cudaGetDevice(&dev) != cudaSuccess)
+    return JV_ERR_UNSUPPORTED;
+  const int sms = sm_count[dev];
   const int n_tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   const int blocks = n_tiles < sms ? n_tiles : sms;
   gemm_tcgen05_kernel<EPI><<<blocks, THREADS, smem, stream>>>(a, b, C, ldc, M, N, K, status);

@@ -238,13 +238,12 @@ int launch(const void* X, int ldx, const void* W, int ldw, void* Y, int ldy, int
   const __nv_bfloat16* x = (const __nv_bfloat16*)X;
   const __nv_bfloat16* w = (const __nv_bfloat16*)W;
   TOut* y = (TOut*)Y;
-  static bool ready = false;   // set once: the attribute calls are kept out of stream captures
-  if (!ready) {
-    if (cudaFuncSetAttribute(skinny_kernel<1, TOut>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes<1>()) != cudaSuccess ||
-        cudaFuncSetAttribute(skinny_kernel<2, TOut>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes<2>()) != cudaSuccess)
-      return JV_ERR_UNSUPPORTED;
-    ready = true;
-  }
+  static bool ready[JV_MAX_DEVICES];
+  if (!jv_once_per_device(ready, [&] {
+        return cudaFuncSetAttribute(skinny_kernel<1, TOut>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes<1>()) == cudaSuccess &&
+               cudaFuncSetAttribute(skinny_kernel<2, TOut>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes<2>()) == cudaSuccess;
+      }))
+    return JV_ERR_UNSUPPORTED;
   if (M <= 8)
     return jv_launch(skinny_kernel<1, TOut>, dim3(blocks), dim3(WARPS * 32), smem_bytes<1>(), stream, x, ldx, w, ldw, y,
                      ldy, M, N, K, n_strips, splits, per_warp, parts);

@@ -20,6 +20,7 @@
 // mbarrier is bounded by a clock deadline; a wait that runs out sets a bit in the status word and the block
 // goes to its tear-down (tensor memory is freed) instead of spinning.
 #include "common.cuh"
+#include "mbarrier.cuh"
 
 #include <cuda.h>
 #include <cudaTypedefs.h>
@@ -32,31 +33,7 @@ constexpr int THREADS = 192;
 constexpr int MAX_ROWS = 128;
 constexpr int SMEM_TILES = 192 * 1024;            // for the stages; 3 to 5 of them depending on the rows of x
 constexpr int MAX_STAGES = 8;
-constexpr long long WAIT_CYCLES = 2000000000LL;   // about a second
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, int bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint64_t* bar, int parity) {
-  uint32_t done;
-  asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
-               : "=r"(done) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-  return done != 0;
-}
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, int parity) {
-  if (mbar_try(bar, parity)) return true;          // the usual case costs no reading of the clock
-  const long long deadline = clock64() + WAIT_CYCLES;
-  while (!mbar_try(bar, parity))
-    if (clock64() > deadline) return false;
-  return true;
-}
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
   asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
                ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
@@ -72,9 +49,6 @@ __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t a_desc, uint64_t 
                "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
                ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar)) : "memory");
-}
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
   uint32_t r[16];
   asm volatile(
@@ -89,7 +63,10 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
 
 struct Shared {
   uint64_t full[MAX_STAGES], empty[MAX_STAGES], acc_full[2], acc_empty[2];
+  uint64_t drain;                 // used only after a wait ran out (see the tear-down)
   uint32_t tmem_base;
+  int failed;                     // a role gave up on a wait
+  int armed[MAX_STAGES];          // parity of the phase that the producer armed last on full[s]; -1: never
 };
 
 struct Params {
@@ -113,6 +90,9 @@ __global__ void __launch_bounds__(THREADS, 1) linear_stream_kernel(const __grid_
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) { mbar_init(&sh->full[s], 1); mbar_init(&sh->empty[s], 1); }
     for (int a = 0; a < 2; ++a) { mbar_init(&sh->acc_full[a], 1); mbar_init(&sh->acc_empty[a], 128); }
+    mbar_init(&sh->drain, 1);
+    sh->failed = 0;
+    for (int s = 0; s < MAX_STAGES; ++s) sh->armed[s] = -1;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   if (warp == 1) {
@@ -159,6 +139,7 @@ __global__ void __launch_bounds__(THREADS, 1) linear_stream_kernel(const __grid_
       Cursor ahead = it;
       int n_ahead = 0;
       for (; n_ahead < p.stages && ahead.u < n_units; ++n_ahead, advance(ahead)) {
+        sh->armed[n_ahead] = 0;
         mbar_expect_tx(&sh->full[n_ahead], W_BYTES + x_bytes);
         load_w(n_ahead, ahead.c, ahead.n0);
       }
@@ -169,12 +150,13 @@ __global__ void __launch_bounds__(THREADS, 1) linear_stream_kernel(const __grid_
       bool ok = true;
       for (; it.u < n_units && ok; advance(it)) {
         if (!mbar_wait(&sh->empty[s], phase ^ 1)) { ok = false; break; }
+        sh->armed[s] = phase;
         mbar_expect_tx(&sh->full[s], W_BYTES + x_bytes);
         load_w(s, it.c, it.n0);
         load_x(s, it.c);
         if (++s == p.stages) { s = 0; phase ^= 1; }
       }
-      if (!ok) atomicOr(p.status, JV_STATUS_WAIT_EXPIRED);
+      if (!ok) { atomicOr(p.status, JV_STATUS_WAIT_EXPIRED); sh->failed = 1; }
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------------- mma issuer
@@ -206,7 +188,7 @@ __global__ void __launch_bounds__(THREADS, 1) linear_stream_kernel(const __grid_
         }
         if (ok) umma_commit(&sh->acc_full[acc]);
       }
-      if (!ok) atomicOr(p.status, JV_STATUS_WAIT_EXPIRED);
+      if (!ok) { atomicOr(p.status, JV_STATUS_WAIT_EXPIRED); sh->failed = 1; }
     }
   } else {
     // ------------------------------------------------------------------ epilogue
@@ -247,12 +229,21 @@ __global__ void __launch_bounds__(THREADS, 1) linear_stream_kernel(const __grid_
       asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
       mbar_arrive(&sh->acc_empty[acc]);
     }
-    if (!ok && lane == 0) atomicOr(p.status, JV_STATUS_WAIT_EXPIRED);
+    if (!ok && lane == 0) { atomicOr(p.status, JV_STATUS_WAIT_EXPIRED); sh->failed = 1; }
   }
 
   // ---- tear-down: everybody is done with tensor memory (or gave up); the allocating warp frees it
   asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
   __syncthreads();
+  if (sh->failed) {
+    // a wait ran out: products already issued may still write tensor memory and copies already asked for still land
+    // in this block's shared memory; both get a bounded time to finish before tensor memory is freed and the block ends
+    if (warp == 1 && lane == 0) drain_products_after_failure(&sh->drain);
+    if (warp == 0 && lane == 0)
+      for (int s = 0; s < p.stages; ++s)
+        if (sh->armed[s] >= 0) drain_copies_after_failure(&sh->full[s], sh->armed[s]);
+    __syncthreads();
+  }
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(p.tmem_cols) : "memory");
@@ -352,12 +343,11 @@ JV_EXPORT int jv_linear_stream(const void* X, int ldx, const void* W, int ldw, v
   CUtensorMap w_map, x_map;
   if (!make_map(&w_map, W, N, K, ldw, BM) || !make_map(&x_map, X, M, K, ldx, p.rows16)) return JV_ERR_UNSUPPORTED;
   constexpr size_t smem = SMEM_TILES + sizeof(Shared) + 1024;
-  static bool ready = false;   // set once: the attribute call is kept out of stream captures
-  if (!ready) {
-    if (cudaFuncSetAttribute(linear_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-      return JV_ERR_UNSUPPORTED;
-    ready = true;
-  }
+  static bool ready[JV_MAX_DEVICES];
+  if (!jv_once_per_device(ready, [&] {
+        return cudaFuncSetAttribute(linear_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess;
+      }))
+    return JV_ERR_UNSUPPORTED;
   const long long units = (long long)p.n_strips * splits;
   const int sms = multiprocessors();
   const int blocks = units < sms ? (int)units : sms;

@@ -13,6 +13,7 @@
 //       page = block_table[entry, position / page_size], slot = position % page_size,
 //       cache[page, slot, kv_head, :].
 #include "common.cuh"
+#include "qk_prepare.cuh"
 
 template <typename T, typename TW>
 __global__ void rope_kv_kernel(T* __restrict__ qkv, int row_stride, const int* __restrict__ positions,
@@ -66,7 +67,7 @@ __global__ void rope_kv_kernel(T* __restrict__ qkv, int row_stride, const int* _
   }
   if (w != nullptr) {
     ss = warp_sum(ss);
-    const float inv = rsqrtf(ss / (float)head_dim + eps);
+    const float inv = qk_norm_factor(ss, head_dim, eps);
     for (int d = lane; d < head_dim; d += 32) buf[d] = buf[d] * inv * to_f32(w[d]);
   }
   __syncwarp();
@@ -75,11 +76,10 @@ __global__ void rope_kv_kernel(T* __restrict__ qkv, int row_stride, const int* _
     float v = buf[d];
     if (d < rot_dim) {
       const int j = d < half ? d : d - half;
-      const float ang = (float)pos * inv_freq[j];
-      float sn, cs;
-      sincosf(ang, &sn, &cs);
-      const float other = d < half ? -buf[d + half] : buf[d - half];
-      v = v * cs + other * sn;
+      float sn, cs, first, second;
+      qk_rotation(pos, inv_freq[j], &sn, &cs);
+      qk_rotate_pair(buf[j], buf[j + half], cs, sn, &first, &second);
+      v = d < half ? first : second;
     }
     dst[d] = from_f32<T>(v);
   }
@@ -131,29 +131,17 @@ __global__ void rope_kv_fast_kernel(T* __restrict__ qkv, int row_stride, const i
     *reinterpret_cast<V*>(dst + HALF + d0) = hi;
     return;
   }
-  float a[E], b[E], ss = 0.f;
+  float a[E], b[E], cs[E], sn[E];
 #pragma unroll
   for (int i = 0; i < E; ++i) {
     a[i] = to_f32(lo.v[i]); b[i] = to_f32(hi.v[i]);
-    ss += a[i] * a[i] + b[i] * b[i];
+    sn[i] = 0.f; cs[i] = 1.f;
+    if (inv_freq != nullptr) qk_rotation(pos, inv_freq[d0 + i], &sn[i], &cs[i]);
   }
   const TW* w = is_q ? q_norm_w : k_norm_w;
-  if (w != nullptr) {
-    ss = warp_sum(ss);
-    const float inv = rsqrtf(ss / (float)D + eps);
+  qk_prepare_head<E>(a, b, d0, HALF, w != nullptr, eps, [&](int i) { return to_f32(w[i]); }, cs, sn);
 #pragma unroll
-    for (int i = 0; i < E; ++i) {
-      a[i] = a[i] * inv * to_f32(w[d0 + i]);
-      b[i] = b[i] * inv * to_f32(w[HALF + d0 + i]);
-    }
-  }
-#pragma unroll
-  for (int i = 0; i < E; ++i) {
-    float sn = 0.f, cs = 1.f;
-    if (inv_freq != nullptr) sincosf((float)pos * inv_freq[d0 + i], &sn, &cs);
-    lo.v[i] = from_f32<T>(a[i] * cs - b[i] * sn);
-    hi.v[i] = from_f32<T>(b[i] * cs + a[i] * sn);
-  }
+  for (int i = 0; i < E; ++i) { lo.v[i] = from_f32<T>(a[i]); hi.v[i] = from_f32<T>(b[i]); }
   *reinterpret_cast<V*>(dst + d0) = lo;
   *reinterpret_cast<V*>(dst + HALF + d0) = hi;
 }
@@ -176,7 +164,7 @@ __global__ void __launch_bounds__(256) rope_kv_token_kernel(
   const int pos = positions[n];
   for (int i = threadIdx.x; i < HALF; i += blockDim.x) {
     float sn = 0.f, cs = 1.f;
-    if (inv_freq != nullptr) sincosf((float)pos * inv_freq[i], &sn, &cs);
+    if (inv_freq != nullptr) qk_rotation(pos, inv_freq[i], &sn, &cs);
     cs_s[i] = cs; sn_s[i] = sn;
   }
   size_t slot = 0;                       // the token's row in the cache, in units of heads
@@ -208,28 +196,16 @@ __global__ void __launch_bounds__(256) rope_kv_token_kernel(
       *reinterpret_cast<V*>(dst + HALF + d0) = hi;
       continue;
     }
-    float a[E], b[E], ss = 0.f;
+    float a[E], b[E], cs[E], sn[E];
 #pragma unroll
     for (int i = 0; i < E; ++i) {
       a[i] = to_f32(lo.v[i]); b[i] = to_f32(hi.v[i]);
-      ss += a[i] * a[i] + b[i] * b[i];
+      cs[i] = cs_s[d0 + i]; sn[i] = sn_s[d0 + i];
     }
     const TW* w = is_q ? q_norm_w : k_norm_w;
-    if (w != nullptr) {
-      ss = warp_sum(ss);
-      const float inv = rsqrtf(ss / (float)D + eps);
+    qk_prepare_head<E>(a, b, d0, HALF, w != nullptr, eps, [&](int i) { return to_f32(w[i]); }, cs, sn);
 #pragma unroll
-      for (int i = 0; i < E; ++i) {
-        a[i] = a[i] * inv * to_f32(w[d0 + i]);
-        b[i] = b[i] * inv * to_f32(w[HALF + d0 + i]);
-      }
-    }
-#pragma unroll
-    for (int i = 0; i < E; ++i) {
-      const float cs = cs_s[d0 + i], sn = sn_s[d0 + i];
-      lo.v[i] = from_f32<T>(a[i] * cs - b[i] * sn);
-      hi.v[i] = from_f32<T>(b[i] * cs + a[i] * sn);
-    }
+    for (int i = 0; i < E; ++i) { lo.v[i] = from_f32<T>(a[i]); hi.v[i] = from_f32<T>(b[i]); }
     *reinterpret_cast<V*>(dst + d0) = lo;
     *reinterpret_cast<V*>(dst + HALF + d0) = hi;
   }

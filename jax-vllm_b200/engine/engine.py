@@ -8,10 +8,8 @@ portions together) and returns the events of the tokens it produced.
 
 from __future__ import annotations
 
-import queue
 import threading
 import time
-import traceback
 from typing import Iterator, Optional
 
 import torch
@@ -19,14 +17,11 @@ import torch
 from ..cache import CacheManager
 from ..config import EngineConfig, parse_dtype
 from ..sampling import Sampler
+from .background import EventRouter
 from .batch import StepEntry
 from .request import EngineStats, Request, SamplingParams, StepEvent
 from .runner import Runner
 from .scheduler import Scheduler
-
-_ACTIVE_SLEEP = 0.0001
-_IDLE_SLEEP = 0.001
-_STREAM_POLL = 0.1
 
 
 class Driver:
@@ -46,14 +41,10 @@ class Driver:
                                    self.stats)
         self.sampler = sampler if sampler is not None else Sampler(config.device)
         self.requests: dict[int, Request] = {}
-        self.streams: dict[int, "queue.Queue[StepEvent]"] = {}
-        self.streams_lock = threading.Lock()
         self.id_lock = threading.Lock()
-        self.step_lock = threading.Lock()
+        self.step_lock = threading.Lock()          # the scheduler and the cache are touched under it only
         self.next_id = 0
-        self.stop_event = threading.Event()
-        self.thread: Optional[threading.Thread] = None
-        self.thread_error: Optional[str] = None
+        self.router = EventRouter(lambda: step(self), lambda: has_work(self))
         self.ahead = None                  # the next step's plan, made while the device ran the last one
         self.host_tokens = None            # pinned memory that the sampled tokens come back to
 
@@ -77,7 +68,7 @@ def make_driver(model, max_num_seqs: int = 4, max_model_len: int = 2048, max_pre
 
 
 def add_request(driver: Driver, prompt_ids, sampling: Optional[SamplingParams] = None) -> int:
-    _raise_if_failed(driver)
+    driver.router.raise_if_failed()
     sp = sampling or SamplingParams()
     prompt = [int(t) for t in prompt_ids]
     vocab = driver.model.spec.vocab_size
@@ -88,11 +79,11 @@ def add_request(driver: Driver, prompt_ids, sampling: Optional[SamplingParams] =
         rid = driver.next_id
         driver.next_id += 1
     req = Request(request_id=rid, prompt_ids=prompt, sampling=sp, arrival=time.perf_counter())
-    with driver.streams_lock:
-        driver.streams[rid] = queue.Queue()
+    driver.router.open(rid)
     with driver.step_lock:
         driver.requests[rid] = req
         driver.scheduler.add(req)
+    driver.router.wake()
     return rid
 
 
@@ -102,7 +93,7 @@ def has_work(driver: Driver) -> bool:
 
 def step(driver: Driver) -> list:
     """One scheduler iteration: at most one batch on the device; returns its StepEvents."""
-    _raise_if_failed(driver)
+    driver.router.raise_if_failed()
     with driver.step_lock:
         return _step_locked(driver)
 
@@ -179,68 +170,28 @@ def generate(driver: Driver, prompts, sampling=None) -> list:
         if not step(driver) and not has_work(driver):
             break
     for i in ids:
-        with driver.streams_lock:
-            driver.streams.pop(i, None)
+        driver.router.close(i)
         driver.requests.pop(i, None)
     return [list(r.output_ids) for r in reqs]
 
 
 # --------------------------------------------------------------- streams and thread
 def stream(driver: Driver, request_id: int) -> Iterator[StepEvent]:
-    """Events of one request as the background thread produces them."""
-    _raise_if_failed(driver)
-    with driver.streams_lock:
-        q = driver.streams.get(request_id)
-    if q is None:
-        raise KeyError(f"unknown or already-drained request_id: {request_id}")
-    while True:
-        try:
-            ev = q.get(timeout=_STREAM_POLL)
-        except queue.Empty:
-            _raise_if_failed(driver)
-            if driver.stop_event.is_set() and (driver.thread is None or not driver.thread.is_alive()):
-                raise RuntimeError("engine stopped before request finished")
-            continue
+    """The events of one request, until the one that finishes it.  With the background thread running they come
+    from the thread; without one, the reader steps the engine itself (see engine/background.py)."""
+    driver.router.raise_if_failed()
+    for ev in driver.router.events(request_id):
         yield ev
-        if ev.finished:
-            with driver.streams_lock:
-                driver.streams.pop(request_id, None)
-            driver.requests.pop(request_id, None)
-            return
+    driver.requests.pop(request_id, None)
 
 
 def start(driver: Driver) -> None:
-    if driver.thread is not None and driver.thread.is_alive():
-        return
-    driver.thread_error = None
-    driver.stop_event.clear()
-    driver.thread = threading.Thread(target=_driver_loop, args=(driver,), name="engine", daemon=True)
-    driver.thread.start()
+    """Starts the background thread that steps the engine whenever there is work."""
+    driver.router.start()
 
 
 def stop(driver: Driver, join: bool = True) -> None:
-    driver.stop_event.set()
-    if join and driver.thread is not None:
-        driver.thread.join()
-        driver.thread = None
-
-
-def _driver_loop(driver: Driver) -> None:
-    try:
-        while not driver.stop_event.is_set():
-            events = step(driver)
-            if events:
-                with driver.streams_lock:
-                    for ev in events:
-                        q = driver.streams.get(ev.request_id)
-                        if q is not None:
-                            q.put(ev)
-                continue
-            time.sleep(_ACTIVE_SLEEP if has_work(driver) else _IDLE_SLEEP)
-    except Exception as exc:  # the latch: every later call re-raises (jllm/engine/engine.py:230-233)
-        driver.thread_error = f"{type(exc).__name__}: {exc}"
-        driver.stop_event.set()
-        traceback.print_exc()
+    driver.router.stop(join)
 
 
 def prewarm(driver: Driver) -> float:
@@ -252,8 +203,3 @@ def prewarm(driver: Driver) -> float:
         driver.ahead = None
         driver.runner.warm_up(decode_batches=driver.max_num_seqs)
     return time.perf_counter() - t0
-
-
-def _raise_if_failed(driver: Driver) -> None:
-    if driver.thread_error is not None:
-        raise RuntimeError(f"engine thread failed: {driver.thread_error}")

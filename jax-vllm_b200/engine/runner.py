@@ -46,6 +46,10 @@ class Runner:
         self.graph_warm: set[int] = set()
         self._ahead = None                 # (requests and lengths, graph) of a batch already laid out in the staging buffer
         self.launches_last_step = 0
+        self.graph_replays = 0             # steps that were replayed from a captured graph
+        # a part that reads the batch from the host lists of the step context (not from its device tensors)
+        # would see, in a replay, the lists of the step that was captured: such a model is never captured
+        self.capturable = model.capturable()
         self.device, self.dtype = torch.device(device), dtype
         if self.device.type != "cuda":
             raise RuntimeError("the engine runs on a CUDA device only (there is no CPU path)")
@@ -65,17 +69,18 @@ class Runner:
             return torch.empty((0, self.model.spec.vocab_size), dtype=torch.float32, device=self.device)
         self._ahead = None                 # the staging buffer is about to be written
         with torch.cuda.device(self.device):
-            if self._graphable(entries):
-                logits = self._step_graph(entries)
-            else:
-                ctx = self.builder.build(entries)
-                logits = self.model.forward(ctx, self.layer_caches)
+            with ops.trace_range("step"):
+                if self._graphable(entries):
+                    logits = self._step_graph(entries)
+                else:
+                    ctx = self.builder.build(entries)
+                    logits = self.model.forward(ctx, self.layer_caches)
         self.steps += 1
         return logits
 
     # ----------------------------------------------------------- captured decode steps
     def _graphable(self, entries) -> bool:
-        if not self.cuda_graphs or len(entries) > self.max_graph_batch:
+        if not self.cuda_graphs or not self.capturable or len(entries) > self.max_graph_batch:
             return False
         return all(len(e.tokens) == 1 and tuple(e.want) == (0,) and e.cache.num_tokens < self.max_model_len
                    for e in entries)
@@ -120,6 +125,7 @@ class Runner:
         g.dev.copy_(pinned[:g.layout.total], non_blocking=True)
         b._copied = torch.cuda.Event(); b._copied.record()
         g.graph.replay()
+        self.graph_replays += 1
         ops.launch_count += g.launches
         return g.logits
 
@@ -186,6 +192,7 @@ class Runner:
             g.dev.copy_(pinned[:g.total], non_blocking=True)
             b._copied = torch.cuda.Event(); b._copied.record()
             g.graph.replay()
+            self.graph_replays += 1
             ops.launch_count += g.launches
         self.steps += 1
         return g.out
@@ -221,7 +228,7 @@ class Runner:
         return ops.status_word(self.device)
 
     def clear_status(self) -> None:
-        ops.status_word(self.device).zero_()
+        ops.clear_status(self.device)
 
     def warm_up(self, decode_batches: int = 0) -> None:
         """One two-token portion and one single token through every kernel of the model; then, with CUDA

@@ -51,10 +51,12 @@ class Scheduler:
         if len(prompt_ids) < 1:
             raise ValueError("empty prompt")
         if len(prompt_ids) > self.prompt_limit:
-            raise ValueError(f"prompt too long for max_prefill_len={self.prompt_limit}")
+            raise ValueError(f"the prompt has {len(prompt_ids)} tokens; the longest accepted (max_prefill_len) is "
+                             f"{self.prompt_limit}")
         total = len(prompt_ids) + sampling.max_new_tokens
         if total > self.max_model_len:
-            raise ValueError("prompt+max_new exceeds max_model_len")
+            raise ValueError(f"{len(prompt_ids)} prompt tokens and {sampling.max_new_tokens} new ones make {total}; "
+                             f"max_model_len is {self.max_model_len}")
         pages = -(-total // self.cache.page_size)
         if self.cache.groups and pages > self.cache.num_pages:
             raise ValueError(f"prompt+max_new needs {pages} pages, the pool has {self.cache.num_pages}")

@@ -13,6 +13,7 @@ kernel of this package.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_float, c_int, c_longlong, c_void_p
 
 import torch
@@ -126,13 +127,72 @@ def raise_on_status(value: int) -> None:
         raise KernelError("a kernel met " + "; ".join(msgs) + f" (status {value})")
 
 
+def clear_status(device=None) -> None:
+    """Zeroes the status word and what a kernel that gave up may have left half done: the arrival counters of
+    the split decode attention (a block that leaves on a bounded wait never counts itself, so its row's
+    counter would stay short of the total for every later launch)."""
+    w = status_word(device)
+    w.zero_()
+    buf = _counters.get(w.device.index)
+    if buf is not None:
+        buf.zero_()
+
+
 def check_status(device=None) -> None:
     """Reads the status word (a device synchronisation) and raises if a kernel set it."""
     w = status_word(device)
     v = int(w.item())
     if v:
-        w.zero_()
+        clear_status(device)
         raise_on_status(v)
+
+
+# NVTX ranges around the parts of a step (JAX_VLLM_B200_NVTX=1): a profiler's timeline then shows which kernels belong
+# to which layer and part.  Off by default: `trace_range` then returns one shared object that does nothing.
+TRACE_RANGES = os.environ.get("JAX_VLLM_B200_NVTX", "0") not in ("", "0")
+
+
+class _NoRange:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        return False
+
+
+class _NvtxRange:
+    def __init__(self, name: str):
+        self.name = name
+
+    def __enter__(self):
+        torch.cuda.nvtx.range_push(self.name)
+        return self
+
+    def __exit__(self, *exc):
+        torch.cuda.nvtx.range_pop()
+        return False
+
+
+_NO_RANGE = _NoRange()
+
+
+def trace_range(name: str):
+    """A context manager that brackets what runs inside it with an NVTX range of that name, if ranges are on."""
+    return _NvtxRange(name) if TRACE_RANGES else _NO_RANGE
+
+
+def wait_probe(cycles: int, arrive: bool, device=None) -> tuple:
+    """Runs the bounded wait of the TMA and tcgen05 kernels alone (csrc/wait_probe.cu): one barrier that a thread
+    arrives on (`arrive`) or that nothing ever arrives on, waited for at most `cycles` clocks.  Returns
+    (succeeded, clocks spent).  A wait that ran out leaves its bit in the status word, as in the product kernels:
+    `check_status` raises afterwards."""
+    word = status_word(device)
+    outcome = torch.zeros(2, dtype=torch.int32, device=word.device)
+    f = _fn("wait_probe", "jv_wait_probe", [c_longlong, c_int, c_void_p, c_void_p, c_void_p])
+    with torch.cuda.device(word.device):
+        _check(f(int(cycles), 1 if arrive else 0, word.data_ptr(), outcome.data_ptr(), _stream()), "wait_probe")
+    done, spent = outcome.tolist()
+    return done == 1, spent
 
 
 # ------------------------------------------------------------------------ embedding
@@ -317,15 +377,19 @@ def attn_mma_tokens_per_tile(n_q_heads: int, n_kv_heads: int) -> int:
 
 
 _counters: dict[int, torch.Tensor] = {}
+_counters_outgrown: list = []     # smaller buffers that a captured graph may still point at: never freed
 
 
 def _split_counters(device, n: int) -> torch.Tensor:
     """Zeroed arrival counters for the split decode attention: one buffer per device, kept for
     the life of the process (the kernel leaves the counters zero; launches on one stream follow
     one another, so they can share it)."""
-    idx = torch.device(device).index or 0
+    idx = torch.device(device).index
+    idx = torch.cuda.current_device() if idx is None else idx
     buf = _counters.get(idx)
     if buf is None or buf.numel() < n:
+        if buf is not None:
+            _counters_outgrown.append(buf)
         buf = torch.zeros(max(n, 1 << 16), dtype=torch.int32, device=device)
         _counters[idx] = buf
     return buf

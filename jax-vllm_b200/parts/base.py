@@ -56,6 +56,11 @@ class BuildContext:
 
 class Part:
     kernels: tuple = ()           # csrc sources whose launchers the part calls
+    # Whether the part's work in a step depends on the step's device tensors only.  A step of single tokens is
+    # captured into a CUDA graph once and replayed with new contents in the same device buffers; a part that
+    # reads `StepContext.host_*` (or anything else on the host that changes from step to step) would replay the
+    # captured step's values, so it says `capturable = False` and its model is stepped eagerly.
+    capturable: bool = True
 
     def tensor_specs(self) -> dict:
         return {}
@@ -102,6 +107,8 @@ class StepContext:
     tile_work: dict               # tile class (tokens per tile, least, most+1 new tokens) -> (work [n, 2] (entry, first token), n)
     decode_work: tuple            # (work [n, 2], n) for entries of exactly one token
     max_seq_len: int              # longest start_pos + new tokens in the batch (or the engine's bound, in a graph)
+    # the same lengths, positions and slots as host lists, for parts that loop over entries on the host; a part
+    # that reads them must say `capturable = False`
     host_q_lens: list = field(default_factory=list)
     host_start_pos: list = field(default_factory=list)
     host_slots: list = field(default_factory=list)

@@ -11,6 +11,7 @@ and normalises in one pass over the stream.  A branch output is a tensor [n, hid
 
 from __future__ import annotations
 
+from ..ops import trace_range
 from .base import Part
 from .registry import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, build, register_block
 
@@ -42,10 +43,14 @@ class PreNormBlock(Part):
             part.bind(tensors)
 
     def forward(self, h, delta, step, cache):
-        x = self.mixer_norm.norm(h, delta)
-        a = self.mixer.forward(x, step, cache)
-        x = self.ffn_norm.norm(h, a)
-        return h, self.feed_forward.forward(x, step)
+        with trace_range("mixer_norm"):
+            x = self.mixer_norm.norm(h, delta)
+        with trace_range("mixer"):
+            a = self.mixer.forward(x, step, cache)
+        with trace_range("ffn_norm"):
+            x = self.ffn_norm.norm(h, a)
+        with trace_range("feed_forward"):
+            return h, self.feed_forward.forward(x, step)
 
 
 register_block("pre_norm", PreNormBlock)

@@ -25,6 +25,8 @@ class Model(Part):
         # earlier place at which the layer it names ran.
         self.order = tuple(spec.run_order())
         self.place_cache = []
+        self.place_names = [f"layer {i}" if self.order.count(i) == 1 else f"layer {i} (place {k})"
+                            for k, i in enumerate(self.order)]
         for k, i in enumerate(self.order):
             src = spec.layers[i].cache_from
             if src is None:
@@ -66,6 +68,12 @@ class Model(Part):
                 names.update(part.kernels)
         return sorted(names)
 
+    def capturable(self) -> bool:
+        """Whether a step of this model may be captured into a CUDA graph and replayed: every part reads the
+        batch from the device tensors of the step context only (`Part.capturable`)."""
+        return all(getattr(part, "capturable", True) for layer in self.layers for part in layer.parts()) \
+            and getattr(self.final_norm, "capturable", True)
+
     # ---------------------------------------------------------------------- cache
     def cache_needs(self):
         """Per place in the run order: what the layer there needs to keep, or None (nothing, or
@@ -85,11 +93,15 @@ class Model(Part):
     # ----------------------------------------------------------------------- step
     def forward(self, step, caches) -> torch.Tensor:
         """Logits [n_logit_rows, vocab] float32 for one batch; caches are updated in place."""
-        h = ops.embed_gather(self.embedding, step.token_ids)
+        with ops.trace_range("embedding"):
+            h = ops.embed_gather(self.embedding, step.token_ids)
         delta = None
         for k, i in enumerate(self.order):
-            h, delta = self.layers[i].forward(h, delta, step, caches[self.place_cache[k]])
+            with ops.trace_range(self.place_names[k]):
+                h, delta = self.layers[i].forward(h, delta, step, caches[self.place_cache[k]])
         if step.n_logit_rows == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=h.device)
-        x = self.final_norm.gather(h, delta, step.logit_rows)
-        return ops.linear(x, self.lm_head, torch.float32)
+        with ops.trace_range("final_norm"):
+            x = self.final_norm.gather(h, delta, step.logit_rows)
+        with ops.trace_range("lm_head"):
+            return ops.linear(x, self.lm_head, torch.float32)

@@ -36,6 +36,10 @@ class WeightError(ValueError):
         super().__init__("\n".join(lines))
 
 
+class DamagedFile(ValueError):
+    """A file of the folder is not a whole safetensors file (cut short while it was copied, say)."""
+
+
 _FLOAT16 = (torch.float16, torch.bfloat16)
 _FLOAT32 = (torch.float32, torch.float64)
 _INTS = (torch.int8, torch.uint8, torch.int16, torch.int32, torch.int64, torch.bool)
@@ -66,10 +70,14 @@ def read_index(folder) -> dict[str, tuple[Path, tuple, str]]:
 
     index = {}
     for shard in list_shards(folder):
-        with safe_open(str(shard), framework="pt") as f:
-            for key in f.keys():
-                sl = f.get_slice(key)
-                index[key] = (shard, tuple(sl.get_shape()), sl.get_dtype())
+        try:
+            with safe_open(str(shard), framework="pt") as f:
+                for key in f.keys():
+                    sl = f.get_slice(key)
+                    index[key] = (shard, tuple(sl.get_shape()), sl.get_dtype())
+        except Exception as exc:          # the library's own error type is not part of its documented interface
+            raise DamagedFile(f"{shard} ({shard.stat().st_size} bytes) cannot be read as a safetensors file; it may "
+                              f"have been cut short: {exc}") from exc
     return index
 
 

@@ -1,4 +1,6 @@
-"""Plain, slow, whole-sequence implementation of Qwen3 dense in 32-bit on the CPU.
+"""Plain, slow, whole-sequence implementation of Qwen3 dense in 32-bit (on the CPU, or for
+shapes of real size on the device that its tensors are moved to, with torch's float32
+products and TF32 switched off by the caller).
 
 This is the oracle that the engine is compared with.  It has no cache, no batching
 and no kernels: one function for each part, each written from the formula that the
@@ -64,7 +66,7 @@ def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
 def rope_cos_sin(positions: torch.Tensor, dim: int, theta: float):
     """inv_freq[j] = 1/theta^(2j/dim); angles = pos * inv_freq, repeated twice along
     the last axis (jllm/model/common.py:51-55)."""
-    inv_freq = 1.0 / (theta ** (torch.arange(0, dim, 2, dtype=torch.float32) / dim))
+    inv_freq = (1.0 / (theta ** (torch.arange(0, dim, 2, dtype=torch.float32) / dim))).to(positions.device)
     freqs = positions.to(torch.float32)[:, None] * inv_freq[None, :]
     emb = torch.cat([freqs, freqs], dim=-1)
     return torch.cos(emb), torch.sin(emb)
@@ -102,12 +104,12 @@ def causal_attention(q, k, v, num_heads, num_kv_heads, head_dim, window=None):
     v = v.repeat_interleave(rep, dim=0)
     T = q.shape[1]
     scores = torch.einsum("hqd,hkd->hqk", q, k) * (1.0 / math.sqrt(head_dim))
-    i = torch.arange(T)[:, None]
-    j = torch.arange(T)[None, :]
+    i = torch.arange(T, device=q.device)[:, None]
+    j = torch.arange(T, device=q.device)[None, :]
     visible = j <= i
     if window is not None:
         visible = visible & (j > i - window)
-    scores = torch.where(visible[None], scores, torch.tensor(float("-inf")))
+    scores = scores.masked_fill(~visible[None], float("-inf"))
     probs = torch.softmax(scores, dim=-1)
     return torch.einsum("hqk,hkd->hqd", probs, v)
 
@@ -151,8 +153,9 @@ def decoder_layer(h, w, i, cfg, positions):
 def forward(cfg: dict, w: dict[str, torch.Tensor], token_ids) -> torch.Tensor:
     """Logits [T, vocab] for one whole sequence (jllm/model/common.py:150-170); the
     output matrix is the embedding table when tied (jllm/model/weights.py:142-146)."""
-    ids = torch.as_tensor(list(token_ids), dtype=torch.long)
-    positions = torch.arange(ids.shape[0])
+    dev = w["model.embed_tokens.weight"].device
+    ids = torch.as_tensor(list(token_ids), dtype=torch.long, device=dev)
+    positions = torch.arange(ids.shape[0], device=dev)
     h = embedding(w["model.embed_tokens.weight"], ids)
     for i in range(cfg["num_hidden_layers"]):
         h = decoder_layer(h, w, i, cfg, positions)
@@ -179,9 +182,11 @@ def greedy(cfg, w, prompt, max_new_tokens, eos_id=None) -> list[int]:
 class PlainModel:
     """A model folder read for the plain implementation."""
 
-    def __init__(self, folder, round_to_bf16: bool = False):
-        self.cfg = read_config(folder)
-        self.w = read_weights(folder)
+    def __init__(self, folder=None, round_to_bf16: bool = False, cfg: dict | None = None, weights: dict | None = None):
+        """From a model folder, or from `cfg` (keys as `read_config` returns them) and a dict of float32 tensors
+        by safetensors name, on whatever device they lie."""
+        self.cfg = read_config(folder) if cfg is None else cfg
+        self.w = read_weights(folder) if weights is None else weights
         if round_to_bf16:
             self.w = {k: v.to(torch.bfloat16).to(torch.float32) for k, v in self.w.items()}
 

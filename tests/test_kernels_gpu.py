@@ -719,3 +719,27 @@ def test_temperature_draws_follow_the_host_restatement_and_the_distribution(ops)
     assert torch.equal(again, got)
     other = ops.sample(big, t, seeds + 1, counters).cpu()
     assert (other != got).float().mean().item() > 0.3
+
+
+def test_a_wait_that_nothing_ends_runs_out_is_reported_and_leaves_the_device_usable(ops):
+    """The bounded wait of the TMA and tcgen05 kernels, alone (csrc/wait_probe.cu): with an arrival it succeeds;
+    with none it gives up after its few thousand clocks, the kernel returns, the status word carries the bit and
+    `check_status` raises an error that names the wait; the word and the split attention's arrival counters are
+    clean afterwards and kernels run as before."""
+    ok, _ = ops.wait_probe(20_000, arrive=True)
+    assert ok
+    ops.check_status()
+    counters = ops._split_counters(DEV, 64)
+    counters[:5] = 3                                   # what blocks that left early would leave behind
+    ok, spent = ops.wait_probe(20_000, arrive=False)
+    assert not ok and 20_000 <= spent < 20_000_000
+    with pytest.raises(ops.KernelError, match="bounded wait"):
+        ops.check_status()
+    ops.check_status()                                 # cleared: the next step starts clean
+    assert int(ops._split_counters(DEV, 64).abs().sum()) == 0
+    x = torch.randn(3, 64, device=DEV)
+    w = torch.ones(64, device=DEV)
+    y = ops.rmsnorm(x.clone(), w, 1e-6, torch.float32)
+    torch.testing.assert_close(y, x * torch.rsqrt((x * x).mean(-1, keepdim=True) + 1e-6), atol=1e-5, rtol=1e-5)
+    with pytest.raises(ops.KernelError, match="outside what the kernel handles"):
+        ops.wait_probe(1 << 40, arrive=False)          # never longer than the product's own bound

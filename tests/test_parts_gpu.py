@@ -265,7 +265,10 @@ def register_toy():
 
     class DecayMixer(parts.Part):
         """y_t = s_t * w with s_t = decay * s_{t-1} + x_t: a running sum kept per request in a
-        fixed-size state row, carried from step to step (torch ops: a toy for this test)."""
+        fixed-size state row, carried from step to step (torch ops: a toy for this test).  It loops over the
+        entries on the host, from the host lists of the step context, so it says that it cannot be captured."""
+
+        capturable = False
 
         def __init__(self, spec, prefix, ctx):
             self.spec, self.name, self.ctx = spec, f"{prefix}.decay.weight", ctx
@@ -292,6 +295,31 @@ def register_toy():
             return out
 
     parts.register_mixer("toy_decay", DecayMixer)
+
+    class DecayMixerOnDevice(DecayMixer):
+        """The same recurrence from the device tensors of the step context only (positions, entry of each token,
+        state slots, offsets of the entries), with shapes that depend on the numbers of tokens and entries alone:
+        a step of it can be captured into a CUDA graph and replayed."""
+
+        capturable = True
+
+        def forward(self, x, step, cache):
+            d = self.spec.decay
+            pos, ent = step.positions.long(), step.token_entry.long()
+            slots, start = step.state_slots.long(), step.start_pos.long()
+            xf = x.float()
+            same = ent[:, None] == ent[None, :]
+            lag = (pos[:, None] - pos[None, :]).clamp(min=0).float()
+            weight = torch.where(same & (pos[None, :] <= pos[:, None]), torch.pow(torch.full_like(lag, d), lag),
+                                 torch.zeros_like(lag))
+            carried = cache.state[slots[ent]] * torch.pow(torch.full_like(pos, d, dtype=torch.float32),
+                                                          (pos - start[ent] + 1).float())[:, None]
+            s = weight @ xf + carried
+            last = step.cu_seqlens.long()[1:] - 1
+            cache.state.index_copy_(0, slots, s[last])
+            return (s * self.w).to(x.dtype)
+
+    parts.register_mixer("toy_decay_on_device", DecayMixerOnDevice)
 
 
 def plain_with_toy(w, cfg, toks, toy_layers, decay):
@@ -340,6 +368,44 @@ def test_toy_mixer_with_own_state_registers_builds_and_steps():
     assert (lb[:13] - want_other[7:]).abs().max().item() <= lim
     assert (lb[13] - want[11]).abs().max().item() <= lim
     runner.check_kernels()
+
+
+@pytest.mark.parametrize("kind,replays", [("toy_decay", False), ("toy_decay_on_device", True)])
+def test_toy_mixer_through_the_entry_point_with_captured_graphs(kind, replays):
+    """Two requests decode side by side through `make_driver` with CUDA graphs on.  The toy that reads the
+    host lists of the step says so (`capturable = False`) and its model is stepped eagerly; the toy written on
+    the device tensors is captured and replayed.  Both give the plain toy's greedy tokens."""
+    j, cache, config, engine, parts, weights = pkg()
+    register_toy()
+    spec = spec_b()
+    layers = list(spec.layers)
+    layers[1] = replace(layers[1], mixer=DecaySpec(spec.hidden_size, 0.9, kind=kind))
+    spec = replace(spec, layers=tuple(layers))
+    ctx = parts.BuildContext(dtype=torch.float32, device=DEV, decode_split_size=32)
+    model = parts.Model(spec, ctx)
+    g = torch.Generator().manual_seed(21)
+    w = {}
+    for name, ts in model.tensor_specs().items():
+        z = torch.randn(ts.shape, generator=g)
+        w[name] = (1 + 0.1 * z) if ts.kind == "vector" else z * (1.5 / ts.shape[-1] ** 0.5)
+    model.bind({k: v.to(DEV) for k, v in w.items()})
+    assert model.capturable() is replays
+    cfg = qwen_cfg(TINY_B)
+    prompts = [random_tokens(9, TINY_B["vocab_size"], seed=22), random_tokens(4, TINY_B["vocab_size"], seed=23)]
+    new = 10
+
+    def plain_greedy(prompt):
+        seq = list(prompt)
+        for _ in range(new):
+            seq.append(int(plain_with_toy(w, cfg, seq, {1}, 0.9)[-1].argmax()))
+        return seq[len(prompt):]
+
+    d = engine.make_driver(model, max_num_seqs=2, max_model_len=32, block_size=8, cuda_graphs=True)
+    got = engine.generate(d, prompts, engine.SamplingParams(max_new_tokens=new))
+    assert got == [plain_greedy(p) for p in prompts]
+    assert (d.runner.graph_replays > 0) is replays
+    d.cache.check()
+    assert not d.cache.live
 
 
 # ------------------------------------- a toy feed-forward with routing, defined here

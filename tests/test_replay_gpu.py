@@ -1,7 +1,10 @@
 """Trace replay against the plain implementation: the same requests whole, with the last 32
 tokens one by one, in portions of changing size down to two tokens, and mixed with other
-requests in a pool so small that pages are used again; in 32-bit and in bfloat16; for two
-tiny configurations that differ in every size."""
+requests in a pool so small that pages are used again (with and without reuse of known
+prefixes, eagerly and through the captured decode graph); in 32-bit and in bfloat16; for
+tiny configurations that differ in every size, one of them with the head layout of the
+benchmarked model.  The largest |difference| of every case is recorded and printed at the end
+of the run (tests/conftest.py)."""
 
 import json
 import os
@@ -18,17 +21,23 @@ from tests.util import PAGE_SIZE, TINY, collect, make_folder, portions, prefix_t
 
 pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parent.parent
-LENGTHS = {"a": [70, 45, 100, 33], "b": [90, 38, 64, 51], "c": [200, 70, 300, 130], "d": [61, 40, 83, 35]}
+LENGTHS = {"a": [70, 45, 100, 33], "b": [90, 38, 64, 51], "c": [200, 70, 300, 130], "d": [61, 40, 83, 35],
+           "e": [200, 70, 300, 130]}
+ABSOLUTE_UPTO = 50.0      # logits up to this size are held to 1e-4 absolute in 32-bit
 
 
 def limits(dtype, want: torch.Tensor):
-    """Largest allowed |difference| of logits.  32-bit: 1e-4 relative to the size of the logits
-    (at least 1).  bfloat16: 3 % of the largest logit (8 bits of mantissa through a few layers)."""
-    scale = max(1.0, want.abs().max().item())
-    return (1e-4 if dtype == "float32" else 3e-2) * scale
+    """Largest allowed |difference| of logits.  32-bit: 1e-4 absolute while no logit of the request exceeds
+    ABSOLUTE_UPTO in size (every configuration here: they reach 5 to 12), beyond that 1e-4 * size / ABSOLUTE_UPTO
+    (a float32 of size 50 is spaced 4e-6).  bfloat16: 3 % of the largest logit (8 bits of mantissa through a few
+    layers)."""
+    size = want.abs().max().item()
+    if dtype == "float32":
+        return 1e-4 * max(1.0, size / ABSOLUTE_UPTO)
+    return 3e-2 * max(1.0, size)
 
 
-@pytest.fixture(scope="module", params=["a", "b", "c", "d"])
+@pytest.fixture(scope="module", params=["a", "b", "c", "d", "e"])
 def setup(request, tmp_path_factory):
     tag = request.param
     folder = make_folder(tmp_path_factory.mktemp(f"model_{tag}"), tag, seed=3)
@@ -36,7 +45,7 @@ def setup(request, tmp_path_factory):
     seqs = {f"r{i}": random_tokens(n, TINY[tag]["vocab_size"], seed=10 + i) for i, n in enumerate(LENGTHS[tag])}
     want = {rid: plain.logits(t) for rid, t in seqs.items()}
     assert all(w.abs().max() > 1.0 for w in want.values())     # logits of order one, not a flat model
-    if tag == "c":
+    if tag in ("c", "e"):
         # the product with the gate in its epilogue is taken from 1,024 rows on; these prompts are shorter, so
         # for this configuration the bar is lowered and portions of 17 tokens or more go through it
         from jax_vllm_b200.parts.feed_forward import GatedMLP
@@ -47,28 +56,39 @@ def setup(request, tmp_path_factory):
     yield tag, folder, seqs, want
 
 
-def replay(folder, tag, dtype, steps, out_dir, max_tokens):
+def replay(folder, tag, dtype, steps, out_dir, max_tokens, **switches):
     from jax_vllm_b200.engine.replay import Replayer
 
-    rep = Replayer(folder, dtype, out_dir, max_tokens=max_tokens, page_size=PAGE_SIZE[tag])
+    rep = Replayer(folder, dtype, out_dir, max_tokens=max_tokens, page_size=PAGE_SIZE[tag], **switches)
     rep.run_stream(json.dumps(s) for s in steps)
     rep.cache.check()
     assert not rep.cache.live
+    for s in steps:       # what every step did is on disk beside its logits
+        meta = json.loads((Path(out_dir) / f"{s['step']}.json").read_text())
+        assert meta["step"] == s["step"] and meta["entries"] == len(s["entries"])
     return rep
 
 
-def compare(steps, out_dir, vocab, want, dtype):
+def compare(steps, out_dir, vocab, want, dtype, case=None):
+    """Every written row against the oracle's; returns what was read and the largest |difference|, which is
+    recorded under `case` for the summary at the end of the run."""
+    from tests.conftest import record_worst
+
     got = collect(steps, out_dir, vocab)
-    worst = 0.0
+    worst, lim_of_worst = 0.0, 0.0
     for rid, rows in got.items():
+        lim = limits(dtype, want[rid])
         for pos, row in rows.items():
             w = want[rid][pos]
             diff = (torch.from_numpy(row.copy()) - w).abs().max().item()
-            lim = limits(dtype, want[rid])
             assert diff <= lim, f"{rid} position {pos}: |diff| {diff:.3e} > {lim:.3e}"
-            worst = max(worst, diff)
+            if diff >= worst:
+                worst, lim_of_worst = diff, lim
             if dtype == "float32":
                 assert int(row.argmax()) == int(w.argmax())
+    assert worst <= lim_of_worst or not got
+    if case is not None:
+        record_worst(case, dtype, worst, lim_of_worst)
     return got, worst
 
 
@@ -79,18 +99,24 @@ def test_each_request_alone_and_whole(setup, dtype, tmp_path):
         steps = whole(rid, toks)
         out = tmp_path / rid
         replay(folder, tag, dtype, steps, out, max_tokens=320)
-        got, _ = compare(steps, out, TINY[tag]["vocab_size"], want, dtype)
+        got, _ = compare(steps, out, TINY[tag]["vocab_size"], want, dtype, case=f"{tag} whole")
         assert sorted(got[rid]) == list(range(len(toks)))
 
 
+@pytest.mark.parametrize("graphs", [False, True], ids=["eager", "graph"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_last_32_tokens_one_by_one(setup, dtype, tmp_path):
+def test_last_32_tokens_one_by_one(setup, dtype, graphs, tmp_path):
+    """Most of a request in one step, then single tokens: stepped eagerly, and replayed from the captured
+    graph that generation uses for such steps (the first step at a batch size runs eagerly, the second is
+    captured, the others replay it)."""
     tag, folder, seqs, want = setup
     for rid, toks in list(seqs.items())[:3]:
         steps = prefix_then_single(rid, toks, tail=32)
         out = tmp_path / rid
-        replay(folder, tag, dtype, steps, out, max_tokens=320)
-        compare(steps, out, TINY[tag]["vocab_size"], want, dtype)
+        rep = replay(folder, tag, dtype, steps, out, max_tokens=320, cuda_graphs=graphs)
+        compare(steps, out, TINY[tag]["vocab_size"], want, dtype, case=f"{tag} last 32 one by one" + (", graph" if graphs else ""))
+        replayed = sum(1 for m in rep.records if m["replayed_graph"])
+        assert replayed == (31 if graphs else 0)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -100,24 +126,30 @@ def test_portions_of_changing_size(setup, dtype, sizes, tmp_path):
     rid, toks = "r2", seqs["r2"]
     steps = portions(rid, toks, sizes)
     replay(folder, tag, dtype, steps, tmp_path, max_tokens=320)
-    got, _ = compare(steps, tmp_path, TINY[tag]["vocab_size"], want, dtype)
+    got, _ = compare(steps, tmp_path, TINY[tag]["vocab_size"], want, dtype, case=f"{tag} portions {sizes}")
     assert sorted(got[rid]) == list(range(len(toks)))
 
 
 REST = 1 << 20      # "all that is left of the request"
+# A portion that fills at least one 128-row tile of the tcgen05 prompt attention (64 tokens with 2 query heads per
+# kv head, 32 with 4) for the configurations that take it, beside single tokens of other requests in the same step.
+TILE_AND_MORE = {"c": (69, 130), "e": (37, 70)}
+FIRST_WANTED_OF_R4 = 33      # with prefix reuse r4's first portion wants its logits from here on (its start is r0's)
 
 
-def mixed_trace(seqs):
+def mixed_trace(seqs, tag="a", reuse_prefix=False):
     """Up to four live requests; portions of some beside single tokens of others; requests
     end and new ones start, in a pool that the sum of all requests would overflow."""
     ids = list(seqs)
     fed = {r: 0 for r in ids}
+    big, bigger = TILE_AND_MORE.get(tag, (24, 20))
     plan = [  # (request, tokens to feed) per step; a request may sit a step out
         [("r0", 9), ("r1", 2)],
         [("r0", 1), ("r1", 17), ("r2", 5)],
         [("r0", 1), ("r1", 1), ("r2", 30), ("r3", 2)],
-        [("r0", 24), ("r1", 1), ("r3", 7)],
+        [("r0", big), ("r1", 1), ("r3", 7)],      # a whole tile and more beside a single token and a short portion
         [("r0", 1), ("r1", 1), ("r2", 1), ("r3", 1)],
+        [("r0", 1), ("r2", bigger), ("r1", 1)],  # two tiles beside two single tokens
         [("r1", REST), ("r0", REST)],            # both finish here: their pages go back
         [("r2", 3), ("r3", REST), ("r4", 40)],   # r4 and r5 repeat r0 and r1 in reused pages
         [("r2", 1), ("r4", 1), ("r5", 2)],
@@ -132,7 +164,8 @@ def mixed_trace(seqs):
             toks = seqs[rid][fed[rid]:fed[rid] + n]
             if not toks:
                 continue
-            entries.append({"id": rid, "tokens": toks, "want": list(range(len(toks)))})
+            first = FIRST_WANTED_OF_R4 if reuse_prefix and rid == "r4" and fed[rid] == 0 else 0
+            entries.append({"id": rid, "tokens": toks, "want": list(range(first, len(toks)))})
             fed[rid] += len(toks)
             if fed[rid] == len(seqs[rid]):
                 end.append(rid)
@@ -148,15 +181,34 @@ def pool_tokens(seqs):
     return sum(-(-len(s) // 64) * 64 for s in list(seqs.values())[:4])
 
 
+@pytest.mark.parametrize("reuse", [False, True], ids=["no reuse", "prefix reuse"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_mixed_requests_in_reused_pages(setup, dtype, tmp_path):
+def test_mixed_requests_in_reused_pages(setup, dtype, reuse, tmp_path):
     tag, folder, seqs, want = setup
-    steps, all_seqs = mixed_trace(seqs)
+    steps, all_seqs = mixed_trace(seqs, tag, reuse_prefix=reuse)
     want = dict(want, r4=want["r0"], r5=want["r1"])
-    rep = replay(folder, tag, dtype, steps, tmp_path, max_tokens=pool_tokens(seqs))
-    got, _ = compare(steps, tmp_path, TINY[tag]["vocab_size"], want, dtype)
-    assert all(sorted(got[r]) == list(range(len(all_seqs[r]))) for r in all_seqs)
+    rep = replay(folder, tag, dtype, steps, tmp_path, max_tokens=pool_tokens(seqs), prefix_cache=reuse)
+    got, _ = compare(steps, tmp_path, TINY[tag]["vocab_size"], want, dtype,
+                     case=f"{tag} mixed" + (", prefix reuse" if reuse else ""))
+    first_of = {r: (FIRST_WANTED_OF_R4 if reuse and r == "r4" else 0) for r in all_seqs}
+    assert all(sorted(got[r]) == list(range(first_of[r], len(all_seqs[r]))) for r in all_seqs)
     assert rep.cache.stats["pages_allocated"] > rep.cache.num_pages       # pages were handed out again
+    meta = {m["step"]: m for m in rep.records}
+    assert sum(m["pages_allocated"] for m in rep.records) == rep.cache.stats["pages_allocated"]
+    assert sum(m["pages_released"] for m in rep.records) == rep.cache.stats["pages_released"]
+    assert meta[6]["pages_released"] > 0 and meta[6]["live_requests"] == 2      # r0 and r1 ended there
+    hit = meta[7]["prefix_hit_tokens"]          # the step in which r4 arrives with r0's first tokens
+    P = PAGE_SIZE[tag]
+    assert hit == (FIRST_WANTED_OF_R4 // P * P if reuse else 0)
+    assert hit == sum(m["prefix_hit_tokens"] for m in rep.records)
+    if tag in TILE_AND_MORE and dtype == "bfloat16":
+        # the step that this configuration is here for: whole tcgen05 prompt tiles and single tokens in one batch
+        whole_tiles = lambda m: sum(n for k, n in m["tiles"].items() if k.startswith(f"{128 // GROUP[tag]} tokens"))
+        assert whole_tiles(meta[3]) >= 2 and meta[3]["single_token_entries"] == 1
+        assert whole_tiles(meta[5]) >= 3 and meta[5]["single_token_entries"] == 2
+
+
+GROUP = {"c": 2, "e": 4}     # query heads per kv head of the configurations with head size 128
 
 
 def test_schedules_agree_with_each_other_in_32_bit(setup, tmp_path):
@@ -174,7 +226,7 @@ def test_schedules_agree_with_each_other_in_32_bit(setup, tmp_path):
 def test_trace_run_program(setup, tmp_path):
     """bin/trace_run as a program: stdin steps, `done <step>` lines, files on disk, exit 0."""
     tag, folder, seqs, want = setup
-    steps, all_seqs = mixed_trace(seqs)
+    steps, all_seqs = mixed_trace(seqs, tag)
     env = dict(os.environ)
     proc = subprocess.run([sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(folder), "--dtype", "float32",
                            "--out", str(tmp_path), "--max-tokens", str(pool_tokens(seqs)), "--page-size", str(PAGE_SIZE[tag])],
@@ -183,6 +235,7 @@ def test_trace_run_program(setup, tmp_path):
     assert proc.returncode == 0, proc.stderr[-2000:]
     assert proc.stdout.split() == [w for s in steps for w in ("done", str(s["step"]))]
     compare(steps, tmp_path, TINY[tag]["vocab_size"], dict(want, r4=want["r0"], r5=want["r1"]), "float32")
+    assert all((tmp_path / f"{s['step']}.json").exists() for s in steps)
 
 
 @pytest.mark.parametrize("head_dim,heads,kv_heads", [(80, 3, 1), (144, 2, 2), (256, 2, 1), (112, 4, 2)])

@@ -242,13 +242,86 @@ def test_prefix_hits_skip_work():
     assert d.stats.cache_hit_blocks == 3 and d.stats.cache_hit_tokens == 12
 
 
-def test_error_latch_like_the_reference():
-    d, _ = driver(max_num_seqs=1, max_model_len=16, block_size=4)
-    d.thread_error = "RuntimeError: boom"
-    with pytest.raises(RuntimeError, match="engine thread failed"):
-        add_request(d, [1], SamplingParams())
-    with pytest.raises(RuntimeError, match="engine thread failed"):
-        list(eng.stream(d, 0))
+class FailingRunner(FakeRunner):
+    """The stand-in device, whose step raises from its `fail_at`-th call on."""
+
+    def __init__(self, fail_at, error):
+        super().__init__()
+        self.fail_at, self.error, self.calls = fail_at, error, 0
+
+    def step(self, entries):
+        self.calls += 1
+        if self.calls >= self.fail_at:
+            raise self.error
+        return super().step(entries)
+
+
+def failing_driver(fail_at, error, **kw):
+    model = Model(registry.config_from_dict(TINY_A).to_spec(), BuildContext(torch.float32, torch.device("cpu")))
+    runner = FailingRunner(fail_at, error)
+    return make_driver(model, runner=runner, sampler=FakeSampler(), **kw), runner
+
+
+def test_an_exception_inside_the_background_thread_reaches_every_caller():
+    """The third step raises inside the thread (as jllm's tests make its loop raise, tests/test_scheduler.py:335-366):
+    the thread ends, the reader of a stream gets the error after the events that were delivered before it, a
+    second reader and `add_request` and `step` get it too, and `stop` still joins."""
+    from jax_vllm_b200.engine.background import EngineFailed
+    d, runner = failing_driver(3, RuntimeError("boom in step three"), max_num_seqs=2, max_model_len=32, block_size=4)
+    a = add_request(d, [1, 2, 3], SamplingParams(max_new_tokens=8))
+    b = add_request(d, [4, 5], SamplingParams(max_new_tokens=8))
+    eng.start(d)
+    try:
+        got = []
+        with pytest.raises(EngineFailed, match="RuntimeError: boom in step three"):
+            for ev in eng.stream(d, a):
+                got.append(ev.token)
+        assert got == expected([1, 2, 3], 8)[:len(got)] and len(got) == 2          # steps one and two delivered
+        with pytest.raises(EngineFailed, match="boom in step three"):
+            list(eng.stream(d, b))
+        with pytest.raises(EngineFailed):
+            add_request(d, [1], SamplingParams())
+        with pytest.raises(EngineFailed):
+            step(d)
+        assert not d.router.running
+    finally:
+        eng.stop(d)                       # joins a thread that has already ended
+    assert runner.calls == 3
+    # starting again clears the latch; the stand-in keeps failing, so the next error is latched in turn
+    eng.start(d)
+    with pytest.raises(EngineFailed):
+        list(eng.stream(d, b))
+    eng.stop(d)
+
+
+def test_the_allocator_running_dry_inside_the_thread_is_latched_too():
+    from jax_vllm_b200.cache.page_pool import OutOfPages
+    from jax_vllm_b200.engine.background import EngineFailed
+    d, _ = failing_driver(2, OutOfPages("no free pages"), max_num_seqs=1, max_model_len=16, block_size=4)
+    a = add_request(d, [1, 2, 3], SamplingParams(max_new_tokens=4))
+    eng.start(d)
+    try:
+        with pytest.raises(EngineFailed, match="OutOfPages: no free pages"):
+            list(eng.stream(d, a))
+    finally:
+        eng.stop(d)
+
+
+def test_streams_without_a_thread_and_after_a_stop():
+    """Without a background thread the reader of a stream drives the engine itself; the events of the other
+    request wait in its queue.  A stream read after `stop` with its request unfinished says so."""
+    d, _ = driver(max_num_seqs=2, max_model_len=32, block_size=4)
+    a = add_request(d, [1, 2], SamplingParams(max_new_tokens=5))
+    b = add_request(d, [3], SamplingParams(max_new_tokens=3))
+    assert [ev.token for ev in eng.stream(d, a)] == expected([1, 2], 5)
+    assert [ev.token for ev in eng.stream(d, b)] == expected([3], 3)
+    with pytest.raises(KeyError, match="no events to read"):
+        list(eng.stream(d, a))
+    eng.start(d)
+    eng.stop(d)
+    c = add_request(d, [9, 9, 9], SamplingParams(max_new_tokens=2))
+    with pytest.raises(RuntimeError, match="stopped with request"):
+        list(eng.stream(d, c))
 
 
 def test_background_thread_streams_events():

@@ -108,3 +108,18 @@ def test_random_mode_writes_a_folder_that_loads(tmp_path):
     # values of a tensor depend on its name and the seed only, not on what else the model holds
     sub = {k: v for k, v in m.tensor_specs().items() if "layers.1" in k}
     assert all(torch.equal(random_tensors(sub, 7, torch.bfloat16)[k], t[k]) for k in sub)
+
+
+@pytest.mark.parametrize("keep", [5, 100, 0.5, -10])
+def test_a_file_that_was_cut_short_is_named(tmp_path, keep):
+    """A safetensors file cut short (inside its header, inside its data, ten bytes before its end) gives one
+    error that names the file, not a stack of the reading library's own."""
+    from jax_vllm_b200.weights import DamagedFile
+    folder = make_folder(tmp_path / "m", "a")
+    path = folder / "model.safetensors"
+    data = path.read_bytes()
+    n = int(len(data) * keep) if isinstance(keep, float) else (keep if keep > 0 else len(data) + keep)
+    path.write_bytes(data[:n])
+    m = _model(TINY_A)
+    with pytest.raises(DamagedFile, match="model.safetensors .* cut short"):
+        load_tensors(folder, m.tensor_specs(), "cpu", m.optional_tensors())

@@ -29,8 +29,13 @@ TINY_C = dict(architectures=["Qwen3ForCausalLM"], vocab_size=300, hidden_size=19
 TINY_D = dict(architectures=["Qwen3ForCausalLM"], vocab_size=301, hidden_size=120, intermediate_size=136,
               num_hidden_layers=1, num_attention_heads=5, num_key_value_heads=5, head_dim=48, rms_norm_eps=3e-6,
               rope_theta=2e4, max_position_embeddings=512, tie_word_embeddings=True)
-TINY = {"a": TINY_A, "b": TINY_B, "c": TINY_C, "d": TINY_D}
-PAGE_SIZE = {"a": 16, "b": 8, "c": 16, "d": 4}
+# A fifth one with the head layout of the benchmarked model (32 query heads in 8 groups of 4, head size 128): the
+# 128-row tiles of the tcgen05 prompt attention hold 32 tokens, the decode attention has 4 query rows per kv head.
+TINY_E = dict(architectures=["Qwen3ForCausalLM"], vocab_size=320, hidden_size=512, intermediate_size=1024,
+              num_hidden_layers=2, num_attention_heads=32, num_key_value_heads=8, head_dim=128, rms_norm_eps=1e-6,
+              rope_theta=1e6, max_position_embeddings=1024, tie_word_embeddings=False)
+TINY = {"a": TINY_A, "b": TINY_B, "c": TINY_C, "d": TINY_D, "e": TINY_E}
+PAGE_SIZE = {"a": 16, "b": 8, "c": 16, "d": 4, "e": 16}
 
 
 def tensor_shapes(c: dict) -> dict:
