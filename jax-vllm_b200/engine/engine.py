@@ -10,6 +10,7 @@ from __future__ import annotations
 
 import threading
 import time
+import weakref
 from typing import Iterator, Optional
 
 import torch
@@ -44,7 +45,13 @@ class Driver:
         self.id_lock = threading.Lock()
         self.step_lock = threading.Lock()          # the scheduler and the cache are touched under it only
         self.next_id = 0
-        self.router = EventRouter(lambda: step(self), lambda: has_work(self))
+        # The router reaches the driver through a weak reference: a strong one would close a cycle, and a driver that
+        # only the cycle collector frees may be freed at any moment, in the middle of another driver's graph capture
+        # (where destroying this driver's captured graphs is an error).  A driver that is dropped stops its thread.
+        me = weakref.ref(self)
+        self.router = EventRouter(lambda: step(me()) if me() is not None else [],
+                                  lambda: me() is not None and has_work(me()))
+        weakref.finalize(self, self.router.stop, False)
         self.ahead = None                  # the next step's plan, made while the device ran the last one
         self.host_tokens = None            # pinned memory that the sampled tokens come back to
 

@@ -9,6 +9,9 @@ one-page rows and a decode step of padded single tokens (jllm/engine/generate.py
 
 from __future__ import annotations
 
+import contextlib
+import gc
+
 import torch
 
 from .. import ops
@@ -16,6 +19,20 @@ from ..cache import CacheManager
 from ..csrc import build as kernel_build
 from ..parts import BuildContext, Model
 from .batch import BatchBuilder, StepEntry
+
+
+@contextlib.contextmanager
+def _capture(graph):
+    """`torch.cuda.graph(graph)` with Python's cycle collector off: a collection that happened to run inside the
+    capture and freed CUDA objects of some other owner (an old driver's graphs, pinned buffers) would invalidate it."""
+    was_on = gc.isenabled()
+    gc.disable()
+    try:
+        with torch.cuda.graph(graph):
+            yield
+    finally:
+        if was_on:
+            gc.enable()
 
 
 class _DecodeGraph:
@@ -115,7 +132,7 @@ class Runner:
             ctx = b.context(entries, layout, dev, max_seq_len=self.max_model_len)
             graph = torch.cuda.CUDAGraph()
             before = ops.launch_count
-            with torch.cuda.graph(graph):
+            with _capture(graph):
                 logits = self.model.forward(ctx, self.layer_caches)
             g = _DecodeGraph(layout, dev, logits, graph, ops.launch_count - before)
             ops.launch_count = before           # nothing ran yet: a replay counts them
@@ -170,7 +187,7 @@ class Runner:
                 temps_d = dev[samp_off + 4 * n:samp_off + 5 * n].view(torch.float32)
                 graph = torch.cuda.CUDAGraph()
                 before = ops.launch_count
-                with torch.cuda.graph(graph):
+                with _capture(graph):
                     logits = self.model.forward(ctx, self.layer_caches)
                     out[:n].copy_(ops.sample(logits, temps_d, seeds_d, counters_d))
                     out[n:].copy_(ops.status_word(self.device))
