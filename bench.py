@@ -133,13 +133,18 @@ def fake_context(driver, batch, ctx):
     return rcs
 
 
+MIN_TIMED_SECONDS = 0.5      # a timed region shorter than this is repeated until it adds up to it
+MAX_CONTEXT = 4096            # requests of the decode runs never grow beyond this
+
+
 def time_decode(model, batch, steps, warmup, ctx=CONTEXT):
-    """Device time of `steps` decode steps at `batch`; returns (ms per step, launches per step)."""
+    """Device time of `steps` decode steps at `batch`, repeated until MIN_TIMED_SECONDS are timed (at most until the
+    requests reach MAX_CONTEXT tokens); returns (median ms per step over the repeats, launches per step, repeats,
+    all the repeats' ms per step)."""
     import torch
     from jax_vllm_b200 import make_driver, ops
     from jax_vllm_b200.engine import StepEntry
-    max_len = ctx + warmup + steps + 8
-    max_len = -(-max_len // PAGE) * PAGE
+    max_len = MAX_CONTEXT
     driver = make_driver(model, max_num_seqs=batch, max_model_len=max_len, block_size=PAGE, prefix_cache=False)
     rcs = fake_context(driver, batch, ctx)
     runner, cache, sampler = driver.runner, driver.cache, driver.sampler
@@ -159,19 +164,25 @@ def time_decode(model, batch, steps, warmup, ctx=CONTEXT):
     for i in range(warmup):
         one(i)
     torch.cuda.synchronize()
-    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    before = ops.launch_count
-    start.record()
-    for i in range(steps):
-        one(warmup + i)
-    end.record()
-    torch.cuda.synchronize()
-    ms = start.elapsed_time(end) / steps
-    launches = (ops.launch_count - before) // steps
+    per_step, launches, done = [], 0, warmup
+    most = max(1, (MAX_CONTEXT - ctx - warmup - 1) // steps)
+    while True:
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        before = ops.launch_count
+        start.record()
+        for i in range(steps):
+            one(done + i)
+        end.record()
+        torch.cuda.synchronize()
+        done += steps
+        per_step.append(start.elapsed_time(end) / steps)
+        launches = (ops.launch_count - before) // steps
+        if sum(per_step) * steps >= MIN_TIMED_SECONDS * 1e3 or len(per_step) >= most:
+            break
     runner.check_kernels()
     del driver, runner, cache
     torch.cuda.empty_cache()
-    return ms, launches
+    return statistics.median(per_step), launches, len(per_step), per_step
 
 
 def time_prefill(model, tokens, warmup, reps=3):
@@ -206,7 +217,9 @@ def time_e2e(model, batch, steps, warmup, ctx=CONTEXT):
     sampled tokens come back to the host each step."""
     import torch
     from jax_vllm_b200 import SamplingParams, add_request, make_driver, step
-    new = warmup + 3 * steps + 4
+    runs = max(3, min(25, int(MIN_TIMED_SECONDS / (steps * 0.004)) + 1))
+    new = min(warmup + runs * steps + 4, MAX_CONTEXT - ctx)
+    runs = max(1, (new - warmup - 4) // steps)
     max_len = -(-(ctx + new) // PAGE) * PAGE
     driver = make_driver(model, max_num_seqs=batch, max_model_len=max_len, block_size=PAGE, prefix_cache=False,
                          max_tokens_per_step=max(2048, batch))
@@ -214,20 +227,17 @@ def time_e2e(model, batch, steps, warmup, ctx=CONTEXT):
         add_request(driver, [(i * 31 + b * 977) % 50000 for i in range(ctx)], SamplingParams(max_new_tokens=new))
     while any(len(r.output_ids) < 1 + warmup for r in driver.requests.values()):   # prompts, then warm-up decodes
         step(driver)
-    # three runs of `steps` steps; the fastest counts (a run is tens of milliseconds of wall clock on a
-    # shared host, and one hiccup of the host halves it)
-    best = None
-    for _ in range(3):
+    # `runs` runs of `steps` steps (a run is tens of milliseconds of wall clock on a shared host, where one hiccup of
+    # the host halves it): the median counts, the fastest is given beside it
+    rates = []
+    for _ in range(runs):
         torch.cuda.synchronize()
         t0 = time.perf_counter()
         emitted = 0
         for _ in range(steps):
             emitted += len(step(driver))
         torch.cuda.synchronize()
-        dt = time.perf_counter() - t0
-        if best is None or emitted / dt > best[0] / best[1]:
-            best = (emitted, dt)
-    emitted, dt = best
+        rates.append(emitted / (time.perf_counter() - t0))
     # one copy per step: the batch description (tokens, positions, block tables, work lists) and, behind it in
     # the same buffer, seeds, counters and temperatures of the sampler
     g = driver.runner.graphs_sampled.get(batch)
@@ -239,7 +249,7 @@ def time_e2e(model, batch, steps, warmup, ctx=CONTEXT):
     d2h = (batch + 1) * 4                        # sampled tokens and the kernels' status word
     del driver
     torch.cuda.empty_cache()
-    return emitted / dt, h2d, d2h
+    return statistics.median(rates), max(rates), len(rates), h2d, d2h
 
 
 def micro(spec: str, reps: int, eager: bool = False) -> int:
@@ -461,6 +471,8 @@ def main():
     ap.add_argument("--micro", default=None, help="run one kernel alone, e.g. linear:24576x4096:8 (see micro())")
     ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS),
                     help="a serving workload of a larger shape through the entry point (see WORKLOADS); --layers cuts it")
+    ap.add_argument("--with-workloads", action="store_true",
+                    help="after the headline run, also run the two serving workloads and add their lines under `workloads`")
     ap.add_argument("--micro-eager", action="store_true",
                     help="with --micro: plain launches instead of replays of a CUDA graph (for a profiler)")
     args = ap.parse_args()
@@ -488,40 +500,61 @@ def main():
         print(json.dumps({"prefill_ms": round(pms, 3), "tokens": PREFILL_TOKENS, "layers": args.layers}))
         return 0
 
+    region_clocks = {}
     with ClockSampler() as clocks:
-        ms, launches = time_decode(model, args.batch, args.steps, warmup)
+        ms, launches, repeats, all_ms = time_decode(model, args.batch, args.steps, warmup)
+    region_clocks["decode"] = clocks.summary
     value = args.batch / (ms / 1e3)
-    bytes_step = decode_bytes(cfg_dict, args.layers, args.batch, CONTEXT + warmup + args.steps // 2)
+    bytes_step = decode_bytes(cfg_dict, args.layers, args.batch, CONTEXT + warmup + repeats * args.steps // 2)
     achieved = bytes_step / (ms / 1e3) / 1e9
     out = {
-        "metric": "decode tok/s (Qwen3-8B shape, bf16, batch 8, 2048-token context)",
+        "metric": f"decode tok/s (Qwen3-8B shape, bf16, batch {args.batch}, {CONTEXT}-token context)",
         "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup,
+        "repeats": repeats, "ms_per_step_of_repeats": [round(v, 4) for v in all_ms],
         "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic (uniform random token ids, random N(0,0.02) weights, seed 5)",
         "config": {"model": "Qwen3-8B shape", "layers": args.layers, "layers_of_config": QWEN3_8B["num_hidden_layers"],
                    "hidden": 4096, "q_heads": 32, "kv_heads": 8, "head_dim": 128, "intermediate": 12288,
                    "vocab": 151936, "global_batch": args.batch, "seq_len": CONTEXT, "max_context": 4096,
                    "page_size": PAGE, "parallelism": "none (1 GPU)", "l2": "inputs larger than L2 (15 GB of weights)",
-                   "cuda_graphs": True},
-        "gpu_launches": launches * args.steps,
+                   "cuda_graphs": True, "timed": f"median of {repeats} repeats of {args.steps} steps"},
+        "gpu_launches": launches * args.steps * repeats,
         "clocks": clocks.summary,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4), "peak_source": pk_src},
     }
     if not args.skip_points:
-        e2e, h2d, d2h = time_e2e(model, args.batch, args.steps, warmup)
+        with ClockSampler() as c:
+            e2e, e2e_best, runs, h2d, d2h = time_e2e(model, args.batch, args.steps, warmup)
+        region_clocks["e2e"] = c.summary
         out["e2e"] = {"value": round(e2e, 1), "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                      "runs": 3, "picked": "fastest run of `steps` steps"}
-        pms = time_prefill(model, PREFILL_TOKENS, warmup=2)
+                      "runs": runs, "picked": "median over the runs of `steps` steps", "best": round(e2e_best, 1)}
+        with ClockSampler() as c:
+            pms = time_prefill(model, PREFILL_TOKENS, warmup=2, reps=max(3, int(MIN_TIMED_SECONDS / 0.027)))
+        region_clocks["prefill"] = c.summary
         flops = prefill_flops(cfg_dict, args.layers, PREFILL_TOKENS)
         out["prefill"] = {"value": round(PREFILL_TOKENS / (pms / 1e3), 1), "tokens": PREFILL_TOKENS, "ms": round(pms, 3),
                           "frac": round(flops / (pms / 1e3) / 1e12 / pk["bf16_tflops"], 4),
                           "peak_tflops": pk["bf16_tflops"], "peak_source": pk_src}
         points = {}
         for b in (1, 64):
-            pms_b, _ = time_decode(model, b, max(8, args.steps // 2), warmup)
+            with ClockSampler() as c:
+                pms_b, _, _, _ = time_decode(model, b, max(8, args.steps // 2), warmup)
+            region_clocks[f"decode_b{b}"] = c.summary
             points[f"decode_b{b}"] = round(b / (pms_b / 1e3), 1)
+            frac = decode_bytes(cfg_dict, args.layers, b, CONTEXT + 64) / (pms_b / 1e3) / 1e9 / pk["hbm_gbs"]
+            points[f"decode_b{b}_hbm_frac"] = round(frac, 4)
         out["points"] = points
+    out["clocks_by_region"] = region_clocks
+    if args.with_workloads:
+        # the two serving workloads of larger shapes, each in a process of its own (they need the device's memory)
+        del model
+        torch.cuda.empty_cache()
+        out["workloads"] = {}
+        for name in sorted(WORKLOADS):
+            proc = subprocess.run([sys.executable, str(ROOT / "bench.py"), "--workload", name], capture_output=True, text=True)
+            line = [l for l in proc.stdout.splitlines() if l.startswith("{")]
+            out["workloads"][name] = json.loads(line[-1]) if proc.returncode == 0 and line else {"failed": proc.stderr[-300:]}
     print(json.dumps(out))
     return 0
 
