@@ -380,6 +380,43 @@ def micro(spec: str, reps: int, eager: bool = False) -> int:
     return 0
 
 
+def timeline(batch: int, layers: int) -> int:
+    """Start, duration and end of every kernel of one replayed decode step (torch's profiler; programmatic dependent
+    launch lets kernels overlap, so a kernel's start is when its first block became resident, and the increments from
+    end to end tell what each adds to the step): `python bench.py --timeline 8 --layers 4`."""
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+    from jax_vllm_b200 import make_driver, random_model, registry
+    from jax_vllm_b200.engine import StepEntry
+    model = random_model(registry.config_from_dict(dict(QWEN3_8B, num_hidden_layers=layers)), seed=5, dtype="bf16")
+    driver = make_driver(model, max_num_seqs=batch, max_model_len=CONTEXT + 64, block_size=PAGE, prefix_cache=False)
+    rcs = fake_context(driver, batch, CONTEXT)
+
+    def one(i):
+        entries = []
+        for b, rc in enumerate(rcs):
+            driver.cache.grow(rc, rc.num_tokens + 1)
+            entries.append(StepEntry(rc, [(i * 7919 + b) % 1000], (0,)))
+        driver.runner.step(entries)
+        for rc in rcs:
+            rc.num_tokens += 1
+
+    for i in range(6):
+        one(i)
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        one(7)
+        torch.cuda.synchronize()
+    evs = sorted((e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA), key=lambda e: e.time_range.start)
+    t0, last_end = evs[0].time_range.start, evs[0].time_range.start
+    print(f"decode step, batch {batch}, {CONTEXT}-token context, {layers} layers: start, duration, end, end minus the latest end before (us)")
+    for e in evs:
+        start, dur = e.time_range.start - t0, e.time_range.end - e.time_range.start
+        print(f"{start:9.1f} {dur:7.1f} {start + dur:9.1f} {e.time_range.end - last_end:+7.1f}  {e.name[:70]}")
+        last_end = max(last_end, e.time_range.end)
+    return 0
+
+
 WORKLOADS = {
     # the larger dense Qwen3 shapes as serving workloads: all requests arrive at once, the scheduler cuts their
     # prompts into portions beside the decode tokens of the others
@@ -471,6 +508,8 @@ def main():
     ap.add_argument("--micro", default=None, help="run one kernel alone, e.g. linear:24576x4096:8 (see micro())")
     ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS),
                     help="a serving workload of a larger shape through the entry point (see WORKLOADS); --layers cuts it")
+    ap.add_argument("--timeline", type=int, default=None, metavar="BATCH",
+                    help="print every kernel of one replayed decode step at this batch with its start and end (use --layers)")
     ap.add_argument("--with-workloads", action="store_true",
                     help="after the headline run, also run the two serving workloads and add their lines under `workloads`")
     ap.add_argument("--micro-eager", action="store_true",
@@ -485,6 +524,8 @@ def main():
         return 2
     if args.workload:
         return workload(args.workload, args.layers)
+    if args.timeline:
+        return timeline(args.timeline, args.layers or 4)
     args.layers = args.layers or QWEN3_8B["num_hidden_layers"]
     warmup = max(3, args.warmup)
 
