@@ -469,6 +469,11 @@ def attn_decode_tcgen05_supports(dtype: torch.dtype, head_dim: int, n_q_heads: i
 _sm_count: dict = {}
 
 
+def multiprocessors(device) -> int:
+    """Multiprocessors of the device (what dispatch rules are scaled by)."""
+    return _multiprocessors(device)
+
+
 def _multiprocessors(device) -> int:
     idx = torch.device(device).index or 0
     if idx not in _sm_count:

@@ -48,14 +48,24 @@ class GatedMLP(Part):
             self.w_gate_up = torch.cat([g, u], dim=0).contiguous()
         self.w_down = self.compute_weight(tensors[f"{p}.down_proj.weight"], self.ctx).contiguous()
 
-    # From this many rows on the gate is applied in the epilogue of the tcgen05 product; below, the product's
-    # 128 x 256 tiles leave multiprocessors idle and the library product followed by the gate kernel is faster
-    # (measured at 24,576 x 4,096: equal at 1,024 rows, 7 % ahead at 2,048, 20 % behind at 64).
-    FUSED_GATE_ROWS = 1024
+    # The gate is applied in the epilogue of the tcgen05 product once its 128 x 256 tiles are at least this many per
+    # multiprocessor; with fewer, too many multiprocessors idle in the last round and the library product followed by
+    # the gate kernel is faster (measured at 24,576 x 4,096 on 148 multiprocessors: equal at 1,024 rows = 5.2 tiles
+    # each, 7 % ahead at 2,048 rows, 20 % behind at 64).  FUSED_GATE_ROWS, if set, is a plain row count instead (tests).
+    FUSED_GATE_TILES_PER_SM = 5.0
+    FUSED_GATE_ROWS = None
+
+    def _fuse_gate(self, rows: int) -> bool:
+        if self.block is None:
+            return False
+        if self.FUSED_GATE_ROWS is not None:
+            return rows >= self.FUSED_GATE_ROWS
+        tiles = -(-rows // 128) * -(-self.w_gate_up.shape[0] // 256)
+        return tiles >= self.FUSED_GATE_TILES_PER_SM * ops.multiprocessors(self.w_gate_up.device)
 
     def forward(self, x, step):
         dt = self.ctx.dtype
-        if self.block is not None and x.shape[0] >= self.FUSED_GATE_ROWS:
+        if self._fuse_gate(x.shape[0]):
             act = ops.gemm_tcgen05(x, self.w_gate_up, "swiglu")
         else:
             act = ops.swiglu(ops.linear(x, self.w_gate_up, dt, parts_ok=True), self.block, out_dtype=dt)

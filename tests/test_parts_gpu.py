@@ -138,7 +138,8 @@ def test_feed_forward_and_block_alone():
 @pytest.mark.parametrize("rows", [3, 16, 17, 150, 1100])
 def test_feed_forward_bf16_with_the_gate_in_the_product(rows):
     """An intermediate size that is a multiple of 128 takes the interleaved gate|up weight: prompt steps apply
-    the gate in the epilogue of the tcgen05 product (from 1,024 rows on), smaller batches in the separate kernel; both equal plain."""
+    the gate in the epilogue of the tcgen05 product (here from 1,024 rows on; the part itself goes by the product's
+    tiles per multiprocessor), smaller batches in the separate kernel; both equal plain."""
     j, cache, config, engine, parts, weights = pkg()
     ctx = parts.BuildContext(torch.bfloat16, DEV)
     ff = parts.FEED_FORWARDS["gated_mlp"](config.GatedMLPSpec(72, 384), "L", ctx)
@@ -146,6 +147,8 @@ def test_feed_forward_bf16_with_the_gate_in_the_product(rows):
     w = {n: (torch.randn(ts.shape, generator=g) * 0.2).to(torch.bfloat16) for n, ts in ff.tensor_specs().items()}
     ff.bind({k: v.to(DEV) for k, v in w.items()})
     assert ff.block == 128
+    assert not ff._fuse_gate(4096)           # 32 x 3 tiles are far fewer than five per multiprocessor
+    ff.FUSED_GATE_ROWS = 1024                # so that this small part takes both ways
     x = torch.randn(rows, 72, generator=g).to(torch.bfloat16)
     got = ff.forward(x.to(DEV), None).float().cpu()
     # the plain formula with the engine's rounding points: the activations are bfloat16 where they reach
@@ -153,7 +156,7 @@ def test_feed_forward_bf16_with_the_gate_in_the_product(rows):
     rnd = lambda t: t.to(torch.bfloat16).double()
     wd = {k: v.double() for k, v in w.items()}
     gate, up = x.double() @ wd["L.mlp.gate_proj.weight"].T, x.double() @ wd["L.mlp.up_proj.weight"].T
-    if rows < ff.FUSED_GATE_ROWS:
+    if not ff._fuse_gate(rows):
         gate, up = rnd(gate), rnd(up)
     want = (rnd(torch.nn.functional.silu(gate) * up) @ wd["L.mlp.down_proj.weight"].T).float()
     torch.testing.assert_close(got, want, atol=2e-2, rtol=1e-2)
