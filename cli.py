@@ -46,6 +46,8 @@ def main(argv=None) -> int:
     p.add_argument("--eos-id", type=int, default=None)
     p.add_argument("--block-size", type=int, default=16, help="tokens per cache page")
     p.add_argument("--num-blocks", type=int, default=None, help="pages in the pool (default: worst case)")
+    p.add_argument("--memory-fraction", type=float, default=None,
+                   help="without --num-blocks: size the pool to this share of the free device memory")
     p.add_argument("--max-tokens-per-step", type=int, default=2048)
     p.add_argument("--ignore-eos", action="store_true", help="generate --max-tokens tokens whatever is sampled")
     p.add_argument("--no-prefix-cache", dest="prefix_cache", action="store_false")
@@ -84,7 +86,8 @@ def main(argv=None) -> int:
     max_prefill_len = args.max_prefill_len if args.max_prefill_len is not None else min(512, args.max_model_len)
     driver = make_driver(model, max_num_seqs=args.max_num_seqs, max_model_len=args.max_model_len,
                          max_prefill_len=max_prefill_len, block_size=args.block_size, num_blocks=args.num_blocks,
-                         max_tokens_per_step=args.max_tokens_per_step, prefix_cache=args.prefix_cache)
+                         max_tokens_per_step=args.max_tokens_per_step, prefix_cache=args.prefix_cache,
+                         memory_fraction=args.memory_fraction)
     if args.prewarm:
         print(f"prewarm: done in {prewarm(driver):.1f}s", flush=True)
 

@@ -31,7 +31,10 @@ class EngineConfig:
     max_model_len: int = 2048             # prompt + generated tokens of one request
     max_prefill_len: Optional[int] = None  # longest prompt accepted (None: max_model_len)
     block_size: int = 16                  # tokens in a page of the cache
-    num_blocks: Optional[int] = None      # pages in each pool (None: max_num_seqs * pages of max_model_len)
+    num_blocks: Optional[int] = None      # pages in each pool (None: by memory_fraction, else the worst case:
+                                          # max_num_seqs * pages of max_model_len)
+    memory_fraction: Optional[float] = None   # with num_blocks None: the pool takes this share of the device memory
+                                          # that is free when the driver is made (never more than the worst case)
     max_tokens_per_step: int = 2048       # token budget of one step (decoded tokens + prompt portions)
     prefix_cache: bool = True
     decode_split_size: int = 256          # key positions per split of a decoded token's attention
@@ -48,6 +51,8 @@ class EngineConfig:
             raise ValueError("max_prefill_len must be <= max_model_len")
         if self.num_blocks is not None and self.num_blocks < 1:
             raise ValueError("num_blocks must be positive")
+        if self.memory_fraction is not None and not 0.0 < self.memory_fraction <= 1.0:
+            raise ValueError("memory_fraction must lie in (0, 1]")
 
     @property
     def prompt_limit(self) -> int:
@@ -60,3 +65,15 @@ class EngineConfig:
     @property
     def pool_pages(self) -> int:
         return self.num_blocks if self.num_blocks is not None else self.max_num_seqs * self.pages_per_request
+
+    def pages_for_memory(self, bytes_per_page: int, free_bytes: int) -> int:
+        """Pages of the pool when it is sized by `memory_fraction`: what fits into that share of `free_bytes`, at
+        most the worst case, at least the pages of one request of max_model_len (fewer could never finish one)."""
+        worst = self.max_num_seqs * self.pages_per_request
+        if self.memory_fraction is None or bytes_per_page <= 0:
+            return worst
+        fit = int(self.memory_fraction * free_bytes) // bytes_per_page
+        if fit < self.pages_per_request:
+            raise MemoryError(f"{self.memory_fraction:.2f} of the free device memory ({free_bytes >> 20} MiB) holds {fit} "
+                              f"pages of {bytes_per_page} bytes; one request of max_model_len needs {self.pages_per_request}")
+        return min(worst, fit)

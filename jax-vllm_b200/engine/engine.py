@@ -31,9 +31,17 @@ class Driver:
         stand-ins with the same `step`/`sample` methods."""
         self.model, self.config = model, config
         self.max_num_seqs, self.max_model_len = config.max_num_seqs, config.max_model_len
-        self.max_prefill_len, self.block_size, self.num_blocks = config.prompt_limit, config.block_size, config.pool_pages
+        self.max_prefill_len, self.block_size = config.prompt_limit, config.block_size
         self.stats = EngineStats()
-        self.cache = CacheManager(model.cache_needs(), config.block_size, config.pool_pages, config.max_num_seqs,
+        pages = config.pool_pages
+        if config.num_blocks is None and config.memory_fraction is not None:
+            # the pool is sized from the memory that is free now (the weights are loaded already)
+            probe = CacheManager(model.cache_needs(), config.block_size, 1, 1, False)
+            itemsize = 4 if config.dtype == torch.float32 else 2
+            free_bytes = torch.cuda.mem_get_info(torch.device(config.device))[0]
+            pages = config.pages_for_memory(probe.bytes_per_page(itemsize), free_bytes)
+        self.num_blocks = pages
+        self.cache = CacheManager(model.cache_needs(), config.block_size, pages, config.max_num_seqs,
                                   config.prefix_cache)
         self.runner = runner if runner is not None else Runner(
             model, self.cache, config.device, config.dtype, max_model_len=config.max_model_len,
@@ -60,7 +68,8 @@ def make_driver(model, max_num_seqs: int = 4, max_model_len: int = 2048, max_pre
                 block_size: int = 16, num_blocks: Optional[int] = None, dtype=None, runner=None, sampler=None,
                 **more) -> Driver:
     """A driver for a loaded model.  `dtype` defaults to the model's compute dtype and must
-    equal it.  `more`: max_tokens_per_step, prefix_cache, decode_split_size, cuda_graphs."""
+    equal it.  `more`: max_tokens_per_step, prefix_cache, decode_split_size, cuda_graphs, memory_fraction (with
+    num_blocks None the pool takes that share of the free device memory instead of the worst case)."""
     model_dtype = model.ctx.dtype
     dtype = parse_dtype(dtype) if dtype is not None else model_dtype
     if dtype != model_dtype:

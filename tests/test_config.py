@@ -88,3 +88,19 @@ def test_schedule_and_cache_from_validation():
     layers[0] = replace(layers[0], cache_from=2)
     with pytest.raises(ValueError):
         replace(spec, layers=tuple(layers)).validate()
+
+
+def test_pool_sized_by_a_share_of_the_free_memory():
+    """With no page count given, `memory_fraction` sizes the pool: what fits into that share of the free memory,
+    never more than the worst case, and an error if not even one request of max_model_len would fit."""
+    from jax_vllm_b200.config import EngineConfig
+    cfg = EngineConfig(max_num_seqs=8, max_model_len=1024, block_size=16, memory_fraction=0.5)
+    per_page = 147456 * 16                       # bytes of a 16-token page of the 8B shape
+    assert cfg.pages_per_request == 64 and cfg.pool_pages == 512
+    assert cfg.pages_for_memory(per_page, 2 * 300 * per_page) == 300
+    assert cfg.pages_for_memory(per_page, 1 << 40) == 512                 # capped at the worst case
+    with pytest.raises(MemoryError, match="one request of max_model_len needs 64"):
+        cfg.pages_for_memory(per_page, 2 * 63 * per_page)
+    assert EngineConfig(max_num_seqs=8, max_model_len=1024).pages_for_memory(per_page, 1) == 512    # no fraction: worst case
+    with pytest.raises(ValueError, match="memory_fraction"):
+        EngineConfig(memory_fraction=1.5)

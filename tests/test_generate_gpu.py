@@ -290,3 +290,24 @@ def test_many_requests_at_once(setup, dtype):
                 checked += 1
             seq.append(tok)
     assert dtype == "fp32" or checked >= 40
+
+
+def test_pool_sized_from_the_free_memory(setup):
+    """`memory_fraction` instead of a page count: the pool gets what fits into that share of the memory that is free
+    (here a share so small that it is fewer pages than the worst case), and generation goes on as ever."""
+    from jax_vllm_b200 import SamplingParams, generate, make_driver
+    tag, folder, plain = setup
+    vocab, P = TINY[tag]["vocab_size"], PAGE_SIZE[tag]
+    model = load(folder, "fp32")
+    roomy = make_driver(model, max_num_seqs=3, max_model_len=8 * P, block_size=P)
+    assert roomy.num_blocks == 24
+    per_page = roomy.cache.bytes_per_page(4)
+    free = torch.cuda.mem_get_info()[0]
+    tight = make_driver(model, max_num_seqs=3, max_model_len=8 * P, block_size=P, memory_fraction=10.5 * per_page / free)
+    assert tight.num_blocks == tight.cache.num_pages == 10
+    prompts = [random_tokens(2 * P + 1, vocab, seed=500 + i) for i in range(3)]
+    sp = SamplingParams(max_new_tokens=2 * P)
+    assert generate(tight, prompts, sp) == generate(roomy, prompts, sp) == [plain.greedy(p, 2 * P) for p in prompts]
+    assert tight.stats.preemptions >= 1
+    with pytest.raises(MemoryError, match="one request of max_model_len"):
+        make_driver(model, max_num_seqs=3, max_model_len=8 * P, block_size=P, memory_fraction=3.5 * per_page / free)
