@@ -112,7 +112,8 @@ def main(argv=None) -> int:
         print(f"  {n} tok · ttft {ttft:.3f}s", flush=True)
     st = driver.stats
     print(f"{total} tok · {total / elapsed:.1f} tok/s · {elapsed:.2f}s · steps {st.steps} · "
-          f"prefix-hit tokens {st.cache_hit_tokens} · preemptions {st.preemptions}", flush=True)
+          f"prefix-hit tokens {st.cache_hit_tokens} · preemptions {st.preemptions} · "
+          f"most pages in use {st.max_pages_in_use} of {st.pages_total} · most tokens in a step {st.max_step_tokens}", flush=True)
     return 0
 
 

@@ -131,7 +131,14 @@ def _step_locked(driver: Driver) -> list:
     both = fused(entries, temps, seeds, counters) if fused is not None and len(sampled) == len(plan) else None
     logits = driver.runner.step(entries) if both is None else None
     sched.committed(plan)
-    driver.stats.steps += 1
+    st = driver.stats
+    st.steps += 1
+    st.last_step_tokens = sum(len(e.tokens) for e in entries)
+    st.max_step_tokens = max(st.max_step_tokens, st.last_step_tokens)
+    if driver.cache.groups:
+        st.pages_total = driver.cache.num_pages
+        st.pages_in_use = max(driver.cache.num_pages - g.pool.num_free for g in driver.cache.groups)
+        st.max_pages_in_use = max(st.max_pages_in_use, st.pages_in_use)
     events: list = []
     if not sampled:
         return events

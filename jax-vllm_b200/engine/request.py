@@ -66,3 +66,9 @@ class EngineStats:
     cache_hit_tokens: int = 0
     preemptions: int = 0
     finished: int = 0
+    # per step (the reference has no counterpart: its pool is always the worst case and its steps are padded)
+    last_step_tokens: int = 0         # tokens that the last step ran
+    max_step_tokens: int = 0
+    pages_in_use: int = 0             # after the last step, in the fullest pool
+    max_pages_in_use: int = 0
+    pages_total: int = 0

@@ -78,6 +78,9 @@ def test_generates_what_the_stand_in_dictates_and_frees_everything():
     outs = generate(d, prompts, SamplingParams(max_new_tokens=6))
     assert outs == [expected(p, 6) for p in prompts]
     assert not has_work(d) and not d.cache.live
+    st = d.stats
+    assert st.pages_total == d.cache.num_pages and 0 < st.max_pages_in_use <= st.pages_total
+    assert 0 < st.last_step_tokens <= st.max_step_tokens <= d.config.max_tokens_per_step
     d.cache.check()
     assert d.stats.emitted_tokens == 24 and d.stats.finished == 4 and d.stats.admissions == 4
 
