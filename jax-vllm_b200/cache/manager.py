@@ -9,9 +9,12 @@ as every position of a page lies before the window of the next query.
 
 Prefix reuse (jllm/engine/cache.py:20-57): full pages are hashed in a chain over the
 tokens; a new request takes the longest run of pages whose hashes are known, in every
-group, but always leaves at least its last token to compute.  It is switched off for
-models with a windowed group or with fixed-size state, where a page hit alone does not
-restore what a layer needs.
+group, but always leaves at least its last token to compute.  A group with a window needs
+only the pages that the window of the next query still reaches: the hit is the longest
+prefix whose pages are known from the start in every group without a window and over the
+last `window` positions in every group with one; the pages before that are entered as
+given back, as they would be had the request computed the prefix itself.  Reuse is
+switched off for models with fixed-size state, which a page hit does not restore.
 """
 
 from __future__ import annotations
@@ -122,8 +125,7 @@ class CacheManager:
             else:
                 raise TypeError(f"layer {layer}: unknown cache need {need!r}")
         self.slots = StateSlots(max_live)
-        self.prefix_cache = bool(prefix_cache) and not self.state_layers and \
-            all(g.need.window is None for g in self.groups)
+        self.prefix_cache = bool(prefix_cache) and not self.state_layers
         self.live: dict[object, RequestCache] = {}
         self.stats = {"prefix_hit_pages": 0, "prefix_hit_tokens": 0, "pages_allocated": 0, "pages_released": 0}
 
@@ -159,24 +161,39 @@ class CacheManager:
         self.live[request_id] = rc
         if self.prefix_cache and prompt is not None and self.groups:
             P = self.page_size
-            parent, hits = b"", []
+            parent, hashes, found = b"", [], []
             for i in range((len(prompt) - 1) // P):       # always leaves >= 1 token to compute
                 h = chain_hash(parent, prompt[i * P:(i + 1) * P])
                 pages = [grp.pool.lookup(h) for grp in self.groups]
-                if any(p is None for p in pages):
+                if any(p is None and grp.need.window is None for p, grp in zip(pages, self.groups)):
                     break
-                hits.append((h, pages))
+                hashes.append(h)
+                found.append(pages)
                 parent = h
-            for h, pages in hits:
-                for g, p in enumerate(pages):
-                    self.groups[g].pool.touch(p)
-                    rc.tables[g].append(p)
-                rc.hashes.append(h)
-            rc.num_tokens = len(hits) * P
+            n = len(hashes)                               # pages known from the start where there is no window
+            windowed = [g for g, grp in enumerate(self.groups) if grp.need.window is not None]
+            while n > 0 and not all(found[i][g] is not None for g in windowed
+                                    for i in range(self._first_page_needed(g, n * P), n)):
+                n -= 1
+            for g, grp in enumerate(self.groups):
+                first = self._first_page_needed(g, n * P)
+                for i in range(n):
+                    if i >= first:
+                        grp.pool.touch(found[i][g])
+                    rc.tables[g].append(found[i][g] if i >= first else -1)
+                rc.freed_upto[g] = first
+            rc.hashes = hashes[:n]
+            rc.num_tokens = n * P
             rc.tokens = list(prompt[:rc.num_tokens])
-            self.stats["prefix_hit_pages"] += len(hits)
+            self.stats["prefix_hit_pages"] += n
             self.stats["prefix_hit_tokens"] += rc.num_tokens
         return rc
+
+    def _first_page_needed(self, g: int, num_tokens: int) -> int:
+        """The first logical page of group g that a query at position >= num_tokens can still see: it sees keys at
+        positions > num_tokens - window, and all keys in a group without a window."""
+        w = self.groups[g].need.window
+        return 0 if w is None else max(0, num_tokens - w + 1) // self.page_size
 
     def pages_needed(self, rc: RequestCache, new_len: int) -> list:
         """Pages each group must still allocate so that positions < new_len have a page."""
@@ -218,12 +235,9 @@ class CacheManager:
                     grp.pool.register(rc.tables[g][i], h)
                 rc.hashes.append(h)
         for g, grp in enumerate(self.groups):
-            w = grp.need.window
-            if w is None:
+            if grp.need.window is None:
                 continue
-            # the next query is at position >= num_tokens and sees keys > num_tokens - w
-            first_needed = max(0, rc.num_tokens - w + 1)
-            upto = first_needed // P
+            upto = self._first_page_needed(g, rc.num_tokens)
             for i in range(rc.freed_upto[g], min(upto, len(rc.tables[g]))):
                 if rc.tables[g][i] >= 0:
                     grp.pool.release([rc.tables[g][i]])

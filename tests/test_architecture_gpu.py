@@ -138,6 +138,35 @@ def test_replay_of_the_toy_architecture_equals_plain(toy, dtype, tmp_path):
             assert sum(m["pages_released"] for m in rep.records[:-1]) >= 5
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_known_prefix_is_taken_over_where_the_window_still_reaches(toy, dtype, tmp_path):
+    """Prefix reuse with a windowed group: a second request that starts like a finished one takes its pages, in the
+    windowed layers only those the window of its first computed token reaches; the rest of its table says given back."""
+    from jax_vllm_b200.engine.replay import Replayer
+    folder, w32, cfg, seqs, want, windows = toy
+    again = seqs["r0"][:52] + random_tokens(25, TOY.vocab, seed=77)
+    first_wanted = 43                           # five pages of eight tokens lie before it
+    steps = [{"step": 0, "entries": [{"id": "r0", "tokens": seqs["r0"], "want": [69]}], "end": ["r0"]},
+             {"step": 1, "entries": [{"id": "r1", "tokens": seqs["r1"], "want": [32]}], "end": ["r1"]},
+             {"step": 2, "entries": [{"id": "again", "tokens": again[:60], "want": list(range(first_wanted, 60))}], "end": []},
+             {"step": 3, "entries": [{"id": "again", "tokens": again[60:], "want": list(range(len(again) - 60))}], "end": ["again"]}]
+    rep = Replayer(folder, dtype, tmp_path, max_tokens=128, page_size=8, prefix_cache=True)
+    assert rep.cache.prefix_cache is True
+    for s in steps[:3]:
+        rep.run_step(s)
+    rc = rep.cache.live["again"]
+    assert rep.records[2]["prefix_hit_tokens"] == 40 and rep.records[2]["tokens"] == 20
+    # the first computed token is at 40 and sees keys from 30 on in the windowed layers: of the five known pages only
+    # 3 and 4 were taken there; after the step (60 tokens, keys from 50 on) they and page 5 have been given back
+    assert rep.records[2]["pages_allocated"] == 3 + 3 and rep.records[2]["pages_released"] == 3
+    assert [p >= 0 for p in rc.tables[1]] == [False] * 6 + [True] * 2 and all(p >= 0 for p in rc.tables[0])
+    rep.run_step(steps[3])
+    rep.cache.check()
+    assert not rep.cache.live
+    want_all = dict(want, again=plain_layers(w32, cfg, again, TOY.order(), windows=windows, cache_from={TOY.reader: 0}))
+    compare(steps, tmp_path, TOY.vocab, want_all, dtype, case="toy architecture, prefix reuse under a window")
+
+
 def test_generation_of_the_toy_architecture_equals_plain(toy):
     from jax_vllm_b200 import SamplingParams, generate, load_from_path, make_driver
     folder, w32, cfg, seqs, want, windows = toy
@@ -153,5 +182,5 @@ def test_generation_of_the_toy_architecture_equals_plain(toy):
         return seq[len(prompt):]
 
     assert got == [plain_greedy(p) for p in prompts]
-    assert d.cache.prefix_cache is False            # a windowed group: known prefixes are not taken over
+    assert d.cache.prefix_cache is True             # a windowed group does not switch prefix reuse off
     d.cache.check()

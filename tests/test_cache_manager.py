@@ -10,6 +10,7 @@ from jax_vllm_b200.parts import FixedStateNeed, PagedKVNeed
 
 FULL = PagedKVNeed(2, 16)
 WIN = PagedKVNeed(2, 16, window=20)
+WIN8 = PagedKVNeed(2, 16, window=8)
 
 
 def test_alloc_order_and_reversed_release():
@@ -70,7 +71,8 @@ def test_groups_by_need_and_state_layers():
     m = CacheManager([FULL, WIN, FULL, None, FixedStateNeed((4, 3)), WIN], page_size=8, num_pages=10, max_live=2)
     assert [g.layers for g in m.groups] == [[0, 2], [1, 5]]
     assert m.layer_group == {0: 0, 2: 0, 1: 1, 5: 1} and list(m.state_layers) == [4]
-    assert m.prefix_cache is False          # a window and fixed state switch prefix reuse off
+    assert m.prefix_cache is False          # fixed state switches prefix reuse off
+    assert CacheManager([FULL, WIN], page_size=8, num_pages=10, max_live=2).prefix_cache is True
     assert m.bytes_per_page(2) == 2 * (2 * 2 * 8 * 2 * 16 * 2)
 
 
@@ -132,6 +134,48 @@ def test_prefix_reuse_hits_full_pages_but_leaves_a_token():
     m.check()
 
 
+def test_prefix_reuse_with_a_window_takes_only_the_pages_the_window_reaches():
+    m = CacheManager([FULL, WIN], page_size=4, num_pages=12, max_live=2)      # the window is 20 positions
+    toks = list(range(200, 241))            # ten full pages and a token
+    a = m.admit("a", toks)
+    m.grow(a, 41); m.commit(a, toks)
+    assert a.tables[1][:5] == [-1] * 5 and all(p >= 0 for p in a.tables[1][5:])   # keys before 41 - 20 + 1 = 22 are gone
+    b = m.admit("b", toks)
+    # ten pages hit; a query at 40 sees keys from 21 on: page 5 (positions 20..23) is the first one needed
+    assert b.num_tokens == 40 and b.tables[0] == a.tables[0][:10]
+    assert b.tables[1] == [-1] * 5 + a.tables[1][5:10] and b.freed_upto == [0, 5]
+    assert m.stats["prefix_hit_pages"] == 10 and m.stats["prefix_hit_tokens"] == 40
+    m.check()
+    m.grow(b, 41); m.commit(b, toks[40:])
+    assert b.tables[1][:6] == [-1] * 5 + [a.tables[1][5]]       # 41 - 20 + 1 = 22: page 5 is still needed
+    m.release("a"); m.release("b"); m.check()
+    # a shorter prompt with the same start: its window would reach pages that the window group gave back and that
+    # have been handed out again since, so the hit shrinks to what every group still has
+    c = m.admit("c", [1, 2, 3, 4] * 6); m.grow(c, 24); m.commit(c, [1, 2, 3, 4] * 6); m.release("c")
+    d = m.admit("d", toks[:25])
+    win_known = [m.groups[1].pool.lookup(h) is not None for h in a.hashes[:6]]
+    want = max(n for n in range(7) if all(win_known[max(0, n * 4 - 19) // 4:n]))
+    assert d.num_tokens == 4 * want and all((p >= 0) == (i >= max(0, 4 * want - 19) // 4) for i, p in enumerate(d.tables[1]))
+    m.check()
+    m.release("d"); m.check()
+    assert all(g.pool.num_free == 12 for g in m.groups)
+
+
+def test_prefix_reuse_with_windows_only():
+    m = CacheManager([WIN], page_size=4, num_pages=12, max_live=2)
+    toks = list(range(300, 333))
+    a = m.admit("a", toks); m.grow(a, 33); m.commit(a, toks)
+    b = m.admit("b", toks + [5, 6])         # eight pages known by hash; the window reaches back to page 3
+    assert b.num_tokens == 32 and b.tables[0] == [-1] * 3 + a.tables[0][3:8] and b.freed_upto == [3]
+    m.check()
+    c_prompt = toks[:13]                    # a hit of three pages would need pages 0..2, which were given back
+    m.release("a"); m.release("b"); m.check()
+    c = m.admit("c", c_prompt)
+    known = [m.groups[0].pool.lookup(h) is not None for h in a.hashes[:3]]
+    assert c.num_tokens == 4 * max(n for n in range(4) if all(known[:n]))
+    m.check()
+
+
 def test_eviction_drops_prefix():
     m = CacheManager([FULL], page_size=2, num_pages=3, max_live=2)
     a = m.admit("a", [1, 2, 3, 4, 5]); m.grow(a, 5); m.commit(a, [1, 2, 3, 4, 5]); m.release("a")
@@ -143,18 +187,23 @@ def test_eviction_drops_prefix():
 
 
 @pytest.mark.parametrize("seed", range(6))
-@pytest.mark.parametrize("needs,prefix", [([FULL, FULL], True), ([FULL, WIN], False), ([FULL], False)])
+@pytest.mark.parametrize("needs,prefix", [([FULL, FULL], True), ([FULL, WIN], False), ([FULL], False),
+                                          ([FULL, WIN], True), ([WIN, WIN8], True)])
 def test_random_orders_lose_no_page(seed, needs, prefix):
     rng = random.Random(seed)
     m = CacheManager(needs, page_size=4, num_pages=24, max_live=4, prefix_cache=prefix)
-    shared = [rng.randrange(50) for _ in range(16)]
+    shared = [rng.randrange(50) for _ in range(32)]
     live, next_id = {}, 0
     for _ in range(400):
         op = rng.random()
         if op < 0.25 and m.can_admit():
-            prompt = (shared[: rng.choice([0, 4, 8, 16])] + [rng.randrange(50) for _ in range(rng.randrange(1, 20))])
+            prompt = (shared[: rng.choice([0, 4, 8, 16, 32])] + [rng.randrange(50) for _ in range(rng.randrange(1, 20))])
             rc = m.admit(next_id, prompt)
             assert rc.num_tokens < len(prompt)
+            for g, grp in enumerate(m.groups):      # every page that the first query can see is there
+                first = 0 if grp.need.window is None else max(0, rc.num_tokens - grp.need.window + 1) // 4
+                assert len(rc.tables[g]) == rc.num_tokens // 4
+                assert all((p >= 0) == (i >= first) for i, p in enumerate(rc.tables[g]))
             live[next_id] = (rc, prompt)
             next_id += 1
         elif op < 0.85 and live:
@@ -187,6 +236,7 @@ def test_random_orders_lose_no_page(seed, needs, prefix):
     for rid in list(live):
         m.release(rid)
     m.check()
+    assert (m.stats["prefix_hit_pages"] > 0) == prefix
     assert all(g.pool.num_free == 24 for g in m.groups) and m.slots.num_free == 4
 
 
