@@ -184,3 +184,40 @@ def test_generation_of_the_toy_architecture_equals_plain(toy):
     assert got == [plain_greedy(p) for p in prompts]
     assert d.cache.prefix_cache is True             # a windowed group does not switch prefix reuse off
     d.cache.check()
+
+
+@pytest.mark.parametrize("seed", [0, 1, 2])
+def test_random_arrivals_with_few_pages_known_prefixes_and_a_window(toy, seed):
+    """Everything at once, through the entry point, in 32-bit where tokens must be equal: requests arrive at random
+    steps, many start alike (known prefixes are taken over, in the windowed layers only as far as the window reaches),
+    prompts are cut by a small token budget, the pool is too small for three requests (the youngest is preempted and
+    run again), pages come back as the window passes and are used again, decode-only steps replay captured graphs.
+    Greedy tokens depend on none of it."""
+    import random
+    from jax_vllm_b200 import SamplingParams, add_request, has_work, load_from_path, make_driver, step
+    folder, w32, cfg, seqs, want, windows = toy
+    rng = random.Random(seed)
+    model = load_from_path(folder, dtype="fp32")
+    d = make_driver(model, max_num_seqs=3, max_model_len=64, block_size=8, num_blocks=9, max_tokens_per_step=24)
+    shared = seqs["r2"][:40]
+    prompts = [shared[:rng.choice([0, 8, 17, 24])] + random_tokens(rng.randrange(1, 14), TOY.vocab, seed=100 * seed + i)
+               for i in range(10)]
+    new_tokens = [rng.randrange(6, 27) for _ in prompts]
+    waiting, ids = list(range(len(prompts))), {}
+    while waiting or has_work(d):
+        if waiting and (rng.random() < 0.4 or not has_work(d)):
+            i = waiting.pop(0)
+            ids[i] = add_request(d, prompts[i], SamplingParams(max_new_tokens=new_tokens[i]))
+        step(d)
+        d.cache.check()
+    assert not d.cache.live and all(g.pool.num_free == 9 for g in d.cache.groups)
+    assert d.stats.preemptions > 0 and d.stats.cache_hit_tokens > 0
+
+    def plain_greedy(prompt, n):
+        seq = list(prompt)
+        for _ in range(n):
+            seq.append(int(plain_layers(w32, cfg, seq, TOY.order(), windows=windows, cache_from={TOY.reader: 0})[-1].argmax()))
+        return seq[len(prompt):]
+
+    for i, prompt in enumerate(prompts):
+        assert d.requests[ids[i]].output_ids == plain_greedy(prompt, new_tokens[i]), f"request {i} of seed {seed}"
