@@ -530,6 +530,20 @@ def test_tcgen05_attention_long_prompt(ops):
     torch.testing.assert_close(got, want, **BF16_TOL)
 
 
+@pytest.mark.parametrize("far", [5, 9000, 20479])
+def test_tcgen05_attention_portions_deep_in_a_long_context(ops, far):
+    # portions that begin after tens of thousands of cached keys (block tables more than a thousand pages wide, more
+    # than a hundred and sixty key tiles a block), one of them with a key far back that its last query must find
+    got, want = run_attention(ops, torch.bfloat16, 8, 2, 128, 16, q_lens=[130, 64, 200], starts=[20400, 3, 8100],
+                              boost=(0, far), tc5=True)
+    torch.testing.assert_close(got, want, **BF16_TOL)
+
+
+def test_tcgen05_attention_prompt_of_several_thousand_tokens(ops):
+    got, want = run_attention(ops, torch.bfloat16, 4, 1, 128, 32, q_lens=[4100], starts=[0], tc5=True)
+    torch.testing.assert_close(got, want, **BF16_TOL)
+
+
 # ---- the tcgen05 decode kernel (bfloat16, head size 128, keys as tensor-core rows, persistent over all requests)
 @pytest.mark.parametrize("hq,hkv,page", [(4, 1, 16), (32, 8, 16), (8, 8, 8), (2, 1, 128), (16, 1, 32), (6, 2, 64), (5, 1, 16),
                                          (12, 1, 16)])
