@@ -22,13 +22,13 @@ from .batch import BatchBuilder, StepEntry
 
 
 @contextlib.contextmanager
-def _capture(graph):
-    """`torch.cuda.graph(graph)` with Python's cycle collector off: a collection that happened to run inside the
+def _capture(graph, pool=None):
+    """`torch.cuda.graph(graph, pool)` with Python's cycle collector off: a collection that happened to run inside the
     capture and freed CUDA objects of some other owner (an old driver's graphs, pinned buffers) would invalidate it."""
     was_on = gc.isenabled()
     gc.disable()
     try:
-        with torch.cuda.graph(graph):
+        with torch.cuda.graph(graph, pool=pool):
             yield
     finally:
         if was_on:
@@ -59,6 +59,10 @@ class Runner:
         self.cuda_graphs = bool(cuda_graphs) and max_model_len is not None
         self.max_graph_batch = max_graph_batch
         self.graphs: dict[int, _DecodeGraph] = {}
+        # All captured steps of this runner take their intermediate tensors from one pool: they never run at the same
+        # time, and nothing but a graph's result (which stays allocated) is read after its replay, so the graphs of
+        # all batch sizes together hold what the largest needs, not the sum.
+        self.graph_pool = None
         self.graphs_sampled: dict[int, _DecodeGraph] = {}
         self.graph_warm: set[int] = set()
         self._ahead = None                 # (requests and lengths, graph) of a batch already laid out in the staging buffer
@@ -102,6 +106,11 @@ class Runner:
         return all(len(e.tokens) == 1 and tuple(e.want) == (0,) and e.cache.num_tokens < self.max_model_len
                    for e in entries)
 
+    def _pool(self):
+        if self.graph_pool is None:
+            self.graph_pool = torch.cuda.graph_pool_handle()
+        return self.graph_pool
+
     def _graph_layout(self, entries):
         width = -(-self.max_model_len // self.cache.page_size)
         return self.builder.layout_for(entries, table_width=width)
@@ -132,7 +141,7 @@ class Runner:
             ctx = b.context(entries, layout, dev, max_seq_len=self.max_model_len)
             graph = torch.cuda.CUDAGraph()
             before = ops.launch_count
-            with _capture(graph):
+            with _capture(graph, self._pool()):
                 logits = self.model.forward(ctx, self.layer_caches)
             g = _DecodeGraph(layout, dev, logits, graph, ops.launch_count - before)
             ops.launch_count = before           # nothing ran yet: a replay counts them
@@ -187,11 +196,12 @@ class Runner:
                 temps_d = dev[samp_off + 4 * n:samp_off + 5 * n].view(torch.float32)
                 graph = torch.cuda.CUDAGraph()
                 before = ops.launch_count
-                with _capture(graph):
+                with _capture(graph, self._pool()):
                     logits = self.model.forward(ctx, self.layer_caches)
                     out[:n].copy_(ops.sample(logits, temps_d, seeds_d, counters_d))
                     out[n:].copy_(ops.status_word(self.device))
-                g.logits, g.graph, g.launches = logits, graph, ops.launch_count - before
+                    del logits                  # only `out` is read after a replay: the logits' memory serves later captures
+                g.graph, g.launches = graph, ops.launch_count - before
                 ops.launch_count = before       # nothing ran yet: a replay counts them
                 self.graphs_sampled[n] = g
                 self._ahead = None
