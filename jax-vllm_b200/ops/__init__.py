@@ -69,12 +69,13 @@ def _fn(lib: str, name: str, argtypes):
 
 
 _raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_raw_device = getattr(torch._C, "_cuda_getDevice", None)
 
 
 def _stream() -> int:
     """The current stream's handle: asked for before every launch, so by the short way where torch has one."""
-    if _raw_stream is not None:
-        return _raw_stream(torch.cuda.current_device())
+    if _raw_stream is not None and _raw_device is not None:
+        return _raw_stream(_raw_device())
     return torch.cuda.current_stream().cuda_stream
 
 
@@ -119,6 +120,17 @@ def status_word(device=None) -> torch.Tensor:
         w = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
         _status[idx] = w
     return w
+
+
+_status_ptrs: dict[int, int] = {}
+
+
+def _status_ptr(device: torch.device) -> int:
+    """Address of the status word of a tensor's device (what every launcher is given), without building anything."""
+    ptr = _status_ptrs.get(device.index)
+    if ptr is None:
+        ptr = _status_ptrs[device.index] = status_word(device).data_ptr()
+    return ptr
 
 
 def raise_on_status(value: int) -> None:
@@ -205,7 +217,7 @@ def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor | Non
     _cuda(out, "out", torch.float32)
     f = _fn("embed", "jv_embed_gather", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p])
     _check(f(table.data_ptr(), _code(table, "table"), ids.data_ptr(), out.data_ptr(), n, hidden, vocab,
-             status_word(table.device).data_ptr(), _stream()), "embed_gather")
+             _status_ptr(table.device), _stream()), "embed_gather")
     return out
 
 
@@ -231,7 +243,7 @@ def rmsnorm(h: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.
                                    c_int, c_int, c_int, c_float, c_int, c_longlong, c_void_p, c_void_p])
     _check(f(h.data_ptr(), _ptr(delta), 0 if delta is None else _code(delta, "delta"), _ptr(rows),
              weight.data_ptr(), _code(weight, "weight"), y.data_ptr(), _code(y, "out"), n_out, n_total, hidden,
-             float(eps), n_parts, part_stride, status_word(h.device).data_ptr(), _stream()), "rmsnorm")
+             float(eps), n_parts, part_stride, _status_ptr(h.device), _stream()), "rmsnorm")
     return y
 
 
@@ -327,7 +339,7 @@ def rope_kv(qkv: torch.Tensor, positions: torch.Tensor, token_entry: torch.Tenso
     _check(f(qkv.data_ptr(), _code(qkv, "qkv"), qkv.stride(0), positions.data_ptr(), token_entry.data_ptr(),
              block_table.data_ptr(), block_table.shape[1], _ptr(inv_freq), rot_dim, _ptr(q_norm_w), _ptr(k_norm_w),
              w_code, float(eps), _ptr(k_cache), _ptr(v_cache), n, n_q_heads, n_kv_heads, head_dim, page_size,
-             num_pages, status_word(qkv.device).data_ptr(), _stream()), "rope_kv")
+             num_pages, _status_ptr(qkv.device), _stream()), "rope_kv")
 
 
 # ------------------------------------------------------------------------ attention
@@ -361,7 +373,7 @@ def attn_simt(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cache: torch.
              k_cache.data_ptr(), v_cache.data_ptr(), block_table.data_ptr(), block_table.shape[1],
              cu_seqlens.data_ptr(), start_pos.data_ptr(), work.data_ptr(), n_work, n_q_heads, n_kv_heads, head_dim,
              k_cache.shape[1], k_cache.shape[0], int(window), float(scale), int(split_size), int(n_splits),
-             status_word(q.device).data_ptr(), _stream()), "attn_simt", launches=2 if n_splits > 0 else 1)
+             _status_ptr(q.device), _stream()), "attn_simt", launches=2 if n_splits > 0 else 1)
 
 
 MMA_HEAD_DIMS = (16, 32, 64, 128)      # head sizes the tensor-core attention kernels are instantiated for
@@ -420,7 +432,7 @@ def attn_mma(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cache: torch.T
              v_cache.data_ptr(), block_table.data_ptr(), block_table.shape[1], cu_seqlens.data_ptr(),
              start_pos.data_ptr(), work.data_ptr(), n_work, n_q_heads, n_kv_heads, head_dim, k_cache.shape[1],
              k_cache.shape[0], int(window), float(scale), int(split_size), int(n_splits),
-             status_word(q.device).data_ptr(), _stream()), "attn_mma")
+             _status_ptr(q.device), _stream()), "attn_mma")
 
 
 def attn_tcgen05_supports(dtype: torch.dtype, head_dim: int, n_q_heads: int, n_kv_heads: int, page_size: int,
@@ -452,7 +464,7 @@ def attn_tcgen05(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cache: tor
     _check(f(q.data_ptr(), q_stride, q.shape[0], out.data_ptr(), out.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),
              block_table.data_ptr(), block_table.shape[1], cu_seqlens.data_ptr(), start_pos.data_ptr(), work.data_ptr(),
              n_work, n_q_heads, n_kv_heads, head_dim, k_cache.shape[1], k_cache.shape[0], float(scale),
-             status_word(q.device).data_ptr(), _stream()), "attn_tcgen05")
+             _status_ptr(q.device), _stream()), "attn_tcgen05")
 
 
 DECODE_TCGEN05_MAX_REQUESTS = 512
@@ -528,7 +540,7 @@ def attn_decode_tcgen05(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cac
              counters.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_table.data_ptr(), block_table.shape[1],
              cu_seqlens.data_ptr(), start_pos.data_ptr(), work.data_ptr(), n_work, n_q_heads, n_kv_heads, head_dim,
              k_cache.shape[1], k_cache.shape[0], float(scale), n_blocks, 0 if prepare is None else 1, _ptr(inv_freq),
-             _ptr(q_w), _ptr(k_w), w_f32, float(eps), status_word(q.device).data_ptr(), _stream()),
+             _ptr(q_w), _ptr(k_w), w_f32, float(eps), _status_ptr(q.device), _stream()),
            "attn_decode_tcgen05")
 
 
@@ -557,7 +569,7 @@ _skinny_plans: dict = {}      # (device, N, K) -> parts of k per strip
 def linear_skinny_splits(device, n: int, k: int) -> int:
     """Into how many parts of k the kernel would best cut the strips of an [n, k] weight on this device
     (1: not at all): few strips, or strips that load the multiprocessors unevenly, are cut."""
-    key = (torch.device(device).index or 0, n, k)
+    key = ((device.index if isinstance(device, torch.device) else torch.device(device).index) or 0, n, k)
     plan = _skinny_plans.get(key)
     if plan is None:
         f = _build.load("linear_skinny").jv_linear_skinny_plan
@@ -601,7 +613,7 @@ _stream_plans: dict = {}
 def linear_stream_splits(device, n: int, k: int) -> int:
     """Into how many parts of k the product for 17 to 128 rows (csrc/linear_stream.cu) would best cut the
     128-row strips of an [n, k] weight on this device (1: not at all)."""
-    key = (torch.device(device).index or 0, n, k)
+    key = ((device.index if isinstance(device, torch.device) else torch.device(device).index) or 0, n, k)
     plan = _stream_plans.get(key)
     if plan is None:
         f = _build.load("linear_stream").jv_linear_stream_plan
@@ -631,7 +643,7 @@ def linear_stream(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype,
     f = _fn("linear_stream", "jv_linear_stream", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
                                                   c_int, c_void_p, c_int, c_void_p, c_void_p])
     _check(f(x.data_ptr(), x.stride(0), weight.data_ptr(), weight.stride(0), _ptr(y), DTYPE_CODE[out_dtype],
-             n if y is None else y.stride(0), m, n, k, _ptr(parts), splits, status_word(x.device).data_ptr(), _stream()),
+             n if y is None else y.stride(0), m, n, k, _ptr(parts), splits, _status_ptr(x.device), _stream()),
            "linear_stream")
     return y if parts is None else PartialSum(parts)
 
@@ -663,22 +675,28 @@ def gemm_tcgen05(x: torch.Tensor, weight: torch.Tensor, epilogue: str = "bf16") 
     f = _fn("gemm_tcgen05", "jv_gemm_tcgen05", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
                                                 c_int, c_void_p, c_void_p])
     _check(f(x.data_ptr(), x.stride(0), weight.data_ptr(), weight.stride(0), y.data_ptr(), y.stride(0), m, n, k, code,
-             status_word(x.device).data_ptr(), _stream()), "gemm_tcgen05")
+             _status_ptr(x.device), _stream()), "gemm_tcgen05")
     return y
 
 
 _sm_counts: dict = {}
 
 
+_strips_fill: dict = {}
+
+
 def _strips_fill_the_device(device, n: int) -> bool:
     """Whether the 128-row strips of a weight of n rows, uncut, keep the multiprocessors busy (0.85 of them over
     the rounds it takes): the tcgen05 product for larger batches takes a weight whole only then."""
-    idx = torch.device(device).index or 0
-    sms = _sm_counts.get(idx)
-    if sms is None:
-        sms = _sm_counts[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
-    strips = -(-n // 128)
-    return strips >= 0.85 * sms * -(-strips // sms)
+    idx = (device.index if isinstance(device, torch.device) else torch.device(device).index) or 0
+    fills = _strips_fill.get((idx, n))
+    if fills is None:
+        sms = _sm_counts.get(idx)
+        if sms is None:
+            sms = _sm_counts[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
+        strips = -(-n // 128)
+        fills = _strips_fill[(idx, n)] = strips >= 0.85 * sms * -(-strips // sms)
+    return fills
 
 
 def _skinny_ok(x: torch.Tensor, weight: torch.Tensor) -> bool:
