@@ -2,23 +2,27 @@
 // scores and output accumulate in tensor memory (TMEM), queries, keys and values come in by TMA in the
 // 128-byte-swizzle layout that tcgen05.mma reads.
 //
-// A block handles up to 128 rows = (token, query head) pairs of ONE kv head (row r -> token r / HPT, head
+// A work item is up to 128 rows = (token, query head) pairs of ONE kv head (row r -> token r / HPT, head
 // r % HPT, HPT = query heads per kv head, any number up to 16: 128 / HPT tokens, the rows that are left over
-// when HPT does not divide 128 are computed and thrown away), against 128-key tiles:
-//   warp 0   key producer: reads the block table, issues the TMA loads of the query tile (once) and of the key
-//            tiles (one 4-D box per page and half of the head: [page slots, 64] elements);
+// when HPT does not divide 128 are computed and thrown away), against 128-key tiles.  Blocks are persistent,
+// one per multiprocessor: block b takes the items b, 2G-1-b, 2G+b, ... of the list ordered longest first (G
+// blocks; back and forth, so that every block gets long and short ones), and the roles run through the tiles
+// of all their items as one sequence, so that an item's first keys, its queries and its first scores are under
+// way while the item before it is still in its softmax and its output leaves:
+//   warp 0   key producer: reads the block table, issues the TMA loads of an item's query tile (two buffers)
+//            and of the key tiles (one 4-D box per page and half of the head: [page slots, 64] elements);
 //   warp 10  value producer: the same for the value tiles (a stage of values is free much later than a stage
 //            of keys, and one warp that waits for both holds the keys back);
 //   warp 1   one thread issues S = Q K^T (8 x tcgen05.mma 128x128x16 over the head) into one of two score
 //            buffers in TMEM, and O += P V (8 x mma over the keys; P is read from TMEM, V is the MN-major
 //            operand from shared memory), after the softmax warps have written P (bfloat16) to TMEM;
 //   warps 2..9  softmax, two threads per row: read the scores from TMEM, mask, running (max, sum) in 32-bit,
-//            exp2, write P; when a row's maximum has moved, rescale O in TMEM first.  At the end O / sum is
-//            written out.
-// The score buffer of tile j+1 is filled while the softmax of tile j runs.  Shared memory moves 128 bytes a
-// clock, which a 128x128x16 product with both operands there needs all by itself: P therefore never goes
-// through shared memory.  Every mbarrier wait is bounded by a clock deadline and reports to the status word
-// instead of spinning.
+//            exp2, write P; when a row's maximum has moved, rescale O in TMEM first.  At an item's end O / sum
+//            leaves through the item's query buffer and a TMA store.
+// The score buffer of the next tile (of this item or the next) is filled while the softmax of a tile runs.
+// Shared memory moves 128 bytes a clock, which a 128x128x16 product with both operands there needs all by
+// itself: P therefore never goes through shared memory.  Every mbarrier wait is bounded by a clock deadline and
+// reports to the status word instead of spinning.
 //
 // Restrictions (the caller falls back to the mma.sync kernel otherwise): bfloat16, head size 128, no
 // window, HPT up to 16, page size a power of two from 8 to 128.
@@ -34,7 +38,7 @@ namespace {
 constexpr int D = 128, ROWS = 128, BN = 128;
 constexpr int TILE_BYTES = 128 * 128 * 2;       // a 128 x 128 bfloat16 tile: two halves of [128 rows][128 bytes]
 constexpr int HALF_BYTES = 128 * 128;            // one half: 128 rows of 128 bytes
-constexpr int KV_STAGES = 3;
+constexpr int K_STAGES = 2, V_STAGES = 3, Q_BUFFERS = 2;   // 7 tiles of 32 KB
 constexpr int THREADS = 352;                     // key producer warp, mma warp, 8 softmax warps, value producer warp
 constexpr int SOFTMAX_THREADS = 256;
 constexpr int TMEM_COLS = 512;                   // S0: [0,128)  S1: [128,256)  O: [256,384)  P0: [384,448)  P1: [448,512)
@@ -45,7 +49,7 @@ struct Params {
   __nv_bfloat16* out; int out_stride;
   const int* block_table; int table_width;
   const int* cu_seqlens; const int* start_pos; const int* work;
-  int n_q_heads, n_kv_heads, page_size, num_pages, hpt, tokens_per_tile;
+  int n_work, n_q_heads, n_kv_heads, page_size, num_pages, hpt, tokens_per_tile;
   float scale_log2;
   int* status;
 };
@@ -187,13 +191,21 @@ __device__ __forceinline__ bool pair_barrier_or(int quad, bool flag) {
 __device__ __forceinline__ void pair_barrier(int quad) { asm volatile("bar.sync %0, 64;\n" ::"r"(quad + 1) : "memory"); }
 
 struct Shared {
-  uint64_t q_full, k_full[KV_STAGES], k_empty[KV_STAGES], v_full[KV_STAGES], v_empty[KV_STAGES];
+  uint64_t q_full[Q_BUFFERS], q_free[Q_BUFFERS], k_full[K_STAGES], k_empty[K_STAGES], v_full[V_STAGES], v_empty[V_STAGES];
   uint64_t s_full[2], p_full[2], o_done[2];
+  uint64_t o_free;              // the softmax threads have read an item's output: the next item's may be written
   uint64_t drain;               // used only after a wait ran out (see the tear-down)
   uint32_t tmem_base;
   int failed;                   // a role gave up on a wait
-  int armed[2][KV_STAGES];      // parity of the phase that the key (0) / value (1) producer armed last on a stage; -1: never
+  int armed_q[Q_BUFFERS], armed_k[K_STAGES], armed_v[V_STAGES];   // parity of the phase a producer armed last; -1: never
   float xch[2][128];            // a row's two softmax threads exchange their maxima (and at the end their sums)
+};
+
+// One work item as every role sees it.
+struct Item {
+  int entry, kv_head, q_first;      // request of the batch, kv head, first row of the tile among all tokens
+  int tokens_here, pos_first;       // tokens in the tile, position of the first
+  int j_hi, n_tiles;                // keys [0, j_hi) are visible to the last row; key tiles
 };
 
 __global__ void __launch_bounds__(THREADS, 1) attn_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map,
@@ -201,42 +213,51 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tcgen05_kernel(const __grid_c
                                                                   const __grid_constant__ CUtensorMap v_map,
                                                                   const __grid_constant__ CUtensorMap out_map,
                                                                   const Params p) {
-  pdl_trigger();      // a kernel launched behind this one (decode attention of the same step) may take the multiprocessors that the last blocks leave free
+  pdl_trigger();      // a kernel launched behind this one (decode attention of the same step) may take the multiprocessors that the first blocks to end leave free
   extern __shared__ unsigned char smem_raw[];
   unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  unsigned char* q_s = base;                                   // [2 halves of d][128 rows][128 B]
-  unsigned char* k_s = q_s + TILE_BYTES;                       // [stages][2 halves of d][128 keys][128 B]
-  unsigned char* v_s = k_s + KV_STAGES * TILE_BYTES;           // [stages][2 halves of d][128 keys][128 B]
-  Shared* sh = reinterpret_cast<Shared*>(v_s + KV_STAGES * TILE_BYTES);
+  unsigned char* q_s = base;                                   // [buffers][2 halves of d][128 rows][128 B]
+  unsigned char* k_s = q_s + Q_BUFFERS * TILE_BYTES;           // [stages][2 halves of d][128 keys][128 B]
+  unsigned char* v_s = k_s + K_STAGES * TILE_BYTES;            // [stages][2 halves of d][128 keys][128 B]
+  Shared* sh = reinterpret_cast<Shared*>(v_s + V_STAGES * TILE_BYTES);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-
-  // longest blocks first, over all heads: the work list is in ascending order of the tile's first token, and
-  // blocks start in the order of their linear index
-  const int linear = blockIdx.x + gridDim.x * blockIdx.y;
-  const int item = gridDim.x - 1 - linear / p.n_kv_heads;
-  const int kv_head = linear % p.n_kv_heads;
-  const int entry = p.work[2 * item], q_off = p.work[2 * item + 1];
   const int G = p.n_q_heads / p.n_kv_heads, HPT = p.hpt;
-  const int q_begin = p.cu_seqlens[entry];
-  const int q_len = p.cu_seqlens[entry + 1] - q_begin;
-  const int ctx = p.start_pos[entry];
-  const int tokens_here = min(p.tokens_per_tile, q_len - q_off);
-  const int pos_first = ctx + q_off;
-  const int j_hi = pos_first + tokens_here;          // keys [0, j_hi) are visible to the last row
-  const int n_tiles = (j_hi + BN - 1) / BN;
+  const int n_items = p.n_work * p.n_kv_heads, n_blocks = gridDim.x;
+
+  // The items of this block: in round r the blocks take the items r G .. r G + G - 1 of the list ordered longest
+  // first (the work list is in ascending order of a tile's first token, so from its end), in the order of their
+  // numbers in even rounds and against it in odd ones.  -1: this block has none in that round.
+  auto item_of_round = [&](int r) -> int {
+    const int L = r * n_blocks + ((r & 1) ? n_blocks - 1 - (int)blockIdx.x : (int)blockIdx.x);
+    return L < n_items ? L : -1;
+  };
+  const int n_rounds = (n_items + n_blocks - 1) / n_blocks;
+  auto load_item = [&](int L) -> Item {
+    Item it;
+    const int w = p.n_work - 1 - L / p.n_kv_heads;
+    it.kv_head = L % p.n_kv_heads;
+    it.entry = p.work[2 * w];
+    const int q_off = p.work[2 * w + 1];
+    const int q_begin = p.cu_seqlens[it.entry];
+    const int q_len = p.cu_seqlens[it.entry + 1] - q_begin;
+    it.q_first = q_begin + q_off;
+    it.tokens_here = min(p.tokens_per_tile, q_len - q_off);
+    it.pos_first = p.start_pos[it.entry] + q_off;
+    it.j_hi = it.pos_first + it.tokens_here;
+    it.n_tiles = it.tokens_here > 0 ? (it.j_hi + BN - 1) / BN : 0;
+    return it;
+  };
 
   if (threadIdx.x == 0) {
-    mbar_init(&sh->q_full, 1);
-    for (int s = 0; s < KV_STAGES; ++s) {
-      mbar_init(&sh->k_full[s], 1); mbar_init(&sh->k_empty[s], 1);
-      mbar_init(&sh->v_full[s], 1); mbar_init(&sh->v_empty[s], 1);
-    }
+    for (int b = 0; b < Q_BUFFERS; ++b) { mbar_init(&sh->q_full[b], 1); mbar_init(&sh->q_free[b], 1); sh->armed_q[b] = -1; }
+    for (int s = 0; s < K_STAGES; ++s) { mbar_init(&sh->k_full[s], 1); mbar_init(&sh->k_empty[s], 1); sh->armed_k[s] = -1; }
+    for (int s = 0; s < V_STAGES; ++s) { mbar_init(&sh->v_full[s], 1); mbar_init(&sh->v_empty[s], 1); sh->armed_v[s] = -1; }
     mbar_init(&sh->s_full[0], 1); mbar_init(&sh->s_full[1], 1);
     mbar_init(&sh->p_full[0], SOFTMAX_THREADS); mbar_init(&sh->p_full[1], SOFTMAX_THREADS);
     mbar_init(&sh->o_done[0], 1); mbar_init(&sh->o_done[1], 1);
+    mbar_init(&sh->o_free, SOFTMAX_THREADS);
     mbar_init(&sh->drain, 1);
     sh->failed = 0;
-    for (int s = 0; s < KV_STAGES; ++s) sh->armed[0][s] = sh->armed[1][s] = -1;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   __syncthreads();
@@ -255,118 +276,186 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tcgen05_kernel(const __grid_c
   const uint32_t tmem = (warp >= 1 && warp <= 9) ? sh->tmem_base : 0u;
   const uint32_t tmem_o = tmem + TMEM_O;
 
-  if (tokens_here > 0) {
-    if (warp == 0 || warp == 10) {
-      // --------------------------------------------------------------- producers
-      const int which = warp == 0 ? 0 : 1;                        // keys or values
-      pdl_wait();                         // queries, keys and values are the work of the kernels before this one
+  if (warp == 0 || warp == 10) {
+    // --------------------------------------------------------------- producers
+    const int which = warp == 0 ? 0 : 1;                        // keys (and queries) or values
+    const int stages = which ? V_STAGES : K_STAGES;
+    pdl_wait();                         // queries, keys and values are the work of the kernels before this one
+    const int P = p.page_size, pages_per_tile = BN / P;
+    uint64_t* full_bars = which ? sh->v_full : sh->k_full;
+    uint64_t* empty_bars = which ? sh->v_empty : sh->k_empty;
+    int* armed = which ? sh->armed_v : sh->armed_k;
+    unsigned char* tiles = which ? v_s : k_s;
+    const CUtensorMap* map = which ? &v_map : &k_map;
+    bool ok = true;
+    int gt = 0, n = 0;                  // tiles and items of this block so far
+    for (int r = 0; r < n_rounds && ok; ++r) {
+      const int L = item_of_round(r);
+      if (L < 0) continue;
+      const Item it = load_item(L);
+      if (it.n_tiles == 0) continue;
       if (which == 0 && lane == 0) {
-        mbar_expect_tx(&sh->q_full, 2 * 128 * G * p.tokens_per_tile);      // two boxes of 64 d x G heads x tokens
-        tma_load_3d(q_s, &q_map, 0, kv_head * G, q_begin + q_off, &sh->q_full);
-        tma_load_3d(q_s + HALF_BYTES, &q_map, 64, kv_head * G, q_begin + q_off, &sh->q_full);
+        const int qb = n % Q_BUFFERS, ph = (n / Q_BUFFERS) & 1;
+        ok = mbar_wait(&sh->q_free[qb], ph ^ 1);                 // the item two before this one has left through this buffer
+        if (ok) {
+          sh->armed_q[qb] = ph;
+          mbar_expect_tx(&sh->q_full[qb], 2 * 128 * G * p.tokens_per_tile);      // two boxes of 64 d x G heads x tokens
+          tma_load_3d(q_s + qb * TILE_BYTES, &q_map, 0, it.kv_head * G, it.q_first, &sh->q_full[qb]);
+          tma_load_3d(q_s + qb * TILE_BYTES + HALF_BYTES, &q_map, 64, it.kv_head * G, it.q_first, &sh->q_full[qb]);
+        }
       }
-      const int P = p.page_size, pages_per_tile = BN / P;
+      ok = __shfl_sync(0xffffffffu, ok, 0);
       // page ids of a tile: lane i reads the i-th (a tile has at most 16 pages); -1 = no page needed or none there
       auto tile_pages = [&](int j) -> int {
         const int pi = j * pages_per_tile + lane;
         int page = -1;
-        if (j < n_tiles && lane < pages_per_tile && pi * P < j_hi && pi < p.table_width) {
-          page = p.block_table[(size_t)entry * p.table_width + pi];
+        if (j < it.n_tiles && lane < pages_per_tile && pi * P < it.j_hi && pi < p.table_width) {
+          page = p.block_table[(size_t)it.entry * p.table_width + pi];
           if (page < 0 || page >= p.num_pages) { atomicOr(p.status, JV_STATUS_BAD_PAGE); page = -1; }
         }
         return page;
       };
-      uint64_t* full_bars = which ? sh->v_full : sh->k_full;
-      uint64_t* empty_bars = which ? sh->v_empty : sh->k_empty;
-      unsigned char* tiles = which ? v_s : k_s;
-      const CUtensorMap* map = which ? &v_map : &k_map;
       // the block-table entries of a tile are read while the tile before it is loaded
       int pages = tile_pages(0);
-      bool ok = true;
-      for (int j = 0; j < n_tiles && ok; ++j) {
+      for (int j = 0; j < it.n_tiles && ok; ++j, ++gt) {
         const int pages_next = tile_pages(j + 1);
-        const int s = j % KV_STAGES, ph = (j / KV_STAGES) & 1;
+        const int s = gt % stages, ph = (gt / stages) & 1;
         unsigned char* dst = tiles + s * TILE_BYTES;
         const int n_pages = __popc(__ballot_sync(0xffffffffu, pages >= 0));
         if (lane == 0) {
           ok = mbar_wait(&empty_bars[s], ph ^ 1);
-          if (ok) { sh->armed[which][s] = ph; mbar_expect_tx(&full_bars[s], n_pages * P * 128 * 2); }
+          if (ok) { armed[s] = ph; mbar_expect_tx(&full_bars[s], n_pages * P * 128 * 2); }
         }
         ok = __shfl_sync(0xffffffffu, ok, 0);      // also orders the announcement before the copies
         // lane i issues the two boxes of page i
         if (ok && pages >= 0) {
-          tma_load_4d(dst + lane * P * 128, map, 0, kv_head, 0, pages, &full_bars[s]);
-          tma_load_4d(dst + HALF_BYTES + lane * P * 128, map, 64, kv_head, 0, pages, &full_bars[s]);
+          tma_load_4d(dst + lane * P * 128, map, 0, it.kv_head, 0, pages, &full_bars[s]);
+          tma_load_4d(dst + HALF_BYTES + lane * P * 128, map, 64, it.kv_head, 0, pages, &full_bars[s]);
         }
         pages = pages_next;
       }
-      if (!ok && lane == 0) { atomicOr(p.status, JV_STATUS_WAIT_EXPIRED); sh->failed = 1; }
-    } else if (warp == 1) {
-      // -------------------------------------------------------------- mma issuer
-      if (lane == 0) {
-        bool ok = mbar_wait(&sh->q_full, 0);
-        const uint64_t q_desc0 = desc_k_major(smem_u32(q_s)), q_desc1 = desc_k_major(smem_u32(q_s + HALF_BYTES));
-        uint64_t k_desc[KV_STAGES][2], v_desc[KV_STAGES];
+      ++n;
+    }
+    if (!ok && lane == 0) { atomicOr(p.status, JV_STATUS_WAIT_EXPIRED); sh->failed = 1; }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- mma issuer
+    if (lane == 0) {
+      uint64_t q_desc[Q_BUFFERS][2], k_desc[K_STAGES][2], v_desc[V_STAGES];
 #pragma unroll
-        for (int st = 0; st < KV_STAGES; ++st) {
-          k_desc[st][0] = desc_k_major(smem_u32(k_s + st * TILE_BYTES));
-          k_desc[st][1] = desc_k_major(smem_u32(k_s + st * TILE_BYTES + HALF_BYTES));
-          v_desc[st] = desc_mn_major(smem_u32(v_s + st * TILE_BYTES));
-        }
-        auto issue_qk = [&](int j) -> bool {                   // S[j % 2] = Q K_j^T
-          const int s = j % KV_STAGES;
-          if (!mbar_wait(&sh->k_full[s], (j / KV_STAGES) & 1)) return false;
-          TC_FENCE_AFTER();
-          const uint64_t k0 = k_desc[s][0], k1 = k_desc[s][1];
-          const uint32_t tmem_s = tmem + (j & 1) * 128;
-#pragma unroll
-          for (int kk = 0; kk < 4; ++kk) umma(tmem_s, q_desc0 + 2 * kk, k0 + 2 * kk, IDESC_QK, kk != 0);
-#pragma unroll
-          for (int kk = 0; kk < 4; ++kk) umma(tmem_s, q_desc1 + 2 * kk, k1 + 2 * kk, IDESC_QK, 1);
-          umma_commit(&sh->k_empty[s]);
-          umma_commit(&sh->s_full[j & 1]);
-          return true;
-        };
-        if (ok) ok = issue_qk(0);
-        for (int j = 0; j < n_tiles && ok; ++j) {
-          if (j + 1 < n_tiles) ok = issue_qk(j + 1);           // the next scores while this tile's softmax runs
-          if (!ok) break;
-          const int s = j % KV_STAGES;
-          if (!mbar_wait(&sh->p_full[j & 1], (j >> 1) & 1) || !mbar_wait(&sh->v_full[s], (j / KV_STAGES) & 1)) { ok = false; break; }
-          TC_FENCE_AFTER();
-          // O += P V_j : 8 steps of 16 keys; P from tensor memory (8 columns a step), V MN-major
-          const uint32_t tmem_p = tmem + TMEM_P + (j & 1) * 64;
-#pragma unroll
-          for (int kk = 0; kk < 8; ++kk)   // 16 keys further: 8 columns of P, 16 rows (2048 bytes) down V
-            umma_a_tmem(tmem_o, tmem_p + kk * 8, v_desc[s] + kk * (16 * 128 / 16), IDESC_PV, (j | kk) != 0);
-          umma_commit(&sh->v_empty[s]);
-          umma_commit(&sh->o_done[j & 1]);
-        }
-        if (!ok) { atomicOr(p.status, JV_STATUS_WAIT_EXPIRED); sh->failed = 1; }
+      for (int b = 0; b < Q_BUFFERS; ++b) {
+        q_desc[b][0] = desc_k_major(smem_u32(q_s + b * TILE_BYTES));
+        q_desc[b][1] = desc_k_major(smem_u32(q_s + b * TILE_BYTES + HALF_BYTES));
       }
-    } else {
-      // ----------------------------------------------------------------- softmax
-      // Two threads per row: warps 2..5 take the first 64 keys of a tile (and the first 64 columns of O),
-      // warps 6..9 the other 64.  A warp reads the 32 TMEM lanes of its number modulo 4.
-      const int quad = warp & 3;
-      const int half = (warp - 2) >> 2;
-      const int r = quad * 32 + lane;                           // this thread's row of the tile
-      const int t = r / HPT, hh = r % HPT;
-      const bool row_ok = t < tokens_here && hh < G;
+#pragma unroll
+      for (int st = 0; st < K_STAGES; ++st) {
+        k_desc[st][0] = desc_k_major(smem_u32(k_s + st * TILE_BYTES));
+        k_desc[st][1] = desc_k_major(smem_u32(k_s + st * TILE_BYTES + HALF_BYTES));
+      }
+#pragma unroll
+      for (int st = 0; st < V_STAGES; ++st) v_desc[st] = desc_mn_major(smem_u32(v_s + st * TILE_BYTES));
+      // Where this thread stands in the block's sequence of tiles: round, item number, tile of the item, its tiles.
+      // The item after the current one is looked up when the current one begins, so that the loads for it have
+      // long arrived when its first scores are due (while the current item's last softmax runs).
+      struct At { int r, n, j, nt; };
+      struct Ahead { int r, nt; };
+      auto find_from = [&](int r) -> Ahead {                    // the first round from r on that holds an item with tiles
+        for (; r < n_rounds; ++r) {
+          const int L = item_of_round(r);
+          if (L < 0) continue;
+          const int nt = load_item(L).n_tiles;
+          if (nt > 0) return Ahead{r, nt};
+        }
+        return Ahead{n_rounds, 0};
+      };
+      Ahead peek = find_from(0);
+      At cur{peek.r, 0, 0, peek.nt};
+      if (cur.r < n_rounds) peek = find_from(cur.r + 1);
+      auto after = [&](const At& a) -> At {
+        if (a.j + 1 < a.nt) return At{a.r, a.n, a.j + 1, a.nt};
+        const At b{peek.r, a.n + 1, 0, peek.nt};
+        if (b.r < n_rounds) peek = find_from(b.r + 1);
+        return b;
+      };
+      auto issue_qk = [&](const At& a, int gt) -> bool {          // S[gt % 2] = Q K^T for tile gt of the sequence
+        const int qb = a.n % Q_BUFFERS, s = gt % K_STAGES;
+        if (a.j == 0 && !mbar_wait(&sh->q_full[qb], (a.n / Q_BUFFERS) & 1)) return false;
+        if (!mbar_wait(&sh->k_full[s], (gt / K_STAGES) & 1)) return false;
+        TC_FENCE_AFTER();
+        const uint64_t q0 = q_desc[qb][0], q1 = q_desc[qb][1], k0 = k_desc[s][0], k1 = k_desc[s][1];
+        const uint32_t tmem_s = tmem + (gt & 1) * 128;
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) umma(tmem_s, q0 + 2 * kk, k0 + 2 * kk, IDESC_QK, kk != 0);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) umma(tmem_s, q1 + 2 * kk, k1 + 2 * kk, IDESC_QK, 1);
+        umma_commit(&sh->k_empty[s]);
+        umma_commit(&sh->s_full[gt & 1]);
+        return true;
+      };
+      bool ok = true;
+      if (cur.r < n_rounds) ok = issue_qk(cur, 0);
+      for (int gt = 0; cur.r < n_rounds && ok; ++gt) {
+        const At nxt = after(cur);
+        if (nxt.r < n_rounds) ok = issue_qk(nxt, gt + 1);          // the next scores while this tile's softmax runs
+        if (!ok) break;
+        const int s = gt % V_STAGES;
+        if (!mbar_wait(&sh->p_full[gt & 1], (gt >> 1) & 1) || !mbar_wait(&sh->v_full[s], (gt / V_STAGES) & 1)) { ok = false; break; }
+        // an item's first product overwrites the output of the item before it, which its softmax threads must have read
+        if (cur.j == 0 && cur.n > 0 && !mbar_wait(&sh->o_free, (cur.n - 1) & 1)) { ok = false; break; }
+        TC_FENCE_AFTER();
+        // O += P V_j : 8 steps of 16 keys; P from tensor memory (8 columns a step), V MN-major
+        const uint32_t tmem_p = tmem + TMEM_P + (gt & 1) * 64;
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)   // 16 keys further: 8 columns of P, 16 rows (2048 bytes) down V
+          umma_a_tmem(tmem_o, tmem_p + kk * 8, v_desc[s] + kk * (16 * 128 / 16), IDESC_PV, (cur.j | kk) != 0);
+        umma_commit(&sh->v_empty[s]);
+        umma_commit(&sh->o_done[gt & 1]);
+        cur = nxt;
+      }
+      if (!ok) { atomicOr(p.status, JV_STATUS_WAIT_EXPIRED); sh->failed = 1; }
+    }
+  } else {
+    // ----------------------------------------------------------------- softmax
+    // Two threads per row: warps 2..5 take the first 64 keys of a tile (and the first 64 columns of O),
+    // warps 6..9 the other 64.  A warp reads the 32 TMEM lanes of its number modulo 4.
+    const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;
+    const int row = quad * 32 + lane;                           // this thread's row of the tile
+    const int t = row / HPT, hh = row % HPT;
+    const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
+    constexpr float LAZY = 8.f;
+    bool ok = true;
+    int gt = 0, n = 0;
+    int stored = -1;              // thread 64: the query buffer whose TMA store has been started but not yet waited for
+    // the numbers of the next item are asked for while the current one runs (two dependent loads from global memory)
+    auto next_item = [&](int& r, Item& out) -> bool {
+      for (; r < n_rounds; ++r) {
+        const int L = item_of_round(r);
+        if (L < 0) continue;
+        out = load_item(L);
+        if (out.n_tiles > 0) return true;
+      }
+      return false;
+    };
+    int r_next = 0;
+    Item upcoming;
+    bool more = next_item(r_next, upcoming);
+    while (more) {
+      const Item it = upcoming;
+      ++r_next;
+      more = next_item(r_next, upcoming);
+      const int n_tiles = it.n_tiles, j_hi = it.j_hi, pos_first = it.pos_first;
+      const bool row_ok = t < it.tokens_here && hh < G;
       const int pos = row_ok ? pos_first + t : -1;
-      const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
       // m_ref is the reference maximum that the exponentials are taken against.  It follows the true
       // maximum lazily: only when the maximum has grown by more than 2^8 (in the exponent) is O rescaled,
       // which is rare after the first tiles; until then probabilities may exceed 1 by at most that factor.
       float m_ref = -INFINITY, l_run = 0.f;
-      constexpr float LAZY = 8.f;
-      bool ok = true;
-      // A wait that runs out makes `ok` false for the whole warp; the loop then only keeps its appointments at
-      // the named barrier (so that nobody is left waiting there) and does no further work.
-      for (int j = 0; j < n_tiles; ++j) {
-        if (ok) ok = mbar_wait(&sh->s_full[j & 1], (j >> 1) & 1);
+      // A wait that runs out makes `ok` false for the whole warp; the loops then only keep their appointments at
+      // the named barriers (so that nobody is left waiting there) and do no further work.
+      for (int j = 0; j < n_tiles; ++j, ++gt) {
+        if (ok) ok = mbar_wait(&sh->s_full[gt & 1], (gt >> 1) & 1);
         ok = __all_sync(0xffffffffu, ok);
-        const uint32_t s_addr = tmem + lane_addr + (j & 1) * 128 + half * 64;
+        const uint32_t s_addr = tmem + lane_addr + (gt & 1) * 128 + half * 64;
         const int key0 = j * BN + half * 64;                     // first key of this thread's 64
         const bool need_mask = j * BN + BN > j_hi || j * BN + BN - 1 > pos_first;   // block-uniform
         uint32_t sr[2][32];
@@ -377,7 +466,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tcgen05_kernel(const __grid_c
           tmem_ld32_issue(s_addr + 32, sr[1]);
           tmem_ld_wait();
           // masking is a loop of its own behind a branch that the whole block takes or not: only the last
-          // tile of a block has keys to hide
+          // tile of an item has keys to hide
           if (need_mask) {
             const int last = min(pos, j_hi - 1) - key0;          // the last of this thread's 64 keys that counts
 #pragma unroll
@@ -400,9 +489,9 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tcgen05_kernel(const __grid_c
         const bool outgrown = ok && my_max != -INFINITY && (m_ref == -INFINITY || (my_max - m_ref) * p.scale_log2 > LAZY);
         float alpha = 1.f;
         if (pair_barrier_or(quad, outgrown)) {
-          sh->xch[half][r] = my_max;
+          sh->xch[half][row] = my_max;
           pair_barrier(quad);
-          const float m_tile = fmaxf(sh->xch[0][r], sh->xch[1][r]);
+          const float m_tile = fmaxf(sh->xch[0][row], sh->xch[1][row]);
           pair_barrier(quad);                                        // both have read before a later tile writes
           if (ok && m_tile != -INFINITY && (m_ref == -INFINITY || (m_tile - m_ref) * p.scale_log2 > LAZY)) {
             alpha = (m_ref == -INFINITY) ? 0.f : fast_exp2((m_ref - m_tile) * p.scale_log2);
@@ -412,7 +501,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tcgen05_kernel(const __grid_c
         const float m_scaled = (m_ref == -INFINITY) ? 0.f : m_ref * p.scale_log2;
         // ---- O is rescaled only if some row of this warp moved its reference; the previous P V must be complete then
         if (ok && j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
-          ok = __all_sync(0xffffffffu, mbar_wait(&sh->o_done[(j - 1) & 1], ((j - 1) >> 1) & 1));
+          ok = __all_sync(0xffffffffu, mbar_wait(&sh->o_done[(gt - 1) & 1], ((gt - 1) >> 1) & 1));
           if (ok) {
             TC_FENCE_AFTER();
 #pragma unroll 1
@@ -425,8 +514,8 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tcgen05_kernel(const __grid_c
             }
           }
         }
-        // this tile's P buffer (in tensor memory) was read by the product of tile j-2, which was issued before
-        // the scores of tile j: their arrival has told that it is complete
+        // this tile's P buffer (in tensor memory) was read by the product of the tile two before it, which was issued
+        // before the scores of this tile: their arrival has told that it is complete
         if (!ok) continue;
         // ---- probabilities: pairs of scores in packed 32-bit arithmetic, as bfloat16 pairs into this thread's 32
         // columns of the P buffer (column c of a row holds its keys 2c and 2c+1)
@@ -449,13 +538,13 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tcgen05_kernel(const __grid_c
             }
           unpack2(sum2[0], sum[0], sum[1]);
           unpack2(sum2[1], sum[2], sum[3]);
-          tmem_st32_bits(tmem + lane_addr + TMEM_P + (j & 1) * 64 + half * 32, pw);
+          tmem_st32_bits(tmem + lane_addr + TMEM_P + (gt & 1) * 64 + half * 32, pw);
         }
         l_run = l_run * alpha + ((sum[0] + sum[1]) + (sum[2] + sum[3]));
-        // ---- in the last tile the value rows past the end become zero (they may hold anything)
+        // ---- in an item's last tile the value rows past the end become zero (they may hold anything)
         if (j == n_tiles - 1 && j_hi < j * BN + BN) {
-          const int s = j % KV_STAGES;
-          ok = __all_sync(0xffffffffu, mbar_wait(&sh->v_full[s], (j / KV_STAGES) & 1));
+          const int s = gt % V_STAGES;
+          ok = __all_sync(0xffffffffu, mbar_wait(&sh->v_full[s], (gt / V_STAGES) & 1));
           if (ok) {
             for (int i = (threadIdx.x - 64); i < (j * BN + BN - j_hi) * 16; i += SOFTMAX_THREADS) {
               const int key_row = (j_hi - j * BN) + i / 16, part = i % 16;     // 16 chunks of 16 bytes per row (both halves)
@@ -467,65 +556,74 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tcgen05_kernel(const __grid_c
         if (!ok) continue;
         if (j == n_tiles - 1) PROXY_FENCE();                     // the zeroed rows visible to the tensor core
         TC_FENCE_BEFORE();                                       // P is in tensor memory before the arrival
-        mbar_arrive(&sh->p_full[j & 1]);
-      }
-      // ---- output: O / sum, each thread its 64 columns; the row's sum is the two threads' together
-      sh->xch[half][r] = l_run;
-      pair_barrier(quad);
-      const float l_row = sh->xch[0][r] + sh->xch[1][r];
-      const bool got = ok && mbar_wait(&sh->o_done[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1);
-      const float inv = row_ok ? 1.f / l_row : 0.f;
-      if (tokens_here == p.tokens_per_tile) {
-        // A whole tile leaves through shared memory (where the queries were: every product has completed) and one
-        // TMA store per half of the head; threads that write their 128 bytes to rows 8 KB apart in memory take
-        // five times as long.
-        if (got) {
-          TC_FENCE_AFTER();
-          unsigned char* row_base = q_s + half * HALF_BYTES + r * 128;
-#pragma unroll 1
-          for (int c = 0; c < 2; ++c) {
-            float v[32];
-            tmem_ld32(tmem_o + lane_addr + half * 64 + c * 32, v);
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              uint4 pk;
-              __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&pk);
-#pragma unroll
-              for (int e = 0; e < 4; ++e) h2[e] = __floats2bfloat162_rn(v[q * 8 + 2 * e] * inv, v[q * 8 + 2 * e + 1] * inv);
-              const int chunk = c * 4 + q;                       // 16-byte chunk within the 128-byte row
-              *reinterpret_cast<uint4*>(row_base + ((chunk ^ (r & 7)) << 4)) = pk;
-            }
-          }
-        }
-        PROXY_FENCE();
-        asm volatile("bar.sync 5, 256;\n" ::: "memory");
-        if (threadIdx.x == 64) {
-          tma_store_3d(&out_map, q_s, 0, kv_head * G, q_begin + q_off);
-          tma_store_3d(&out_map, q_s + HALF_BYTES, 64, kv_head * G, q_begin + q_off);
-          asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
+        mbar_arrive(&sh->p_full[gt & 1]);
+        if (stored >= 0) {
+          // the output of the item before this one has long been read out of its query buffer by now: the buffer
+          // may take the queries of the item after this one
           asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory");
+          mbar_arrive(&sh->q_free[stored]);
+          stored = -1;
         }
-      } else if (got) {
+      }
+      // ---- the item's output: O / sum, each thread its 64 columns; the row's sum is the two threads' together
+      const int g_last = gt - 1, qb = n % Q_BUFFERS;
+      sh->xch[half][row] = l_run;
+      pair_barrier(quad);
+      const float l_row = sh->xch[0][row] + sh->xch[1][row];
+      pair_barrier(quad);                                        // both have read before the next item's first tile writes
+      const bool got = ok && mbar_wait(&sh->o_done[g_last & 1], (g_last >> 1) & 1);
+      const float inv = row_ok ? 1.f / l_row : 0.f;
+      const bool whole = it.tokens_here == p.tokens_per_tile;
+      // A whole tile leaves through shared memory (where the item's queries were: every product with them has
+      // completed) and one TMA store per half of the head; threads that write their 128 bytes to rows 8 KB apart in
+      // memory take five times as long.
+      unsigned char* row_base = q_s + qb * TILE_BYTES + half * HALF_BYTES + row * 128;
+      __nv_bfloat16* dst = p.out + (size_t)(it.q_first + t) * p.out_stride + (size_t)(it.kv_head * G + hh) * D + half * 64;
+      if (got) {
         TC_FENCE_AFTER();
-        __nv_bfloat16* dst = p.out + (size_t)(q_begin + q_off + t) * p.out_stride + (size_t)(kv_head * G + hh) * D + half * 64;
 #pragma unroll 1
         for (int c = 0; c < 2; ++c) {
           float v[32];
           tmem_ld32(tmem_o + lane_addr + half * 64 + c * 32, v);
-          if (row_ok) {
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              uint4 pk;
-              __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&pk);
+          for (int q = 0; q < 4; ++q) {
+            uint4 pk;
+            __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&pk);
 #pragma unroll
-              for (int e = 0; e < 4; ++e) h2[e] = __floats2bfloat162_rn(v[q * 8 + 2 * e] * inv, v[q * 8 + 2 * e + 1] * inv);
-              *reinterpret_cast<uint4*>(dst + c * 32 + q * 8) = pk;
-            }
+            for (int e = 0; e < 4; ++e) h2[e] = __floats2bfloat162_rn(v[q * 8 + 2 * e] * inv, v[q * 8 + 2 * e + 1] * inv);
+            const int chunk = c * 4 + q;                       // 16-byte chunk within the 128-byte row
+            if (whole) *reinterpret_cast<uint4*>(row_base + ((chunk ^ (row & 7)) << 4)) = pk;
+            else if (row_ok) *reinterpret_cast<uint4*>(dst + c * 32 + q * 8) = pk;
           }
         }
+        TC_FENCE_BEFORE();
+        mbar_arrive(&sh->o_free);                                // this thread has read its part of the output
       }
-      if (!got && lane == 0) { atomicOr(p.status, JV_STATUS_WAIT_EXPIRED); sh->failed = 1; }
+      if (whole) {
+        PROXY_FENCE();
+        asm volatile("bar.sync 5, 256;\n" ::: "memory");
+        if (threadIdx.x == 64) {
+          if (got) {
+            // started here, waited for after the next item's first tile (or at the end): this thread's warp is not held up
+            tma_store_3d(&out_map, q_s + qb * TILE_BYTES, 0, it.kv_head * G, it.q_first);
+            tma_store_3d(&out_map, q_s + qb * TILE_BYTES + HALF_BYTES, 64, it.kv_head * G, it.q_first);
+            asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
+            stored = qb;
+          } else {
+            mbar_arrive(&sh->q_free[qb]);
+          }
+        }
+      } else if (threadIdx.x == 64) {
+        mbar_arrive(&sh->q_free[qb]);                            // nothing left through the buffer
+      }
+      if (!got) ok = false;
+      ++n;
     }
+    if (stored >= 0) {                                           // shared memory must have been read before the block ends
+      asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory");
+      mbar_arrive(&sh->q_free[stored]);
+    }
+    if (!ok && lane == 0) { atomicOr(p.status, JV_STATUS_WAIT_EXPIRED); sh->failed = 1; }
   }
 
   TC_FENCE_BEFORE();
@@ -534,12 +632,15 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tcgen05_kernel(const __grid_c
     // a wait ran out: products already issued may still write tensor memory and copies already asked for still land
     // in this block's shared memory; both get a bounded time to finish before tensor memory is freed and the block ends
     if (warp == 1 && lane == 0) drain_products_after_failure(&sh->drain);
-    if ((warp == 0 || warp == 10) && lane == 0) {
-      const int which = warp == 0 ? 0 : 1;
-      if (which == 0) drain_copies_after_failure(&sh->q_full, 0);
-      for (int s = 0; s < KV_STAGES; ++s)
-        if (sh->armed[which][s] >= 0) drain_copies_after_failure(which ? &sh->v_full[s] : &sh->k_full[s], sh->armed[which][s]);
+    if (warp == 0 && lane == 0) {
+      for (int b = 0; b < Q_BUFFERS; ++b)
+        if (sh->armed_q[b] >= 0) drain_copies_after_failure(&sh->q_full[b], sh->armed_q[b]);
+      for (int s = 0; s < K_STAGES; ++s)
+        if (sh->armed_k[s] >= 0) drain_copies_after_failure(&sh->k_full[s], sh->armed_k[s]);
     }
+    if (warp == 10 && lane == 0)
+      for (int s = 0; s < V_STAGES; ++s)
+        if (sh->armed_v[s] >= 0) drain_copies_after_failure(&sh->v_full[s], sh->armed_v[s]);
     __syncthreads();
   }
   if (warp == 1) {
@@ -612,14 +713,23 @@ JV_EXPORT int jv_attn_tcgen05(const void* q, int q_stride, int n_tokens, void* o
   }
   Params p;
   p.out = (__nv_bfloat16*)out; p.out_stride = out_stride; p.block_table = block_table; p.table_width = table_width;
-  p.cu_seqlens = cu_seqlens; p.start_pos = start_pos; p.work = work; p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads;
+  p.cu_seqlens = cu_seqlens; p.start_pos = start_pos; p.work = work; p.n_work = n_work; p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads;
   p.page_size = page_size; p.num_pages = num_pages; p.hpt = G; p.tokens_per_tile = ROWS / G;
   p.scale_log2 = scale * LOG2E; p.status = status;
-  constexpr size_t smem = TILE_BYTES * (1 + 2 * KV_STAGES) + sizeof(Shared) + 1024;
+  constexpr size_t smem = TILE_BYTES * (Q_BUFFERS + K_STAGES + V_STAGES) + sizeof(Shared) + 1024;
   static bool ready[JV_MAX_DEVICES];
   if (!jv_once_per_device(ready, [&] {
         return cudaFuncSetAttribute(attn_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess;
       }))
     return JV_ERR_UNSUPPORTED;
-  return jv_launch(attn_tcgen05_kernel, dim3(n_work, n_kv_heads), dim3(THREADS), smem, stream, q_map, k_map, v_map, out_map, p);
+  // persistent blocks: one per multiprocessor (or per item, if there are fewer)
+  static int sm_count[JV_MAX_DEVICES];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= JV_MAX_DEVICES) return JV_ERR_UNSUPPORTED;
+  if (sm_count[dev] == 0 &&
+      (cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count[dev] <= 0))
+    sm_count[dev] = 148;
+  const long long items = (long long)n_work * n_kv_heads;
+  const int blocks = items < sm_count[dev] ? (int)items : sm_count[dev];
+  return jv_launch(attn_tcgen05_kernel, dim3(blocks), dim3(THREADS), smem, stream, q_map, k_map, v_map, out_map, p);
 }
