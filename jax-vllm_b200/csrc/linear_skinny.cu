@@ -197,24 +197,38 @@ int multiprocessors() {
   return sms;
 }
 
+// How evenly `n_strips` strips cut into `s` parts of k load the device, between 0 and 1: the useful share of the
+// busiest multiprocessor's time (blocks go to multiprocessors in turn; a multiprocessor's load is the units of its
+// blocks).
+double load_evenness(int n_strips, int K, int sms, int s) {
+  const int chunks = (K + KC - 1) / KC;
+  const long long units = (long long)n_strips * s, slots = (long long)sms * CTAS_PER_SM;
+  const long long blocks = units < slots ? units : slots;
+  long long worst = 0;
+  for (int sm = 0; sm < sms && sm < blocks; ++sm) {
+    long long load = 0;
+    for (long long b = sm; b < blocks; b += sms) load += (units - 1 - b) / blocks + 1;
+    if (load > worst) worst = load;
+  }
+  const int per_warp = (chunks + WARPS * s - 1) / (WARPS * s);
+  const double used = (double)chunks / ((double)per_warp * WARPS * s);   // the last part may reach past K
+  return used * (double)units / ((double)worst * sms);
+}
+
+// The useful share of the busiest block's time when the strips are not cut: 1 while every strip has a block of its
+// own; with a few strips more than resident blocks, the blocks that take a second strip run on alone when the
+// others are done (448 strips for 444 blocks: 0.50).
+double rounds_evenness(int n_strips, int sms) {
+  const long long units = n_strips, slots = (long long)sms * CTAS_PER_SM;
+  const long long blocks = units < slots ? units : slots;
+  return (double)units / ((double)((units + blocks - 1) / blocks) * blocks);
+}
+
 // Into how many parts the k of a strip is cut: the smallest number, up to 8, that loads the multiprocessors
 // evenly (each unit keeps at least two 64-wide chunks per warp), if that gains a tenth or more over uncut strips.
 int choose_splits(int n_strips, int K, int sms) {
   const int chunks = (K + KC - 1) / KC;
-  auto efficiency = [&](int s) {
-    const long long units = (long long)n_strips * s, slots = (long long)sms * CTAS_PER_SM;
-    const long long blocks = units < slots ? units : slots;
-    // blocks go to multiprocessors in turn; a multiprocessor's load is the units of its blocks
-    long long worst = 0;
-    for (int sm = 0; sm < sms && sm < blocks; ++sm) {
-      long long load = 0;
-      for (long long b = sm; b < blocks; b += sms) load += (units - 1 - b) / blocks + 1;
-      if (load > worst) worst = load;
-    }
-    const int per_warp = (chunks + WARPS * s - 1) / (WARPS * s);
-    const double used = (double)chunks / ((double)per_warp * WARPS * s);   // the last part may reach past K
-    return used * (double)units / ((double)worst * sms);
-  };
+  auto efficiency = [&](int s) { return load_evenness(n_strips, K, sms, s); };
   int best = 1;
   double best_eff = efficiency(1);
   const double floor_gain = best_eff * 1.03;
@@ -259,6 +273,10 @@ JV_EXPORT int jv_linear_skinny_max_rows() { return 16; }
 
 // Into how many parts the kernel would best cut the k of a strip for an [N, K] weight on this device (1: not at all).
 JV_EXPORT int jv_linear_skinny_plan(int N, int K) { return choose_splits((N + 15) / 16, K, multiprocessors()); }
+
+// How evenly the uncut strips of a weight of N rows fill the rounds of this device's resident blocks, in thousandths
+// (see `rounds_evenness`): what a caller that wants one tensor gets.
+JV_EXPORT int jv_linear_skinny_fill(int N) { return (int)(1000.0 * rounds_evenness((N + 15) / 16, multiprocessors())); }
 
 // X: [M, K] bfloat16 rows of ldx elements; W: [N, K] bfloat16 rows of ldw.  splits == 1: Y [M, N] rows of ldy,
 // bfloat16 (out_dtype 1) or float (0).  splits > 1 (at most 8, each part at least 8 chunks of 64): Y is not

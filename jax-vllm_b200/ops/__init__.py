@@ -580,6 +580,28 @@ def linear_skinny_splits(device, n: int, k: int) -> int:
     return plan
 
 
+# Where the caller wants one tensor, the kernel's strips are not cut, and a number of strips just above a multiple of
+# the resident blocks leaves most of them idle for a second round: below this evenness (the useful share of the busiest
+# block's time, csrc/linear_skinny.cu) the library's product is taken instead.  7,168 x 5,120 (448 strips for 444
+# blocks): 0.50 and 20.4 against 14.1 us; 6,144 x 4,096: 1; 10,240 x 5,120: 0.72 and 22.6 against 21.8 us alone,
+# where starting under the kernel before still favours the kernel.
+SKINNY_MIN_EVENNESS = 0.6
+_skinny_fill: dict = {}
+
+
+def linear_skinny_evenness(device, n: int) -> float:
+    """How evenly the uncut 16-row strips of a weight of n rows fill the rounds of this device's resident blocks
+    (1: every strip has a block of its own, or the rounds are full)."""
+    key = ((device.index if isinstance(device, torch.device) else torch.device(device).index) or 0, n)
+    fill = _skinny_fill.get(key)
+    if fill is None:
+        f = _build.load("linear_skinny").jv_linear_skinny_fill
+        f.argtypes, f.restype = [c_int], c_int
+        with torch.cuda.device(key[0]):
+            fill = _skinny_fill[key] = f(n) / 1000.0
+    return fill
+
+
 def linear_skinny(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype, parts_ok: bool = False):
     """x [M <= 16, K] times weight [N, K] transposed, bfloat16 operands, 32-bit accumulation
     (csrc/linear_skinny.cu); the result is bfloat16 or float32, or with `parts_ok`, where the kernel cuts k
@@ -721,7 +743,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None 
     if _stream_ok(x, weight) and x.shape[0] <= STREAM_BEST_ROWS and out_dtype in (torch.bfloat16, torch.float32) and \
             (parts_ok or _strips_fill_the_device(x.device, weight.shape[0])):
         return linear_stream(x, weight, out_dtype, parts_ok)
-    if _skinny_ok(x, weight):
+    if _skinny_ok(x, weight) and (parts_ok or linear_skinny_evenness(x.device, weight.shape[0]) >= SKINNY_MIN_EVENNESS):
         return linear_skinny(x, weight, out_dtype, parts_ok)
     if out_dtype == torch.bfloat16:
         return torch.mm(x, weight.t())

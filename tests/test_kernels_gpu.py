@@ -172,6 +172,23 @@ def test_linear_stream_parts_of_a_sum(ops, m, n, k):
     ops.check_status()
 
 
+def test_dispatcher_leaves_a_few_strips_too_many_to_the_library(ops):
+    """One tensor wanted, few rows: 448 strips of 16 rows for 444 resident blocks would leave all but four blocks idle
+    for a second round, so the dispatcher takes the library's product there; the result is the same product."""
+    assert ops.linear_skinny_evenness(DEV, 6144) == 1.0 and ops.linear_skinny_evenness(DEV, 96) == 1.0
+    assert ops.linear_skinny_evenness(DEV, 7168) < ops.SKINNY_MIN_EVENNESS < ops.linear_skinny_evenness(DEV, 10240)
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(8, 512, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(7168, 512, generator=g) / 512 ** 0.5).to(torch.bfloat16).to(DEV)
+    before = ops.launch_count
+    y = ops.linear(x, w, torch.bfloat16)
+    assert ops.launch_count == before                      # not a kernel of this package
+    torch.testing.assert_close(y.double(), x.double() @ w.double().T, atol=2e-2, rtol=2e-2)
+    y2 = ops.linear(x, w[:6144], torch.bfloat16)
+    assert ops.launch_count == before + 1
+    torch.testing.assert_close(y2.double(), x.double() @ w[:6144].double().T, atol=2e-2, rtol=2e-2)
+
+
 def test_linear_skinny_cuts_k_when_strips_are_few(ops):
     # few strips of a long k are cut into parts that other blocks take; many strips, or a short k, are not
     assert ops.linear_skinny_splits(DEV, 4096, 12288) > 1
