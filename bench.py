@@ -257,7 +257,7 @@ def micro(spec: str, reps: int, eager: bool = False) -> int:
     gemm:<N>x<K>:<M>:<impl>  the prompt product, impl = tcgen05 | tcgen05_swiglu | library (cuBLAS)
     linear:<N>x<K>:<M>[:parts][:stream|:skinny|:library]   the decode product of M rows with an [N, K] weight (several weights in turn):
                          as the engine picks it, or the tcgen05 kernel, the mma.sync kernel, cuBLAS
-    attn_decode:<B>:<CTX>[:<SPLIT>[:<PAGE>[:<KV HEADS>]]]   split decode attention of B requests with CTX cached tokens (8B head layout,
+    attn_decode:<B>:<CTX>[:<SPLIT>[:<PAGE>[:<KV HEADS>[:<QUERY HEADS PER KV HEAD>]]]]   split decode attention of B requests with CTX cached tokens (8B head layout,
                          several caches in turn so that none stays in the L2), mma.sync kernel
     attn_decode_tcgen05:<B>:<CTX>[:<SPLIT>[:<PAGE>]]   the same with the tcgen05 kernel
     (the decode kernels are timed as replays of a CUDA graph of one launch per cache, as the engine runs them)
@@ -312,7 +312,7 @@ def micro(spec: str, reps: int, eager: bool = False) -> int:
             split = int(rest[2]) if len(rest) > 2 else 256
             page = int(rest[3]) if len(rest) > 3 else PAGE
             if len(rest) > 4:
-                hkv = int(rest[4]); hq = 4 * hkv
+                hkv = int(rest[4]); hq = (int(rest[5]) if len(rest) > 5 else 4) * hkv
             q_lens = [1] * b
         else:
             b, ctx, q_lens = 1, 0, [int(rest[0])]
