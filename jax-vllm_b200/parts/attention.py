@@ -117,11 +117,17 @@ class Attention(Part):
         self.attend(qkv, out, step, cache, table)
         return ops.linear(out, self.w_o, dt, parts_ok=True)    # maybe the parts of a sum, for the next norm to add
 
+    # The decode kernel prepares a pair's queries in one warp, head after head; the separate kernel spreads the heads
+    # of all tokens over the device.  Up to this many query heads per kv head the launch that the kernel saves is
+    # worth more (a decode step at batch 8: 3 % faster with 2, equal with 4, 3 % slower with 5 and with 8).
+    PREPARE_IN_DECODE_KERNEL_UP_TO = 4
+
     def _decode_kernel_prepares(self, cache, n_dec) -> bool:
         """Whether the tcgen05 decode kernel takes these tokens together with their preparation (it rotates whole
         heads only)."""
-        return (ops.attn_decode_tcgen05_supports(self.ctx.dtype, self.d, self.hq, self.hkv, cache.k.shape[1], self.window,
-                                                 n_dec)
+        return (self.hq // self.hkv <= self.PREPARE_IN_DECODE_KERNEL_UP_TO
+                and ops.attn_decode_tcgen05_supports(self.ctx.dtype, self.d, self.hq, self.hkv, cache.k.shape[1], self.window,
+                                                     n_dec)
                 and (self.position is None or self.position.dim == self.d))
 
     def attend(self, qkv, out, step, cache, table):
