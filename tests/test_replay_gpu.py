@@ -22,7 +22,7 @@ from tests.util import PAGE_SIZE, TINY, collect, make_folder, portions, prefix_t
 pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parent.parent
 LENGTHS = {"a": [70, 45, 100, 33], "b": [90, 38, 64, 51], "c": [200, 70, 300, 130], "d": [61, 40, 83, 35],
-           "e": [200, 70, 300, 130]}
+           "e": [200, 70, 300, 130], "f": [180, 66, 270, 110]}
 ABSOLUTE_UPTO = 50.0      # logits up to this size are held to 1e-4 absolute in 32-bit
 
 
@@ -37,7 +37,7 @@ def limits(dtype, want: torch.Tensor):
     return 3e-2 * max(1.0, size)
 
 
-@pytest.fixture(scope="module", params=["a", "b", "c", "d", "e"])
+@pytest.fixture(scope="module", params=["a", "b", "c", "d", "e", "f"])
 def setup(request, tmp_path_factory):
     tag = request.param
     folder = make_folder(tmp_path_factory.mktemp(f"model_{tag}"), tag, seed=3)
@@ -45,7 +45,7 @@ def setup(request, tmp_path_factory):
     seqs = {f"r{i}": random_tokens(n, TINY[tag]["vocab_size"], seed=10 + i) for i, n in enumerate(LENGTHS[tag])}
     want = {rid: plain.logits(t) for rid, t in seqs.items()}
     assert all(w.abs().max() > 1.0 for w in want.values())     # logits of order one, not a flat model
-    if tag in ("c", "e"):
+    if tag in ("c", "e", "f"):
         # the product with the gate in its epilogue is taken from 1,024 rows on; these prompts are shorter, so
         # for this configuration the bar is lowered and portions of 17 tokens or more go through it
         from jax_vllm_b200.parts.feed_forward import GatedMLP
@@ -132,8 +132,8 @@ def test_portions_of_changing_size(setup, dtype, sizes, tmp_path):
 
 REST = 1 << 20      # "all that is left of the request"
 # A portion that fills at least one 128-row tile of the tcgen05 prompt attention (64 tokens with 2 query heads per
-# kv head, 32 with 4) for the configurations that take it, beside single tokens of other requests in the same step.
-TILE_AND_MORE = {"c": (69, 130), "e": (37, 70)}
+# kv head, 32 with 4, 25 with 5) for the configurations that take it, beside single tokens of other requests in the same step.
+TILE_AND_MORE = {"c": (69, 130), "e": (37, 70), "f": (29, 55)}
 FIRST_WANTED_OF_R4 = 33      # with prefix reuse r4's first portion wants its logits from here on (its start is r0's)
 
 
@@ -209,7 +209,7 @@ def test_mixed_requests_in_reused_pages(setup, dtype, reuse, tmp_path):
         assert whole_tiles(meta[5]) >= 3 and meta[5]["single_token_entries"] == 2
 
 
-GROUP = {"c": 2, "e": 4}     # query heads per kv head of the configurations with head size 128
+GROUP = {"c": 2, "e": 4, "f": 5}     # query heads per kv head of the configurations with head size 128
 
 
 def test_schedules_agree_with_each_other_in_32_bit(setup, tmp_path):

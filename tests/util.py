@@ -34,8 +34,14 @@ TINY_D = dict(architectures=["Qwen3ForCausalLM"], vocab_size=301, hidden_size=12
 TINY_E = dict(architectures=["Qwen3ForCausalLM"], vocab_size=320, hidden_size=512, intermediate_size=1024,
               num_hidden_layers=2, num_attention_heads=32, num_key_value_heads=8, head_dim=128, rms_norm_eps=1e-6,
               rope_theta=1e6, max_position_embeddings=1024, tie_word_embeddings=False)
-TINY = {"a": TINY_A, "b": TINY_B, "c": TINY_C, "d": TINY_D, "e": TINY_E}
-PAGE_SIZE = {"a": 16, "b": 8, "c": 16, "d": 4, "e": 16}
+# A sixth one with five query heads per kv head, as the 14B shape has them: a number that does not divide the 128 rows
+# of a tile (25 tokens a tile, three rows left over), more heads per group than the decode kernel prepares itself
+# (the separate kernel runs before it), pages of 32 tokens.
+TINY_F = dict(architectures=["Qwen3ForCausalLM"], vocab_size=310, hidden_size=320, intermediate_size=640,
+              num_hidden_layers=2, num_attention_heads=10, num_key_value_heads=2, head_dim=128, rms_norm_eps=2e-6,
+              rope_theta=3e5, max_position_embeddings=1024, tie_word_embeddings=True)
+TINY = {"a": TINY_A, "b": TINY_B, "c": TINY_C, "d": TINY_D, "e": TINY_E, "f": TINY_F}
+PAGE_SIZE = {"a": 16, "b": 8, "c": 16, "d": 4, "e": 16, "f": 32}
 
 
 def tensor_shapes(c: dict) -> dict:
