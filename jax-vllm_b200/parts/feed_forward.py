@@ -50,9 +50,11 @@ class GatedMLP(Part):
 
     # The gate is applied in the epilogue of the tcgen05 product once its 128 x 256 tiles are at least this many per
     # multiprocessor; with fewer, too many multiprocessors idle in the last round and the library product followed by
-    # the gate kernel is faster (measured at 24,576 x 4,096 on 148 multiprocessors: equal at 1,024 rows = 5.2 tiles
-    # each, 7 % ahead at 2,048 rows, 20 % behind at 64).  FUSED_GATE_ROWS, if set, is a plain row count instead (tests).
-    FUSED_GATE_TILES_PER_SM = 5.0
+    # the gate kernel is faster.  Measured on 148 multiprocessors, this product against the library's plus the gate
+    # kernel, microseconds: 24,576 x 4,096 at 1,024 rows (5.2 tiles each) 165 / 159, at 2,048 rows (10.4) 291 / 307;
+    # 34,816 x 5,120 at 1,024 rows (7.4) 275 / 268, at 2,048 rows (14.7) 501 / 507; 51,200 x 5,120 at 1,024 rows (10.8)
+    # 388 / 390, at 2,048 rows (21.6) 731 / 728.  FUSED_GATE_ROWS, if set, is a plain row count instead (tests).
+    FUSED_GATE_TILES_PER_SM = 9.0
     FUSED_GATE_ROWS = None
 
     def _fuse_gate(self, rows: int) -> bool:

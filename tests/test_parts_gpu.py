@@ -147,7 +147,7 @@ def test_feed_forward_bf16_with_the_gate_in_the_product(rows):
     w = {n: (torch.randn(ts.shape, generator=g) * 0.2).to(torch.bfloat16) for n, ts in ff.tensor_specs().items()}
     ff.bind({k: v.to(DEV) for k, v in w.items()})
     assert ff.block == 128
-    assert not ff._fuse_gate(4096)           # 32 x 3 tiles are far fewer than five per multiprocessor
+    assert not ff._fuse_gate(4096)           # 32 x 3 tiles are far fewer than nine per multiprocessor
     ff.FUSED_GATE_ROWS = 1024                # so that this small part takes both ways
     x = torch.randn(rows, 72, generator=g).to(torch.bfloat16)
     got = ff.forward(x.to(DEV), None).float().cpu()
