@@ -34,6 +34,7 @@ def uniform(seed: int, counter: int, v: int) -> float:
 class Sampler:
     def __init__(self, device):
         self.device = torch.device(device)
+        self._zeros: dict = {}            # rows -> (temperatures, seeds and counters) of greedy sampling, made once
 
     def sample(self, logits: torch.Tensor, temperatures, seeds, counters) -> torch.Tensor:
         """One token (int32, on the device) per row of float32 logits."""
@@ -47,6 +48,8 @@ class Sampler:
 
     def greedy(self, logits: torch.Tensor) -> torch.Tensor:
         rows = logits.shape[0]
-        z = torch.zeros(rows, dtype=torch.float32, device=self.device)
-        zi = torch.zeros(rows, dtype=torch.int64, device=self.device)
-        return ops.sample(logits, z, zi, zi)
+        zeros = self._zeros.get(rows)
+        if zeros is None:
+            zeros = self._zeros[rows] = (torch.zeros(rows, dtype=torch.float32, device=self.device),
+                                         torch.zeros(rows, dtype=torch.int64, device=self.device))
+        return ops.sample(logits, zeros[0], zeros[1], zeros[1])
