@@ -380,15 +380,17 @@ def micro(spec: str, reps: int, eager: bool = False) -> int:
     return 0
 
 
-def timeline(batch: int, layers: int) -> int:
+def timeline(batch: int, layers: int, shape=None) -> int:
     """Start, duration and end of every kernel of one replayed decode step (torch's profiler; programmatic dependent
     launch lets kernels overlap, so a kernel's start is when its first block became resident, and the increments from
-    end to end tell what each adds to the step): `python bench.py --timeline 8 --layers 4`."""
+    end to end tell what each adds to the step): `python bench.py --timeline 8 --layers 4`; with `--workload NAME`
+    the layer sizes of that workload's shape instead of the 8B ones."""
     import torch
     from torch.profiler import ProfilerActivity, profile
     from jax_vllm_b200 import make_driver, random_model, registry
     from jax_vllm_b200.engine import StepEntry
-    model = random_model(registry.config_from_dict(dict(QWEN3_8B, num_hidden_layers=layers)), seed=5, dtype="bf16")
+    cfg = dict(QWEN3_8B, **(WORKLOADS[shape]["config"] if shape else {}))
+    model = random_model(registry.config_from_dict(dict(cfg, num_hidden_layers=layers)), seed=5, dtype="bf16")
     driver = make_driver(model, max_num_seqs=batch, max_model_len=CONTEXT + 64, block_size=PAGE, prefix_cache=False)
     rcs = fake_context(driver, batch, CONTEXT)
 
@@ -522,10 +524,10 @@ def main():
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
+    if args.timeline:
+        return timeline(args.timeline, args.layers or 4, args.workload)
     if args.workload:
         return workload(args.workload, args.layers)
-    if args.timeline:
-        return timeline(args.timeline, args.layers or 4)
     args.layers = args.layers or QWEN3_8B["num_hidden_layers"]
     warmup = max(3, args.warmup)
 
